@@ -1,0 +1,362 @@
+// Cache lookup, row gathers and the one-pass assembly of batch.x.
+//
+// Replaces the torch index arithmetic of HistoryCache.lookup_and_load
+// (hiscache/history_cache.py:275-356) and HistoryTable.lookup
+// (hiscache/history_table.py:94-125).  The reference builds batch.x with a
+// masked host read followed by two more full-width passes; here one kernel
+// decides per row between the host-resident table, the raw-feature cache in
+// HBM and zeros, and writes the row once.
+#include "common.cuh"
+
+namespace hc {
+
+// Moves `units` groups of 8 elements (unit8) or 4 fp32 elements (unit4) of one
+// row with 16-byte accesses; `gl`/`G` = lane and width of the lane group.
+__device__ __forceinline__ void load_unit8(const void* src, int sdt, int64_t off, float* f) {
+  if (sdt == HC_F16) {
+    Vec16<__half>::unpack(ldg16(reinterpret_cast<const __half*>(src) + off), f);
+  } else {
+    Vec16<float>::unpack(ldg16(reinterpret_cast<const float*>(src) + off), f);
+    Vec16<float>::unpack(ldg16(reinterpret_cast<const float*>(src) + off + 4), f + 4);
+  }
+}
+__device__ __forceinline__ void store_unit8(void* dst, int ddt, int64_t off, const float* f) {
+  if (ddt == HC_F16) {
+    __half2 h0 = __floats2half2_rn(f[0], f[1]), h1 = __floats2half2_rn(f[2], f[3]);
+    __half2 h2 = __floats2half2_rn(f[4], f[5]), h3 = __floats2half2_rn(f[6], f[7]);
+    uint4 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(dst) + off) = pk;
+  } else {
+    float4* d = reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + off);
+    d[0] = make_float4(f[0], f[1], f[2], f[3]);
+    d[1] = make_float4(f[4], f[5], f[6], f[7]);
+  }
+}
+
+// Copies / converts one row. src == nullptr writes zeros.
+//   mode 2: same dtype, 16-byte copies; mode 1: groups of 8 elements with
+//   conversion; mode 0: scalar.
+__device__ __forceinline__ void move_row(const void* src, int sdt, int64_t soff, void* dst,
+                                         int ddt, int64_t doff, int feat, int gl, int G,
+                                         int mode) {
+  if (mode == 2) {
+    const int es = ddt == HC_F16 ? 2 : 4;
+    const int nvec = feat * es / 16;
+    const char* s = src ? reinterpret_cast<const char*>(src) + soff * es : nullptr;
+    char* d = reinterpret_cast<char*>(dst) + doff * es;
+    for (int v = gl; v < nvec; v += G)
+      reinterpret_cast<uint4*>(d)[v] = s ? ldg16(s + 16 * v) : make_uint4(0u, 0u, 0u, 0u);
+  } else if (mode == 1) {
+    for (int u = gl; u < (feat >> 3); u += G) {
+      float f[8];
+      if (src) {
+        load_unit8(src, sdt, soff + 8 * u, f);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) f[k] = 0.f;
+      }
+      store_unit8(dst, ddt, doff + 8 * u, f);
+    }
+  } else {
+    for (int c = gl; c < feat; c += G)
+      store_from_f32(dst, ddt, doff + c, src ? load_as_f32(src, sdt, soff + c) : 0.f);
+  }
+}
+
+__global__ void map_lookup_kernel(const int64_t* __restrict__ map, int64_t map_len,
+                                  const int64_t* __restrict__ ids, int64_t n, int64_t offset,
+                                  int64_t force_miss_below, int64_t* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int64_t v = -1;
+  if (i >= force_miss_below) {
+    int64_t p = ids[i] + offset;
+    if (p < 0) p += map_len;  // torch negative indexing
+    if (p >= 0 && p < map_len) v = map[p];
+  }
+  out[i] = v;
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+    gather_rows_kernel(const void* __restrict__ table, int tdt, int64_t table_rows,
+                       int64_t table_stride, int feat, const int64_t* __restrict__ rows, int64_t n,
+                       int zero_missing, void* __restrict__ out, int odt, int64_t out_stride,
+                       int mode) {
+  const int gl = threadIdx.x % G;
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  if (i >= n) return;
+  int64_t r = rows[i];
+  const void* src = table;
+  if (r < 0) {
+    if (zero_missing) src = nullptr;
+    r += table_rows;  // -1 reads the last row
+  }
+  if (r < 0 || r >= table_rows) src = nullptr;
+  move_row(src, tdt, r * table_stride, out, odt, i * out_stride, feat, gl, G, mode);
+}
+
+struct LoadArgs {
+  const void* host_table; int host_dtype; int64_t host_rows; int64_t host_stride;
+  const void* feat_cache; int cache_dtype; int64_t cache_rows; int64_t cache_stride;
+  int feat;
+  const int64_t* sub_to_full; const int64_t* sub2feat; const uint8_t* used;
+  int64_t n;
+  void* x; int x_dtype; int64_t x_stride;
+  uint8_t* load_mask_out; unsigned long long* stats;
+  int host_mode, cache_mode, zero_mode;
+};
+
+template <int G>
+__global__ void __launch_bounds__(256) load_rows_kernel(const LoadArgs a) {
+  const int gl = threadIdx.x % G;
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  const bool live = i < a.n;
+  int from_host = 0, from_cache = 0;
+  if (live) {
+    const int64_t sf = a.sub2feat ? a.sub2feat[i] : -1;
+    const bool used = a.used == nullptr || a.used[i] != 0;
+    const bool load = used && sf == -1;
+    if (load) {
+      const int64_t g = a.sub_to_full[i];
+      const bool ok = g >= 0 && g < a.host_rows;
+      move_row(ok ? a.host_table : nullptr, a.host_dtype, g * a.host_stride, a.x, a.x_dtype,
+               i * a.x_stride, a.feat, gl, G, ok ? a.host_mode : a.zero_mode);
+      from_host = gl == 0;
+    } else if (sf != -1) {
+      int64_t r = sf < 0 ? sf + a.cache_rows : sf;
+      const bool ok = r >= 0 && r < a.cache_rows;
+      move_row(ok ? a.feat_cache : nullptr, a.cache_dtype, r * a.cache_stride, a.x, a.x_dtype,
+               i * a.x_stride, a.feat, gl, G, ok ? a.cache_mode : a.zero_mode);
+      from_cache = gl == 0;
+    } else {
+      move_row(nullptr, a.x_dtype, 0, a.x, a.x_dtype, i * a.x_stride, a.feat, gl, G, a.zero_mode);
+    }
+    if (a.load_mask_out && gl == 0) a.load_mask_out[i] = load ? 1 : 0;
+  }
+  if (a.stats) {
+    const int h = __syncthreads_count(from_host), c = __syncthreads_count(from_cache);
+    if (threadIdx.x == 0) {
+      if (h) atomicAdd(a.stats, (unsigned long long)h);
+      if (c) atomicAdd(a.stats + 1, (unsigned long long)c);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    owner_lookup_flags_kernel(const int64_t* __restrict__ map, int64_t map_len,
+                              const int64_t* __restrict__ ids, int64_t n, int64_t* slots,
+                              uint8_t* flags) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int64_t id = ids[k];
+  const int64_t s = (id >= 0 && id < map_len) ? map[id] : -1;
+  if (slots) slots[k] = s;
+  flags[k] = s != -1;
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+    owner_lookup_rows_kernel(const int64_t* __restrict__ map, int64_t map_len,
+                             const int64_t* __restrict__ ids, int64_t n,
+                             const void* __restrict__ table, int dt, int64_t table_rows,
+                             int64_t table_stride, int feat, void* __restrict__ rows_out,
+                             int64_t out_stride, uint8_t* __restrict__ flags, int mode) {
+  const int gl = threadIdx.x % G;
+  const int64_t k = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  if (k >= n) return;
+  const int64_t id = ids[k];
+  const int64_t s = (id >= 0 && id < map_len) ? map[id] : -1;
+  const bool hit = s >= 0 && s < table_rows;
+  if (gl == 0) flags[k] = hit ? 1 : 0;
+  if (hit) move_row(table, dt, s * table_stride, rows_out, dt, k * out_stride, feat, gl, G, mode);
+}
+
+template <int G>
+__global__ void __launch_bounds__(256)
+    unpermute_rows_kernel(const void* __restrict__ src, int dt, int64_t src_stride, int feat,
+                          const int64_t* __restrict__ perm, const uint8_t* __restrict__ flags,
+                          int64_t n, void* __restrict__ dst, int64_t dst_stride,
+                          int64_t* __restrict__ hit_out, int mode) {
+  const int gl = threadIdx.x % G;
+  const int64_t k = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
+  if (k >= n) return;
+  const int64_t p = perm[k];
+  const bool on = flags == nullptr || flags[k] != 0;
+  if (hit_out && gl == 0) hit_out[p] = on ? k : -1;
+  if (on && dst) move_row(src, dt, k * src_stride, dst, dt, p * dst_stride, feat, gl, G, mode);
+}
+
+// how a row of `feat` elements can be moved between the two layouts
+static int move_mode(const void* src, int sdt, int64_t sstride, const void* dst, int ddt,
+                     int64_t dstride, int feat) {
+  const int ss = dtype_size(sdt), ds = dtype_size(ddt);
+  const bool s_ok = src == nullptr || (aligned16(src) && (sstride * ss) % 16 == 0);
+  const bool d_ok = aligned16(dst) && (dstride * ds) % 16 == 0;
+  if (!s_ok || !d_ok) return 0;
+  if (sdt == ddt && ((int64_t)feat * ds) % 16 == 0) return 2;
+  if (feat % 8 == 0) return 1;
+  return 0;
+}
+
+static int group_width(int feat, int mode, int dt) {
+  int units = mode == 2 ? feat * dtype_size(dt) / 16 : (mode == 1 ? feat / 8 : feat);
+  int g = 4;
+  while (g < 32 && g < units) g <<= 1;
+  return g;
+}
+
+}  // namespace hc
+
+using namespace hc;
+
+#define HC_DISPATCH_G(G, ...)                \
+  switch (G) {                               \
+    case 4: { constexpr int kG = 4; __VA_ARGS__; } break;   \
+    case 8: { constexpr int kG = 8; __VA_ARGS__; } break;   \
+    case 16: { constexpr int kG = 16; __VA_ARGS__; } break; \
+    default: { constexpr int kG = 32; __VA_ARGS__; } break; \
+  }
+
+extern "C" int hc_map_lookup(const int64_t* map, int64_t map_len, const int64_t* ids, int64_t n,
+                             int64_t offset, int64_t force_miss_below, int64_t* out, void* stream) {
+  HC_REQUIRE(n >= 0 && map_len >= 0, HC_ERR_SIZE);
+  if (n == 0) return 0;
+  HC_REQUIRE(map && ids && out, HC_ERR_NULL);
+  const int64_t blocks = ceil_div(n, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  map_lookup_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      map, map_len, ids, n, offset, force_miss_below, out);
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_gather_rows(const void* table, int32_t table_dtype, int64_t table_rows,
+                              int64_t table_stride, int32_t feat, const int64_t* rows, int64_t n,
+                              int32_t zero_missing, void* out, int32_t out_dtype,
+                              int64_t out_stride, void* stream) {
+  HC_REQUIRE(n >= 0 && feat > 0 && table_rows >= 0, HC_ERR_SIZE);
+  HC_REQUIRE(dtype_size(table_dtype) && dtype_size(out_dtype), HC_ERR_DTYPE);
+  if (n == 0) return 0;
+  HC_REQUIRE(rows && out && (table || table_rows == 0), HC_ERR_NULL);
+  if (table_stride == 0) table_stride = feat;
+  if (out_stride == 0) out_stride = feat;
+  HC_REQUIRE(table_stride >= feat && out_stride >= feat, HC_ERR_SIZE);
+  const int mode = move_mode(table, table_dtype, table_stride, out, out_dtype, out_stride, feat);
+  const int G = group_width(feat, mode, out_dtype);
+  const int64_t blocks = ceil_div(n * G, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  HC_DISPATCH_G(G, gather_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(
+                       table, table_dtype, table_rows, table_stride, feat, rows, n, zero_missing,
+                       out, out_dtype, out_stride, mode));
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                            int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
+                            int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                            const int64_t* sub_to_full, const int64_t* sub2feat,
+                            const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                            int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                            void* stream) {
+  HC_REQUIRE(n >= 0 && feat > 0 && host_rows >= 0 && cache_rows >= 0, HC_ERR_SIZE);
+  HC_REQUIRE(dtype_size(x_dtype) != 0, HC_ERR_DTYPE);
+  if (n == 0) return 0;
+  HC_REQUIRE(sub_to_full && x, HC_ERR_NULL);
+  HC_REQUIRE(host_table != nullptr || host_rows == 0, HC_ERR_NULL);
+  if (host_table) HC_REQUIRE(dtype_size(host_dtype) != 0, HC_ERR_DTYPE);
+  if (sub2feat) {
+    HC_REQUIRE(feat_cache != nullptr || cache_rows == 0, HC_ERR_NULL);
+    if (feat_cache) HC_REQUIRE(dtype_size(cache_dtype) != 0, HC_ERR_DTYPE);
+  }
+  if (host_stride == 0) host_stride = feat;
+  if (cache_stride == 0) cache_stride = feat;
+  if (x_stride == 0) x_stride = feat;
+  HC_REQUIRE(host_stride >= feat && cache_stride >= feat && x_stride >= feat, HC_ERR_SIZE);
+  LoadArgs a{};
+  a.host_table = host_table; a.host_dtype = host_table ? host_dtype : x_dtype;
+  a.host_rows = host_table ? host_rows : 0; a.host_stride = host_stride;
+  a.feat_cache = feat_cache; a.cache_dtype = feat_cache ? cache_dtype : x_dtype;
+  a.cache_rows = feat_cache ? cache_rows : 0; a.cache_stride = cache_stride;
+  a.feat = feat; a.sub_to_full = sub_to_full; a.sub2feat = sub2feat; a.used = used; a.n = n;
+  a.x = x; a.x_dtype = x_dtype; a.x_stride = x_stride; a.load_mask_out = load_mask_out;
+  a.stats = reinterpret_cast<unsigned long long*>(stats);
+  a.zero_mode = move_mode(nullptr, x_dtype, 0, x, x_dtype, x_stride, feat);
+  a.host_mode = host_table ? move_mode(host_table, a.host_dtype, host_stride, x, x_dtype, x_stride, feat) : a.zero_mode;
+  a.cache_mode = feat_cache ? move_mode(feat_cache, a.cache_dtype, cache_stride, x, x_dtype, x_stride, feat) : a.zero_mode;
+  int worst = a.zero_mode < a.host_mode ? a.zero_mode : a.host_mode;
+  if (a.cache_mode < worst) worst = a.cache_mode;
+  const int G = group_width(feat, worst, x_dtype);
+  const int64_t blocks = ceil_div(n * G, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  HC_DISPATCH_G(G, load_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(a));
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids, int64_t n,
+                               const void* table, int32_t dtype, int64_t table_rows,
+                               int64_t table_stride, int32_t feat, void* rows_out,
+                               int64_t out_stride, uint8_t* flags, void* stream) {
+  HC_REQUIRE(n >= 0 && map_len >= 0 && table_rows >= 0, HC_ERR_SIZE);
+  if (n == 0) return 0;
+  HC_REQUIRE(map && ids && flags, HC_ERR_NULL);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows_out == nullptr) {
+    const int64_t blocks = ceil_div(n, 256);
+    HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+    owner_lookup_flags_kernel<<<(unsigned)blocks, 256, 0, st>>>(map, map_len, ids, n, nullptr, flags);
+    HC_LAUNCH_OK();
+    return 0;
+  }
+  HC_REQUIRE(feat > 0, HC_ERR_SIZE);
+  HC_REQUIRE(dtype_size(dtype) != 0, HC_ERR_DTYPE);
+  HC_REQUIRE(table != nullptr || table_rows == 0, HC_ERR_NULL);
+  if (table_stride == 0) table_stride = feat;
+  if (out_stride == 0) out_stride = feat;
+  HC_REQUIRE(table_stride >= feat && out_stride >= feat, HC_ERR_SIZE);
+  const int mode = move_mode(table, dtype, table_stride, rows_out, dtype, out_stride, feat);
+  const int G = group_width(feat, mode, dtype);
+  const int64_t blocks = ceil_div(n * G, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  HC_DISPATCH_G(G, owner_lookup_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(
+                       map, map_len, ids, n, table, dtype, table_rows, table_stride, feat,
+                       rows_out, out_stride, flags, mode));
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_unpermute_rows(const void* src, int32_t dtype, int64_t src_stride, int32_t feat,
+                                 const int64_t* perm, const uint8_t* flags, int64_t n, void* dst,
+                                 int64_t dst_stride, int64_t* hit_out, void* stream) {
+  HC_REQUIRE(n >= 0, HC_ERR_SIZE);
+  if (n == 0) return 0;
+  HC_REQUIRE(perm != nullptr, HC_ERR_NULL);
+  HC_REQUIRE(dst != nullptr || hit_out != nullptr, HC_ERR_NULL);
+  int mode = 0, G = 4;
+  if (dst) {
+    HC_REQUIRE(src != nullptr, HC_ERR_NULL);
+    HC_REQUIRE(feat > 0, HC_ERR_SIZE);
+    HC_REQUIRE(dtype_size(dtype) != 0, HC_ERR_DTYPE);
+    if (src_stride == 0) src_stride = feat;
+    if (dst_stride == 0) dst_stride = feat;
+    HC_REQUIRE(src_stride >= feat && dst_stride >= feat, HC_ERR_SIZE);
+    mode = move_mode(src, dtype, src_stride, dst, dtype, dst_stride, feat);
+    G = group_width(feat, mode, dtype);
+  }
+  const int64_t blocks = ceil_div(n * G, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  HC_DISPATCH_G(G, unpermute_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(
+                       src, dtype, src_stride, feat, perm, flags, n, dst, dst_stride, hit_out,
+                       mode));
+  HC_LAUNCH_OK();
+  return 0;
+}

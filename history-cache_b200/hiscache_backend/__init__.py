@@ -1,0 +1,515 @@
+"""`hiscache_backend`: the operator module of HisCache, backed by libhiscache_b200.
+
+The eight functions of the reference's pybind11 module keep their names,
+argument order and meaning (src/cpp/python_bindings/binding.cpp:9-19):
+
+    record_history, count_history_reconstruct, count_num,
+    get_graph_structure_score, aggr_forward_history,
+    aggr_forward_history_edge_value, p2psend, p2psend_gentensor
+
+Differences that a caller can observe: argument errors raise RuntimeError
+instead of ending the process (src/cpp/include/common.h:13-34); ring slots in
+record_history follow ascending row order instead of warp-scheduling order
+(src/cpp/src/grad_check.cu:25); history_size == 0 means "no history" instead
+of exit(1) (src/cpp/src/history_aggr.cu:440-441).
+
+The functions below the line are the wider operators the `hiscache` package
+uses: history rows read straight from the table, per-source select inside the
+gather, fp16 storage, the admission score fused into the backward pass, the
+device-side threshold and admission, row assembly from host-resident features.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _capi
+from ._capi import (HC_F16, HC_F32, HC_SCORE_L1, HC_SCORE_L2, AggrArgs, check, dtype_code, i64c,
+                    lib, ptr, require_cuda, rows2d, scratch, stream_of)
+
+__all__ = [
+    "record_history", "count_history_reconstruct", "count_num", "get_graph_structure_score",
+    "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
+    "aggr_forward", "score_rows", "select_threshold", "cache_admit", "evict_stale",
+    "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
+    "unpermute_rows", "owner_lookup", "mix64", "launch_count",
+]
+
+_launches = 0
+
+
+def launch_count() -> int:
+    """Number of library entry points called so far in this process."""
+    return _launches
+
+
+def _called(n=1):
+    global _launches
+    _launches += n
+
+
+def _empty(t):
+    return t is None or (isinstance(t, torch.Tensor) and t.numel() == 0)
+
+
+# ---------------------------------------------------------------------------
+# aggregation
+# ---------------------------------------------------------------------------
+def _aggr_args(inp, ptr_t, idx_t, num_node, edge_value, hmap, hbuf, h_indexed, src_map, src_alt):
+    a = AggrArgs()
+    a.struct_size = C.sizeof(AggrArgs)
+    multi = inp.dim() == 3
+    H = inp.shape[1] if multi else 1
+    F = inp.shape[-1]
+    a.ptr, a.idx, a.num_node = ptr(ptr_t), ptr(idx_t), num_node
+    a.input, a.in_dtype, a.feat, a.num_head = ptr(inp), dtype_code(inp), F, H
+    a.n_src, a.in_stride = inp.shape[0], inp.stride(0) if inp.shape[0] > 1 else H * F
+    if src_map is not None:
+        a.src_map, a.src_alt = ptr(src_map), ptr(src_alt)
+        a.alt_dtype = dtype_code(src_alt)
+        a.alt_stride = src_alt.stride(0) if src_alt.shape[0] > 1 else H * F
+    a.edge_value = ptr(edge_value)
+    if hmap is not None:
+        a.hmap, a.hbuf, a.h_dtype = ptr(hmap), ptr(hbuf), dtype_code(hbuf)
+        a.h_indexed = 1 if h_indexed else 0
+        a.hsize = hbuf.stride(0) if hbuf.dim() > 1 and hbuf.shape[0] > 1 else hbuf.shape[-1]
+    return a
+
+
+class _AggrFunction(torch.autograd.Function):
+    """Counterpart of AggrHistoryFunction / AggrHistoryEdgeValueFunction
+    (src/cpp/src/history_aggr.cu:475-596).  Saves the index tensors themselves
+    (the reference keeps raw device pointers across forward and backward,
+    history_aggr.cu:406-408)."""
+
+    @staticmethod
+    def forward(ctx, inp, ptr_t, idx_t, edge_value, hmap, hbuf, num_node, h_indexed, src_map,
+                src_alt, score_out, score_kind):
+        dev = require_cuda(inp, ptr_t, idx_t, edge_value, hmap, hbuf, src_map, src_alt)
+        inp = rows2d(inp)
+        ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
+        hmap, src_map = i64c(hmap, "history_map"), i64c(src_map, "src_map")
+        if edge_value is not None:
+            edge_value = edge_value.contiguous()
+            if edge_value.dtype != torch.float32:
+                raise TypeError("edge_value must be float32")
+        if hbuf is not None:
+            hbuf = rows2d(hbuf)
+        if src_alt is not None:
+            src_alt = rows2d(src_alt)
+        multi = inp.dim() == 3
+        if idx_t.numel() == 0:  # a block without edges still needs a valid address
+            idx_t = torch.zeros(1, dtype=torch.int64, device=dev)
+        if ptr_t.shape[0] < num_node + 1:
+            raise RuntimeError(f"aggr_forward: ptr has {ptr_t.shape[0]} entries, need {num_node + 1}")
+        if hmap is not None and hmap.shape[0] < num_node:
+            raise RuntimeError("aggr_forward: history_map shorter than num_node")
+        if hmap is not None and not h_indexed and hbuf.shape[0] < num_node:
+            raise RuntimeError("aggr_forward: row-aligned history_buffer shorter than num_node")
+        shape = (num_node, inp.shape[1], inp.shape[2]) if multi else (num_node, inp.shape[1])
+        out = torch.empty(shape, dtype=torch.float32, device=dev)
+        a = _aggr_args(inp, ptr_t, idx_t, num_node, edge_value, hmap, hbuf, h_indexed, src_map, src_alt)
+        with torch.cuda.device(dev):
+            check(lib.hc_aggr_fwd(C.byref(a), ptr(out), stream_of(dev)), "hc_aggr_fwd")
+        _called()
+        ctx.save_for_backward(inp, ptr_t, idx_t, edge_value, hmap, hbuf, src_map, src_alt)
+        ctx.num_node, ctx.h_indexed = num_node, h_indexed
+        ctx.score_out, ctx.score_kind = score_out, score_kind
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        inp, ptr_t, idx_t, edge_value, hmap, hbuf, src_map, src_alt = ctx.saved_tensors
+        dev = inp.device
+        grad_out = grad_out.contiguous()
+        if grad_out.dtype != torch.float32:
+            grad_out = grad_out.float()
+        need_in = ctx.needs_input_grad[0]
+        need_ev = edge_value is not None and ctx.needs_input_grad[3]
+        need_h = hbuf is not None and ctx.needs_input_grad[5]
+        if need_h and ctx.h_indexed:
+            raise RuntimeError("gradients w.r.t. an indexed history table are not defined; "
+                               "pass a row-aligned history_buffer")
+        a = _aggr_args(inp, ptr_t, idx_t, ctx.num_node, edge_value, hmap, hbuf, ctx.h_indexed,
+                       src_map, src_alt)
+        g_in = torch.empty(inp.shape, dtype=torch.float32, device=dev) if need_in else None
+        g_ev = torch.empty_like(edge_value) if need_ev else None
+        g_h = None
+        if need_h:
+            g_h = torch.zeros(hbuf.shape, dtype=torch.float32, device=dev)
+            a.hsize = hbuf.shape[-1]  # grad_history is dense
+        score = ctx.score_out
+        if score is not None and (inp.dim() == 3):
+            score = None
+        if not (need_in or need_ev or need_h or score is not None):
+            return (None,) * 12
+        with torch.cuda.device(dev):
+            check(lib.hc_aggr_bwd(C.byref(a), ptr(grad_out), ptr(g_in), 1, ptr(g_h), ptr(g_ev),
+                                  ptr(score), ctx.score_kind, stream_of(dev)), "hc_aggr_bwd")
+        _called()
+        if g_in is not None and g_in.dtype != inp.dtype:
+            g_in = g_in.to(inp.dtype)
+        if g_h is not None and g_h.dtype != hbuf.dtype:
+            g_h = g_h.to(hbuf.dtype)
+        return g_in, None, None, g_ev, None, g_h, None, None, None, None, None, None
+
+
+def aggr_forward(input, ptr, idx, num_node=0, *, history_map=None, history_buffer=None,
+                 indexed=False, edge_value=None, src_map=None, src_alt=None, score_out=None,
+                 score_kind=HC_SCORE_L2):
+    """History-aware aggregation.
+
+    out[r] = history row if history_map[r] != -1 else mean (or edge-weighted sum) of the
+    source rows of r's neighbours.  `indexed=True` reads row history_map[r] of
+    `history_buffer` (the table itself); otherwise row r (a row-aligned gather, the
+    reference layout).  `src_map`/`src_alt` choose, per source, a cached row instead of the
+    fresh one.  If `score_out` (fp32 [num_node]) is given, the backward pass writes the
+    per-row admission score of the incoming gradient into it.
+    The result always requires grad (history_aggr.cu:604).
+    """
+    if num_node == 0:
+        num_node = ptr.shape[0] - 1
+    if _empty(history_map) or _empty(history_buffer):
+        history_map = history_buffer = None
+    if _empty(edge_value):
+        edge_value = None
+    if _empty(src_map):
+        src_map = src_alt = None
+    out = _AggrFunction.apply(input, ptr, idx, edge_value, history_map, history_buffer,
+                              int(num_node), bool(indexed), src_map, src_alt, score_out,
+                              int(score_kind))
+    if not out.requires_grad:
+        out.requires_grad_(True)
+    return out
+
+
+def aggr_forward_history(input, ptr, idx, history_map, history_buffer, history_size, num_node):
+    """src/cpp/src/history_aggr.cu:598-606.  history_buffer is row-aligned: row r of it
+    replaces output row r where history_map[r] != -1."""
+    if history_size == 0:
+        history_map = history_buffer = None
+    elif not _empty(history_buffer) and history_buffer.dim() == 1:
+        history_buffer = history_buffer.view(-1, history_size)
+    return aggr_forward(input, ptr, idx, num_node, history_map=history_map,
+                        history_buffer=history_buffer)
+
+
+def aggr_forward_history_edge_value(input, ptr, idx, edge_value, history_map, history_buffer,
+                                    history_size, num_node):
+    """src/cpp/src/history_aggr.cu:608-617: weighted sum; edge_value [E] or [E, H] with
+    input [n, H, F]."""
+    if history_size == 0:
+        history_map = history_buffer = None
+    elif not _empty(history_buffer) and history_buffer.dim() == 1:
+        history_buffer = history_buffer.view(-1, history_size)
+    if _empty(edge_value):
+        raise RuntimeError("aggr_forward_history_edge_value: edge_value is empty")
+    if edge_value.dim() == 2 and (input.dim() != 3 or input.shape[1] != edge_value.shape[1]):
+        raise RuntimeError("multi-head edge_value needs input [n, num_head, feat] "
+                           "(history_aggr.cu:421-422)")
+    return aggr_forward(input, ptr, idx, num_node, history_map=history_map,
+                        history_buffer=history_buffer, edge_value=edge_value)
+
+
+# ---------------------------------------------------------------------------
+# scores, threshold, admission, eviction
+# ---------------------------------------------------------------------------
+def score_rows(x, kind=HC_SCORE_L2, out=None):
+    """Per-row L2 / L1 norm in the library's fixed reduction order."""
+    dev = require_cuda(x)
+    x = rows2d(x)
+    if x.dtype != torch.float32:
+        x = x.float()
+    n, F = x.shape
+    if out is None:
+        out = torch.empty(n, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_score_rows(ptr(x), n, F, x.stride(0) if n > 1 else F, kind, ptr(out),
+                                stream_of(dev)), "hc_score_rows")
+    _called()
+    return out
+
+
+def select_threshold(score, q, out=None):
+    """torch.quantile(score, q) (linear interpolation) without leaving the device."""
+    dev = require_cuda(score)
+    score = score.contiguous()
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
+                                      stream_of(dev)), "hc_select_threshold")
+    _called()
+    return out
+
+
+def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_history,
+                   history_to_full, full_to_history, header, score, thres, checkin_iter, glb_iter,
+                   n_admitted=None):
+    """src/cpp/src/grad_check.cu:48-68, same argument order; mutates buffer_all, both maps,
+    header and checkin_iter in place.  `thres` is a 1-element tensor."""
+    dev = require_cuda(buffer_new, buffer_all, sub_to_full, sub_to_history, history_to_full,
+                       full_to_history, header, score, thres, checkin_iter)
+    buffer_new = rows2d(buffer_new)
+    if buffer_new.dtype != torch.float32:
+        buffer_new = buffer_new.float()
+    n, hs = buffer_new.shape
+    if not buffer_all.is_contiguous():
+        raise RuntimeError("record_history: buffer_all must be contiguous")
+    if buffer_all.shape[1] != hs:
+        raise RuntimeError("record_history: row widths differ")
+    for name, t in (("history_to_full", history_to_full), ("full_to_history", full_to_history),
+                    ("header", header), ("checkin_iter", checkin_iter)):
+        if t.dtype != torch.int64 or not t.is_contiguous():
+            raise TypeError(f"record_history: {name} must be contiguous int64")
+    if used_mask is not None:
+        if used_mask.dtype not in (torch.bool, torch.uint8):
+            raise TypeError("record_history: used_mask must be bool")
+        used_mask = used_mask.contiguous()
+        if used_mask.shape[0] < n:
+            raise RuntimeError("record_history: used_mask shorter than buffer_new")
+    if sub_to_full.shape[0] < n or sub_to_history.shape[0] < n or score.shape[0] < n:
+        raise RuntimeError("record_history: per-row arguments shorter than buffer_new")
+    thres = thres.reshape(-1).float()
+    sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
+    with torch.cuda.device(dev):
+        check(lib.hc_record_history(
+            ptr(buffer_new), buffer_new.stride(0) if n > 1 else hs, n, ptr(buffer_all),
+            dtype_code(buffer_all), buffer_all.shape[0], hs, ptr(used_mask),
+            ptr(i64c(sub_to_full)), ptr(i64c(sub_to_history)), ptr(history_to_full),
+            ptr(full_to_history), ptr(header), ptr(score.contiguous().float()), ptr(thres),
+            ptr(checkin_iter), int(glb_iter), ptr(n_admitted), ptr(sc), stream_of(dev)),
+            "hc_record_history")
+    _called()
+
+
+def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, sub2embed, score,
+                thres, full2embed, total_num_node, embed2full, feat2full, header,
+                reset_header=False, n_admitted=None):
+    """Device-side HistoryCache.update_history (hiscache/history_cache.py:211-254)."""
+    dev = require_cuda(produced, buffer, sub_to_full, sub2embed, score, thres, full2embed,
+                       embed2full, header)
+    produced = rows2d(produced)
+    if produced.dtype != torch.float32:
+        produced = produced.float()
+    n = produced.shape[0]
+    sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
+    f2f_len = 0 if feat2full is None else feat2full.shape[0]
+    with torch.cuda.device(dev):
+        check(lib.hc_cache_admit(
+            ptr(produced), produced.stride(0) if n > 1 else hidden, n, ptr(buffer),
+            dtype_code(buffer), hidden, in_feat, embed_capacity, ptr(i64c(sub_to_full)),
+            ptr(i64c(sub2embed)), ptr(score), ptr(thres), ptr(full2embed), total_num_node,
+            ptr(embed2full), ptr(feat2full), f2f_len, ptr(header), 1 if reset_header else 0,
+            ptr(n_admitted), ptr(sc), stream_of(dev)), "hc_cache_admit")
+    _called()
+
+
+def evict_stale(checkin_iter, history_to_full, full_to_history, glb_iter, limit):
+    """hiscache/history_table.py:189-200."""
+    dev = require_cuda(checkin_iter, history_to_full, full_to_history)
+    with torch.cuda.device(dev):
+        check(lib.hc_evict_stale(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
+                                 checkin_iter.shape[0], int(glb_iter), int(limit),
+                                 stream_of(dev)), "hc_evict_stale")
+    _called()
+
+
+def evict_by_score(sub_to_history, score, thres, checkin_iter, history_to_full, full_to_history):
+    """hiscache/history_table.py:234-241."""
+    dev = require_cuda(sub_to_history, score, thres, checkin_iter)
+    n = min(sub_to_history.shape[0], score.shape[0])
+    with torch.cuda.device(dev):
+        check(lib.hc_evict_by_score(ptr(i64c(sub_to_history)), ptr(score.contiguous()),
+                                    ptr(thres.reshape(-1)), n, ptr(checkin_iter),
+                                    ptr(history_to_full), ptr(full_to_history), stream_of(dev)),
+              "hc_evict_by_score")
+    _called()
+
+
+# ---------------------------------------------------------------------------
+# receptive-field bookkeeping
+# ---------------------------------------------------------------------------
+def count_history_reconstruct(ptr_t, idx_t, history_maps, num_node, num_seed, num_layer):
+    """src/cpp/src/grad_check.cu:103-130: list of num_layer+1 bool masks [num_node];
+    [num_layer] is the seed level, [0] gates raw-feature loading."""
+    dev = require_cuda(ptr_t, idx_t)
+    ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
+    hm = None if _empty(history_maps) else i64c(history_maps, "history_maps")
+    buf = torch.empty((num_layer + 1, num_node), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_used_masks(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, ptr(hm),
+                                0 if hm is None else hm.shape[0], num_node, num_seed, num_layer,
+                                ptr(buf), stream_of(dev)), "hc_used_masks")
+    _called()
+    b = buf.view(torch.bool)
+    return [b[k] for k in range(num_layer + 1)]
+
+
+def get_graph_structure_score(ptr_t, idx_t, num_node, num_seed, num_layer):
+    """src/cpp/src/grad_check.cu:149-163 (level-synchronous, lowest-numbered parent wins)."""
+    dev = require_cuda(ptr_t, idx_t)
+    ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
+    out = torch.empty(num_node, dtype=torch.int64, device=dev)
+    sc = torch.empty(num_node, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_structure_score(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, num_node,
+                                     num_seed, num_layer, ptr(out), ptr(sc), stream_of(dev)),
+              "hc_structure_score")
+    _called()
+    return out
+
+
+def count_num(arr, mmax):
+    """src/cpp/src/grad_check.cu:174-182: int32 histogram [mmax+1]; value 0 is not counted."""
+    dev = require_cuda(arr)
+    arr = i64c(arr, "arr")
+    out = torch.empty(int(mmax) + 1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_count_num(ptr(arr), arr.shape[0], int(mmax), ptr(out), stream_of(dev)),
+              "hc_count_num")
+    _called()
+    return out
+
+
+# ---------------------------------------------------------------------------
+# lookup and row assembly
+# ---------------------------------------------------------------------------
+def map_lookup(map_t, ids, offset=0, force_miss_below=0, out=None):
+    """out[i] = map[ids[i] + offset]; first `force_miss_below` entries forced to -1."""
+    dev = require_cuda(map_t, ids)
+    ids = i64c(ids, "ids")
+    n = ids.shape[0]
+    if out is None:
+        out = torch.empty(n, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_map_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, int(offset),
+                                int(force_miss_below), ptr(out), stream_of(dev)), "hc_map_lookup")
+    _called()
+    return out
+
+
+def gather_rows(table, rows, zero_missing=False, out_dtype=None):
+    """table[rows] with torch's negative indexing (or zeros for -1 when zero_missing)."""
+    dev = require_cuda(table, rows)
+    table = rows2d(table)
+    rows = i64c(rows, "rows")
+    n, F = rows.shape[0], table.shape[1]
+    out = torch.empty((n, F), dtype=out_dtype or table.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_gather_rows(ptr(table), dtype_code(table), table.shape[0],
+                                 table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows), n,
+                                 1 if zero_missing else 0, ptr(out), dtype_code(out), F,
+                                 stream_of(dev)), "hc_gather_rows")
+    _called()
+    return out
+
+
+def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=None,
+              want_mask=False, stats=None):
+    """One-pass batch.x assembly (hiscache/history_cache.py:327-350).  host_table may be a
+    pinned host tensor (rows are then read over the host link by the kernel) or a CUDA
+    tensor.  Returns x, or (x, load_mask) when want_mask."""
+    dev = require_cuda(sub_to_full, sub2feat, used, feat_cache,
+                       host_table if host_table.is_cuda else None)
+    if not host_table.is_cuda and not host_table.is_pinned():
+        raise RuntimeError("load_rows: a host feature table must be pinned memory")
+    host_table = rows2d(host_table)
+    sub_to_full = i64c(sub_to_full, "sub_to_full")
+    sub2feat = i64c(sub2feat, "sub2feat")
+    n, F = sub_to_full.shape[0], host_table.shape[1]
+    x = torch.empty((n, F), dtype=out_dtype or host_table.dtype, device=dev)
+    mask = torch.empty(n, dtype=torch.uint8, device=dev) if want_mask else None
+    if used is not None:
+        used = used.contiguous()
+    cd, cr, cs = HC_F32, 0, 0
+    if feat_cache is not None:
+        feat_cache = rows2d(feat_cache)
+        cd, cr = dtype_code(feat_cache), feat_cache.shape[0]
+        cs = feat_cache.stride(0) if cr > 1 else F
+    with torch.cuda.device(dev):
+        check(lib.hc_load_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
+                               host_table.stride(0) if host_table.shape[0] > 1 else F,
+                               ptr(feat_cache), cd, cr, cs, F, ptr(sub_to_full), ptr(sub2feat),
+                               ptr(used), n, ptr(x), dtype_code(x), F, ptr(mask), ptr(stats),
+                               stream_of(dev)), "hc_load_rows")
+    _called()
+    return (x, mask.view(torch.bool)) if want_mask else x
+
+
+# ---------------------------------------------------------------------------
+# sharded-table helpers
+# ---------------------------------------------------------------------------
+def mix64(x: int) -> int:
+    return int(lib.hc_mix64(C.c_uint64(x & 0xFFFFFFFFFFFFFFFF)))
+
+
+def bucket_by_owner(ids, world, keep=None):
+    """Stable bucket sort by owner(id) = mix64(id) mod world: (counts, perm, bucketed)."""
+    dev = require_cuda(ids, keep)
+    ids = i64c(ids, "ids")
+    n = ids.shape[0]
+    counts = torch.empty(world, dtype=torch.int64, device=dev)
+    perm = torch.empty(n, dtype=torch.int64, device=dev)
+    bucketed = torch.empty(n, dtype=torch.int64, device=dev)
+    sc = scratch(dev, lib.hc_bucket_scratch_bytes(n, world), "bucket")
+    if keep is not None:
+        keep = keep.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.hc_bucket_by_owner(ptr(ids), ptr(keep), n, world, ptr(counts), ptr(perm),
+                                     ptr(bucketed), ptr(sc), stream_of(dev)), "hc_bucket_by_owner")
+    _called()
+    return counts, perm, bucketed
+
+
+def unpermute_rows(src, perm, flags, dst, hit_out=None):
+    """dst[perm[k]] = src[k] where flags[k]; hit_out[perm[k]] = k or -1."""
+    dev = require_cuda(perm, src, dst, hit_out)
+    n = perm.shape[0]
+    F = 0 if src is None else src.shape[1]
+    if flags is not None:
+        flags = flags.contiguous()
+    with torch.cuda.device(dev):
+        check(lib.hc_unpermute_rows(ptr(src), HC_F32 if src is None else dtype_code(src),
+                                    0 if src is None else (src.stride(0) if n > 1 else F), F,
+                                    ptr(i64c(perm)), ptr(flags), n, ptr(dst),
+                                    0 if dst is None else (dst.stride(0) if dst.shape[0] > 1 else F),
+                                    ptr(hit_out), stream_of(dev)), "hc_unpermute_rows")
+    _called()
+
+
+def owner_lookup(map_t, ids, table, rows_out=None):
+    """Owner-side lookup of the exchange: (flags, rows_out)."""
+    dev = require_cuda(map_t, ids, table)
+    ids = i64c(ids, "ids")
+    n = ids.shape[0]
+    flags = torch.empty(n, dtype=torch.uint8, device=dev)
+    F = table.shape[1]
+    if rows_out is None:
+        rows_out = torch.empty((n, F), dtype=table.dtype, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.hc_owner_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, ptr(table),
+                                  dtype_code(table), table.shape[0],
+                                  table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows_out),
+                                  rows_out.stride(0) if n > 1 else F, ptr(flags), stream_of(dev)),
+              "hc_owner_lookup")
+    _called()
+    return flags, rows_out
+
+
+# ---------------------------------------------------------------------------
+# peer copies (kept for API compatibility; the multi-GPU path uses NCCL)
+# ---------------------------------------------------------------------------
+def p2psend(tsrc, tdst, num_element, target_device):
+    """src/cpp/src/comm.cu:3-11: copies the first num_element elements of tsrc into tdst,
+    which lives on target_device.  Unlike the reference the current device is left
+    unchanged and the element size follows the dtype."""
+    tdst.view(-1)[:num_element].copy_(tsrc.reshape(-1)[:num_element], non_blocking=True)
+
+
+def p2psend_gentensor(tsrc, num_element, target_device):
+    """src/cpp/src/comm.cu:13-20: allocates the destination on target_device first."""
+    tdst = torch.empty_like(tsrc, device=torch.device("cuda", int(target_device)))
+    p2psend(tsrc, tdst, num_element, target_device)
+    return tdst

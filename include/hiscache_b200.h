@@ -1,0 +1,368 @@
+/*
+ * hiscache_b200.h -- C ABI of libhiscache_b200.so
+ *
+ * B200 (sm_100a) kernels for the data-parallel hot path of HisCache:
+ * history-aware CSR gather-reduce aggregation (forward / backward), the
+ * gradient-based admission with history writeback, used-mask propagation,
+ * cache lookup + feature-row assembly (host-resident rows included), and the
+ * bucket / un-permute steps either side of the multi-GPU table exchange.
+ *
+ * This library replaces the pybind11 module `hiscache_backend` of the
+ * reference (src/cpp/python_bindings/binding.cpp:9-19) and the torch index
+ * arithmetic of hiscache/history_cache.py / hiscache/history_table.py that sits
+ * on the same path.  Every entry point cites the reference interface it
+ * replaces.
+ *
+ * Conventions
+ *   - plain C: raw device pointers, sizes, a CUDA stream passed as `void*`
+ *     (a `cudaStream_t`; NULL = the legacy default stream);
+ *   - indices are int64 as in the reference (`using Index = int64_t`,
+ *     src/cpp/include/common.h:11); -1 means "no entry";
+ *   - every function returns an int: 0 = ok, negative = HC_ERR_* argument
+ *     error detected before any launch, positive = the `cudaError_t` of the
+ *     failing runtime call.  Nothing here exits, aborts, resets the device or
+ *     traps (the reference does: common.h:13-34);
+ *   - nothing is allocated unless the function says so; the caller owns every
+ *     buffer; launches are asynchronous on the given stream;
+ *   - row storage dtype is HC_F32 or HC_F16, accumulation is always fp32.
+ */
+#ifndef HISCACHE_B200_H
+#define HISCACHE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HC_ABI_VERSION 1
+
+/* storage dtypes */
+#define HC_F32 0
+#define HC_F16 1
+
+/* argument errors (returned negated: e.g. -HC_ERR_NULL) */
+#define HC_ERR_NULL 1      /* a required pointer is NULL                      */
+#define HC_ERR_SIZE 2      /* a size / count / stride is out of range         */
+#define HC_ERR_DTYPE 3     /* unknown dtype code                              */
+#define HC_ERR_ALIGN 4     /* pointer not aligned to its element type         */
+#define HC_ERR_UNSUPPORTED 5 /* combination of options not implemented        */
+#define HC_ERR_STRUCT 6    /* args->struct_size does not match this build     */
+
+/* score kinds */
+#define HC_SCORE_L2 0 /* sqrt(sum x^2): HistoryCache.update_history, history_cache.py:205 */
+#define HC_SCORE_L1 1 /* sum |x|     : HistoryTable.record_history, history_table.py:161 */
+
+int hc_abi_version(void);
+/* Human-readable text for a return code of any function below. The pointer is
+ * static storage (negative codes) or CUDA's own string (positive codes). */
+const char* hc_error_string(int code);
+
+/* ------------------------------------------------------------------------ */
+/* Aggregation                                                              */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * One descriptor serves forward and backward so that both see the same block.
+ * Set struct_size = sizeof(hc_aggr_args) and zero the rest before filling.
+ *
+ * A "target" is a (destination row, head) pair; num_head == 1 gives one target
+ * per row.  Source row s, head h starts at input + (s*num_head + h)*feat when
+ * in_stride == num_head*feat (the only layout the reference has).
+ */
+typedef struct hc_aggr_args {
+  uint32_t struct_size;
+  /* CSR block over destination rows */
+  const int64_t* ptr;      /* [num_node + 1]                                 */
+  const int64_t* idx;      /* [ptr[num_node]] local source ids               */
+  int64_t num_node;        /* destination rows to process                    */
+  /* source rows */
+  const void* input;       /* [n_src, num_head, feat]                        */
+  int32_t in_dtype;        /* HC_F32 | HC_F16                                */
+  int32_t feat;            /* F, columns per (row, head)                     */
+  int32_t num_head;        /* >= 1                                           */
+  int64_t n_src;           /* rows of input (size of grad_input)             */
+  int64_t in_stride;       /* elements between source rows; 0 = num_head*feat*/
+  /* optional per-source select made inside the gather: when src_map is not
+   * NULL and src_map[s] != -1, source s is read from row src_map[s] of
+   * src_alt instead of from input, and receives no gradient in backward.    */
+  const int64_t* src_map;  /* [n_src] or NULL                                */
+  const void* src_alt;     /* [*, num_head*feat] rows, stride alt_stride     */
+  int32_t alt_dtype;
+  int64_t alt_stride;      /* elements; 0 = num_head*feat                    */
+  /* NULL => mean over neighbours; else weighted sum with edge_value[e] or
+   * edge_value[e*num_head + h] (no division; written for empty rows too)     */
+  const float* edge_value;
+  /* optional per-destination history override: hmap[r] != -1 => the output
+   * row is a copy of a history row and nothing flows to its neighbours.      */
+  const int64_t* hmap;     /* [num_node] or NULL                             */
+  const void* hbuf;        /* history rows, stride hsize elements            */
+  int32_t h_dtype;
+  int32_t h_indexed;       /* 0: read row r (reference layout, row-aligned
+                              buffer); 1: read row hmap[r] of the table       */
+  int64_t hsize;           /* == feat, or == num_head*feat (per-head rows)   */
+} hc_aggr_args;
+
+/*
+ * out[t, :] (fp32, [num_node, num_head, feat]) for every target t.  Every
+ * element of out is written (empty rows get zeros), so out need not be
+ * cleared.  Replaces aggr_forward_history / aggr_forward_history_edge_value
+ * (src/cpp/src/history_aggr.cu:598-617; kernels :7-125; launcher :399-473).
+ * With hmap == NULL it is the plain mean aggregation the reference takes from
+ * cxgnncomp.sage_mean_forward (hiscache/history_model.py:90).
+ */
+int hc_aggr_fwd(const hc_aggr_args* a, float* out, void* stream);
+
+/*
+ * Transposed scatter of grad_out (fp32 [num_node, num_head, feat]).
+ *   grad_input  fp32 [n_src, num_head, feat] or NULL: miss rows add
+ *               grad_out[t]/deg (or * edge_value) to every neighbour's row.
+ *               zero_grad_input != 0 clears it first (cudaMemsetAsync).
+ *   grad_history fp32, stride hsize, rows [0, num_node), or NULL: hit rows
+ *               receive grad_out[t]; miss rows are written as zeros
+ *               (row-aligned, as zeros_like(history_buffer) in the reference).
+ *   edge_grad   fp32 [E(, num_head)] or NULL: <grad_out[t], source row>.
+ *   row_score   fp32 [num_node] or NULL (num_head must be 1): the admission
+ *               score of grad_out[r, :] (score_kind), computed in the same
+ *               pass in the library's fixed reduction order (see hc_score_rows).
+ * Replaces AggrHistoryFunction::backward / historyBackwardImpl
+ * (history_aggr.cu:493-596; kernels :127-397) and, with row_score, the
+ * `grad.norm(dim=1)` of hiscache/history_cache.py:205.
+ */
+int hc_aggr_bwd(const hc_aggr_args* a, const float* grad_out, float* grad_input,
+                int32_t zero_grad_input, float* grad_history, float* edge_grad,
+                float* row_score, int32_t score_kind, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Scores and thresholds                                                    */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * score[r] = L2 or L1 norm of x[r, 0:feat] (fp32, row stride `stride`
+ * elements).  Fixed order, restated by the oracle bit for bit: element e
+ * goes to lane (e/4) mod 32; each lane adds its terms in increasing e with
+ * separately rounded multiply and add; the 32 partial sums are combined by
+ * an xor butterfly (16, 8, 4, 2, 1); L2 takes a correctly rounded sqrt.
+ * Replaces grad.norm(dim=1) (history_cache.py:205) and sum(|grad|, 1)
+ * (history_table.py:161,219).
+ */
+int hc_score_rows(const float* x, int64_t n, int32_t feat, int64_t stride,
+                  int32_t kind, float* score, void* stream);
+
+/*
+ * thres[0] = torch.quantile(score, q) with linear interpolation
+ * (history_cache.py:211, history_table.py:173,230): rank = fp32(q)*(n-1)
+ * computed in fp32, the two neighbouring order statistics found by an exact
+ * radix select, combined as fma(w, hi-lo, lo) for w < 0.5 and
+ * fma(-(hi-lo), 1-w, hi) otherwise (torch's lerp, whose multiply-add is fused
+ * in its CPU and CUDA builds).  NaN in score gives NaN.
+ * n == 0 is HC_ERR_SIZE.  scratch: device, >= hc_select_scratch_bytes(n).
+ */
+int64_t hc_select_scratch_bytes(int64_t n);
+int hc_select_threshold(const float* score, int64_t n, float q, float* thres,
+                        void* scratch, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Admission and eviction                                                   */
+/* ------------------------------------------------------------------------ */
+
+/* Device scratch needed by the two admission entry points for n candidates. */
+int64_t hc_admit_scratch_bytes(int64_t n);
+
+/*
+ * Ring-buffer admission of the per-layer table path; deterministic
+ * restatement of record_history (src/cpp/src/grad_check.cu:6-68).  Row `sub`
+ * of buffer_new is admitted iff sub_to_history[sub] == -1 and not
+ * (thres[0] != 0 and score[sub] > thres[0]) and used_mask[sub] (NULL = all
+ * used).  Admitted rows take consecutive ring slots in ascending `sub`
+ * starting at header[0] (the reference takes them in warp-scheduling order,
+ * grad_check.cu:25); a slot's previous owner g is unmapped only while
+ * full_to_history[g] still equals that slot; the row is copied (converted to
+ * table_dtype); full_to_history[sub_to_full[sub]], history_to_full[slot] and
+ * checkin_iter[slot] are set; header[0] advances modulo capacity.  If more
+ * rows are admitted than the table holds, the result equals applying them one
+ * by one.  n_admitted (device int64[1], may be NULL) receives the count.
+ */
+int hc_record_history(const float* buffer_new, int64_t new_stride, int64_t n,
+                      void* buffer_all, int32_t table_dtype, int64_t capacity,
+                      int32_t history_size, const uint8_t* used_mask,
+                      const int64_t* sub_to_full, const int64_t* sub_to_history,
+                      int64_t* history_to_full, int64_t* full_to_history,
+                      int64_t* header, const float* score, const float* thres,
+                      int64_t* checkin_iter, int64_t glb_iter,
+                      int64_t* n_admitted, void* scratch, void* stream);
+
+/*
+ * Admission of the unified-buffer cache path; restatement of
+ * HistoryCache.update_history (hiscache/history_cache.py:211-254) with the
+ * write position kept on the device.  Row r of produced ([n, hidden] fp32) is
+ * admitted iff score[r] < thres[0] and sub2embed[r] == -1; admitted rows are
+ * appended in ascending r at embedding slots header[0].. ; raw-feature slots
+ * overlapped by the new rows lose their mapping through feat2full; previous
+ * owners of the overwritten embedding slots are unmapped only if their map
+ * still points into the overwritten range; then full2embed / embed2full are
+ * set and header[0] advances.  Unlike the reference, rows that would run past
+ * embed_capacity are not admitted.  reset_header != 0 sets header[0] = 0
+ * first (the ring restart of history_cache.py:190-192).
+ * full2embed has 2*total_num_node + 1 entries (history_cache.py:42-46).
+ */
+int hc_cache_admit(const float* produced, int64_t prod_stride, int64_t n,
+                   void* buffer, int32_t buf_dtype, int32_t hidden,
+                   int32_t in_feat, int64_t embed_capacity,
+                   const int64_t* sub_to_full, const int64_t* sub2embed,
+                   const float* score, const float* thres, int64_t* full2embed,
+                   int64_t total_num_node, int64_t* embed2full,
+                   const int64_t* feat2full, int64_t feat2full_len,
+                   int64_t* header, int32_t reset_header, int64_t* n_admitted,
+                   void* scratch, void* stream);
+
+/*
+ * Staleness eviction: every slot with -1 < checkin_iter[s] <= glb_iter - limit
+ * is cleared in checkin_iter, history_to_full and full_to_history
+ * (hiscache/history_table.py:189-200, :244-251).
+ */
+int hc_evict_stale(int64_t* checkin_iter, int64_t* history_to_full,
+                   int64_t* full_to_history, int64_t capacity, int64_t glb_iter,
+                   int64_t limit, void* stream);
+
+/*
+ * Score eviction: for r < n with score[r] >= thres[0] and
+ * sub_to_history[r] != -1 the slot is cleared in all three arrays
+ * (hiscache/history_table.py:234-241).
+ */
+int hc_evict_by_score(const int64_t* sub_to_history, const float* score,
+                      const float* thres, int64_t n, int64_t* checkin_iter,
+                      int64_t* history_to_full, int64_t* full_to_history,
+                      void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Receptive-field bookkeeping                                              */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * masks: num_layer+1 consecutive byte masks of num_node entries each
+ * (masks[k] at masks + k*num_node), all written here.  masks[num_layer] is
+ * the seed level, masks[0] gates raw-feature loading; a row with
+ * history_map[r] != -1 stops the propagation at the second step only.
+ * Replaces count_history_reconstruct (grad_check.cu:70-130).  ptr has
+ * ptr_rows+1 entries; history_map may be NULL or have >= the number of rows
+ * that can be live at the second step.
+ */
+int hc_used_masks(const int64_t* ptr, const int64_t* idx, int64_t ptr_rows,
+                  const int64_t* history_map, int64_t history_map_len,
+                  int64_t num_node, int64_t num_seed, int32_t num_layer,
+                  uint8_t* masks, void* stream);
+
+/*
+ * Level-synchronous form of get_graph_structure_score (grad_check.cu:132-163):
+ * seeds get 1; at each of num_layer steps an unset neighbour takes
+ * score(parent)*deg(parent) of its lowest-numbered parent that was set before
+ * the step.  output: int64 [num_node], written here.  scratch: int64
+ * [num_node].
+ */
+int hc_structure_score(const int64_t* ptr, const int64_t* idx, int64_t ptr_rows,
+                       int64_t num_node, int64_t num_seed, int32_t num_layer,
+                       int64_t* output, int64_t* scratch, void* stream);
+
+/*
+ * output[v] (int32 [mmax+1], cleared here) = number of i with arr[i] == v,
+ * except that value 0 is never counted (count_num, grad_check.cu:165-182).
+ * Values outside [0, mmax] are ignored.
+ */
+int hc_count_num(const int64_t* arr, int64_t n, int64_t mmax, int32_t* output,
+                 void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Lookup and feature-row assembly                                          */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * out[i] = map[ids[i] + offset] for i < n (negative positions wrap from the
+ * end as torch indexing does).  The two lookups of lookup_and_load
+ * (history_cache.py:310,315) are this with offset 0 / total_num_node.
+ * force_miss_below: entries i < force_miss_below are set to -1 (the
+ * seeds-are-never-history rule of history_table.py:106).
+ */
+int hc_map_lookup(const int64_t* map, int64_t map_len, const int64_t* ids,
+                  int64_t n, int64_t offset, int64_t force_miss_below,
+                  int64_t* out, void* stream);
+
+/*
+ * out[i, :] = table[rows[i], :] for i < n; rows[i] == -1 reads the last row
+ * (torch negative indexing, which history_cache.py:312-313 relies on), unless
+ * zero_missing != 0, in which case the output row is zeros.  Output dtype may
+ * differ from the table's.
+ */
+int hc_gather_rows(const void* table, int32_t table_dtype, int64_t table_rows,
+                   int64_t table_stride, int32_t feat, const int64_t* rows,
+                   int64_t n, int32_t zero_missing, void* out, int32_t out_dtype,
+                   int64_t out_stride, void* stream);
+
+/*
+ * Assembles batch.x in one pass (history_cache.py:327-350 and :276-288):
+ *   load_mask[i] = (used == NULL || used[i]) && sub2feat[i] == -1
+ *   x[i] = load_mask[i] ? host_table[sub_to_full[i]]
+ *        : sub2feat[i] != -1 ? feat_cache[sub2feat[i]] : 0
+ * host_table may be device memory or mapped pinned host memory (history_uvm
+ * mode): rows are fetched by the kernel itself over the host link and staged
+ * through shared memory.  load_mask_out (bytes, may be NULL) receives the
+ * mask; stats (int64[2], may be NULL) accumulates {rows from host_table, rows
+ * from the feature cache}.
+ */
+int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                 int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
+                 int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                 const int64_t* sub_to_full, const int64_t* sub2feat,
+                 const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                 int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                 void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* Multi-GPU table exchange helpers                                         */
+/* ------------------------------------------------------------------------ */
+
+/* owner(id) = hc_mix64(id) mod world; the partition function of the sharded
+ * history table (the reference has none: its only sharding attempt splits the
+ * feature axis, history_cache.py:72-78). Host-callable. */
+uint64_t hc_mix64(uint64_t x);
+
+/*
+ * Stable bucket sort of ids by owner: counts[w] (int64 [world]) = ids owned by
+ * w; perm[k] (int64 [n]) = position in ids of the k-th element in bucket
+ * order (buckets ascending, original order inside a bucket);
+ * bucketed[k] = ids[perm[k]].  keep (bytes, may be NULL): entries with
+ * keep[i] == 0 are left out (counts exclude them; the tail of perm/bucketed is
+ * unspecified).  Replaces the per-(src,dst) index_select of prepare_transfer
+ * (hiscache/comm.py:132-143).  scratch >= hc_bucket_scratch_bytes(n, world).
+ */
+int64_t hc_bucket_scratch_bytes(int64_t n, int32_t world);
+int hc_bucket_by_owner(const int64_t* ids, const uint8_t* keep, int64_t n,
+                       int32_t world, int64_t* counts, int64_t* perm,
+                       int64_t* bucketed, void* scratch, void* stream);
+
+/*
+ * dst[perm[k], :] = src[k, :] for k < n where flags == NULL or flags[k] != 0
+ * (post_transfer of hiscache/comm.py:146-151, by rows instead of by feature
+ * slices).  hit_out (int64 [*], may be NULL): hit_out[perm[k]] = flags[k] ?
+ * k : -1, the row-aligned history map the aggregation consumes.
+ */
+int hc_unpermute_rows(const void* src, int32_t dtype, int64_t src_stride,
+                      int32_t feat, const int64_t* perm, const uint8_t* flags,
+                      int64_t n, void* dst, int64_t dst_stride, int64_t* hit_out,
+                      void* stream);
+
+/*
+ * Owner-side lookup for the exchange: for k < n, slot = map[ids[k]] (ids are
+ * global node ids this rank owns); flags[k] = slot != -1; rows_out[k, :] =
+ * table[slot, :] when hit (left untouched otherwise).
+ */
+int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids,
+                    int64_t n, const void* table, int32_t dtype,
+                    int64_t table_rows, int64_t table_stride, int32_t feat,
+                    void* rows_out, int64_t out_stride, uint8_t* flags,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HISCACHE_B200_H */

@@ -1,0 +1,286 @@
+"""numpy front end of the CPU oracle.  TEST INFRASTRUCTURE.
+
+Only tests/, the smoke check and the bench's CPU-baseline leg may import this
+module; the `hiscache` package and libhiscache_b200 never do.  The loops live
+in hc_oracle.c (built by oracle/Makefile into oracle/_build/libhc_oracle.so);
+index arithmetic that the reference writes as torch indexing is restated here
+with numpy.  File:line citations are relative to the reference project.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "libhc_oracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compiles hc_oracle.c (gcc + OpenMP) if the shared object is missing or stale."""
+    src = os.path.join(_HERE, "hc_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-s", "-C", _HERE, "oracle"], check=True)
+    return _SO
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_SO):
+            build()
+        _lib = C.CDLL(_SO)
+        _lib.orc_quantile.restype = C.c_float
+        _lib.orc_record_history.restype = C.c_int64
+        _lib.orc_cache_admit.restype = C.c_int64
+        _lib.orc_mix64.restype = C.c_uint64
+        _lib.orc_mix64.argtypes = [C.c_uint64]
+    return _lib
+
+
+def _p(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i64(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _u8(a):
+    return None if a is None else np.ascontiguousarray(a).astype(np.uint8)
+
+
+# ---------------------------------------------------------------------------
+# aggregation
+# ---------------------------------------------------------------------------
+def aggr_fwd(ptr, idx, inp, num_node, *, src_map=None, src_alt=None, edge_value=None,
+             hmap=None, hbuf=None, h_indexed=False, acc64=True, use_omp=False):
+    """history_aggr.cu:7-125.  inp: [n_src, F] or [n_src, H, F]; fp16 inputs are widened
+    exactly.  Returns fp32 [num_node, (H,) F]."""
+    ptr, idx = _i64(ptr), _i64(idx)
+    inp = _f32(inp)
+    multi = inp.ndim == 3
+    H = inp.shape[1] if multi else 1
+    F = inp.shape[-1]
+    src_map, src_alt, edge_value = _i64(src_map), _f32(src_alt), _f32(edge_value)
+    hmap, hbuf = _i64(hmap), _f32(hbuf)
+    hsize = hbuf.shape[-1] if hbuf is not None and hbuf.ndim > 1 else F
+    out = np.zeros((num_node, H, F) if multi else (num_node, F), dtype=np.float32)
+    lib().orc_aggr_fwd(_p(ptr), _p(idx), C.c_int64(num_node), _p(inp), C.c_int64(H * F),
+                       C.c_int(F), C.c_int(H), _p(src_map), _p(src_alt), C.c_int64(H * F),
+                       _p(edge_value), _p(hmap), _p(hbuf), C.c_int64(hsize),
+                       C.c_int(int(h_indexed)), C.c_int(int(acc64)), C.c_int(int(use_omp)),
+                       _p(out))
+    return out
+
+
+def aggr_bwd(ptr, idx, inp, num_node, grad_out, *, src_map=None, src_alt=None, edge_value=None,
+             hmap=None, hsize=None, want_edge_grad=False, want_grad_history=True):
+    """history_aggr.cu:127-397, :493-580.  Returns (grad_input, grad_history, edge_grad)."""
+    ptr, idx = _i64(ptr), _i64(idx)
+    inp = _f32(inp)
+    multi = inp.ndim == 3
+    H = inp.shape[1] if multi else 1
+    F = inp.shape[-1]
+    n_src = inp.shape[0]
+    src_map, src_alt, edge_value = _i64(src_map), _f32(src_alt), _f32(edge_value)
+    hmap = _i64(hmap)
+    grad_out = _f32(grad_out)
+    if hsize is None:
+        hsize = F
+    acc = np.zeros(n_src * H * F, dtype=np.float64)
+    gi = np.zeros_like(inp)
+    gh = np.zeros((num_node, hsize), dtype=np.float32) if (hmap is not None and want_grad_history) else None
+    eg = np.zeros_like(edge_value) if (want_edge_grad and edge_value is not None) else None
+    lib().orc_aggr_bwd(_p(ptr), _p(idx), C.c_int64(num_node), _p(inp), C.c_int64(H * F),
+                       C.c_int(F), C.c_int(H), C.c_int64(n_src), _p(src_map), _p(src_alt),
+                       C.c_int64(H * F), _p(edge_value), _p(hmap), C.c_int64(hsize),
+                       _p(grad_out), _p(acc), _p(gi), _p(gh), _p(eg))
+    return gi, gh, eg
+
+
+def aggr_bwd_omp(ptr, idx, num_node, n_src, grad_out, hmap=None):
+    """fp32 OpenMP scatter, for CPU-baseline timing only."""
+    ptr, idx, hmap, grad_out = _i64(ptr), _i64(idx), _i64(hmap), _f32(grad_out)
+    F = grad_out.shape[-1]
+    gi = np.empty((n_src, F), dtype=np.float32)
+    lib().orc_aggr_bwd_omp(_p(ptr), _p(idx), C.c_int64(num_node), C.c_int(F), C.c_int64(n_src),
+                           _p(hmap), _p(grad_out), _p(gi))
+    return gi
+
+
+# ---------------------------------------------------------------------------
+# scores / threshold
+# ---------------------------------------------------------------------------
+def score_rows(x, kind="l2"):
+    """history_cache.py:205 (l2) / history_table.py:161 (l1) in the library's fixed order."""
+    x = _f32(x)
+    n, F = x.shape
+    out = np.empty(n, dtype=np.float32)
+    lib().orc_score_rows(_p(x), C.c_int64(n), C.c_int(F), C.c_int64(F),
+                         C.c_int(0 if kind == "l2" else 1), _p(out))
+    return out
+
+
+def quantile(score, q):
+    """torch.quantile(score, q), linear interpolation (history_cache.py:211)."""
+    score = _f32(score)
+    return np.float32(lib().orc_quantile(_p(score), C.c_int64(score.shape[0]), C.c_float(q)))
+
+
+# ---------------------------------------------------------------------------
+# admission / eviction (arrays are modified in place, as the reference does)
+# ---------------------------------------------------------------------------
+def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_history,
+                   history_to_full, full_to_history, header, score, thres, checkin_iter, glb_iter):
+    """grad_check.cu:6-68 in ascending row order; same argument order as the reference op."""
+    buffer_new = _f32(buffer_new)
+    assert buffer_all.dtype == np.float32 and buffer_all.flags.c_contiguous
+    for a in (history_to_full, full_to_history, header, checkin_iter):
+        assert a.dtype == np.int64 and a.flags.c_contiguous
+    n, hs = buffer_new.shape
+    return int(lib().orc_record_history(
+        _p(buffer_new), C.c_int64(hs), C.c_int64(n), _p(buffer_all),
+        C.c_int64(buffer_all.shape[0]), C.c_int(hs), _p(_u8(used_mask)), _p(_i64(sub_to_full)),
+        _p(_i64(sub_to_history)), _p(history_to_full), _p(full_to_history), _p(header),
+        _p(_f32(score)), C.c_float(float(thres)), _p(checkin_iter), C.c_int64(glb_iter)))
+
+
+def cache_admit(produced, buffer, hidden, in_feat, sub_to_full, sub2embed, score, thres,
+                full2embed, total_num_node, embed2full, feat2full, header, reset_header=False,
+                embed_capacity=None):
+    """history_cache.py:213-254.  buffer: flat fp32; header: int64[1].  Returns
+    (n_admitted, record_mask)."""
+    produced = _f32(produced)
+    n = produced.shape[0]
+    assert buffer.dtype == np.float32 and buffer.flags.c_contiguous
+    for a in (full2embed, embed2full, header):
+        assert a.dtype == np.int64 and a.flags.c_contiguous
+    if embed_capacity is None:
+        embed_capacity = buffer.size // hidden
+    feat2full = _i64(feat2full) if feat2full is not None else np.zeros(0, dtype=np.int64)
+    mask = np.zeros(n, dtype=np.uint8)
+    num = lib().orc_cache_admit(
+        _p(produced), C.c_int64(produced.shape[1] if n else hidden), C.c_int64(n), _p(buffer),
+        C.c_int(hidden), C.c_int(in_feat), C.c_int64(embed_capacity), _p(_i64(sub_to_full)),
+        _p(_i64(sub2embed)), _p(_f32(score)), C.c_float(float(thres)), _p(full2embed),
+        C.c_int64(total_num_node), _p(embed2full), _p(feat2full), C.c_int64(feat2full.shape[0]),
+        _p(header), C.c_int(int(reset_header)), _p(mask))
+    return int(num), mask.astype(bool)
+
+
+def evict_stale(checkin, h2f, f2h, glb_iter, limit):
+    """history_table.py:189-200."""
+    lib().orc_evict_stale(_p(checkin), _p(h2f), _p(f2h), C.c_int64(checkin.shape[0]),
+                          C.c_int64(glb_iter), C.c_int64(limit))
+
+
+def evict_by_score(sub_to_history, score, thres, checkin, h2f, f2h):
+    """history_table.py:234-241."""
+    s2h = _i64(sub_to_history)
+    lib().orc_evict_by_score(_p(s2h), _p(_f32(score)), C.c_float(float(thres)),
+                             C.c_int64(s2h.shape[0]), _p(checkin), _p(h2f), _p(f2h))
+
+
+# ---------------------------------------------------------------------------
+# receptive-field bookkeeping
+# ---------------------------------------------------------------------------
+def used_masks(ptr, idx, history_map, num_node, num_seed, num_layer):
+    """grad_check.cu:70-130; returns a list of num_layer+1 bool arrays [num_node]."""
+    ptr, idx = _i64(ptr), _i64(idx)
+    hm = _i64(history_map) if history_map is not None and len(history_map) else None
+    masks = np.zeros((num_layer + 1, num_node), dtype=np.uint8)
+    lib().orc_used_masks(_p(ptr), _p(idx), C.c_int64(ptr.shape[0] - 1), _p(hm),
+                         C.c_int64(0 if hm is None else hm.shape[0]), C.c_int64(num_node),
+                         C.c_int64(num_seed), C.c_int(num_layer), _p(masks))
+    return [masks[k].astype(bool) for k in range(num_layer + 1)]
+
+
+def structure_score(ptr, idx, num_node, num_seed, num_layer):
+    """grad_check.cu:132-163, level-synchronous reading."""
+    ptr, idx = _i64(ptr), _i64(idx)
+    out = np.zeros(num_node, dtype=np.int64)
+    lib().orc_structure_score(_p(ptr), _p(idx), C.c_int64(ptr.shape[0] - 1), C.c_int64(num_node),
+                              C.c_int64(num_seed), C.c_int(num_layer), _p(out))
+    return out
+
+
+def count_num(arr, mmax):
+    """grad_check.cu:165-182."""
+    arr = _i64(arr)
+    out = np.zeros(mmax + 1, dtype=np.int32)
+    lib().orc_count_num(_p(arr), C.c_int64(arr.shape[0]), C.c_int64(mmax), _p(out))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# lookup / row assembly (numpy restatement of torch indexing)
+# ---------------------------------------------------------------------------
+def cache_lookup(full2embed, sub_to_full, n1, total_num_node):
+    """history_cache.py:307-315: (sub2embed [n1], sub2feat [n_all])."""
+    sub_to_full = _i64(sub_to_full)
+    return full2embed[sub_to_full[:n1]].copy(), full2embed[sub_to_full + total_num_node].copy()
+
+
+def gather_rows(table, rows):
+    """table[rows] with torch negative indexing (history_cache.py:312-313)."""
+    return table[_i64(rows)].copy()
+
+
+def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used):
+    """history_cache.py:327-350 (used given) and :276-288 (used None).  Returns (x, load_mask).
+    uvm.masked_get(ids, mask) is read as: rows of the host table where mask, zeros elsewhere."""
+    sub_to_full, sub2feat = _i64(sub_to_full), _i64(sub2feat)
+    hit = sub2feat != -1
+    load = ~hit if used is None else (np.asarray(used, dtype=bool) & ~hit)
+    x = np.zeros((sub_to_full.shape[0], host_table.shape[1]), dtype=np.float32)
+    x[load] = host_table[sub_to_full[load]].astype(np.float32)
+    if feat_cache is not None and hit.any():
+        cached = feat_cache[sub2feat].astype(np.float32)
+        cached[~hit] = 0
+        x += cached
+    return x, load
+
+
+def table_lookup(full_to_history, sub_to_full, num_node, num_seed):
+    """history_table.py:102-121: (sub_to_history with seeds forced to miss, compact remap)."""
+    s2h = full_to_history[_i64(sub_to_full)[:num_node]].copy()
+    s2h[:num_seed] = -1
+    mask = s2h != -1
+    remap = np.full(num_node, -1, dtype=np.int64)
+    remap[mask] = np.arange(int(mask.sum()), dtype=np.int64)
+    return s2h, remap
+
+
+# ---------------------------------------------------------------------------
+# sharded table
+# ---------------------------------------------------------------------------
+def mix64(x):
+    x = np.asarray(x, dtype=np.uint64)
+    with np.errstate(over="ignore"):
+        x = x + np.uint64(0x9E3779B97F4A7C15)
+        x = (x ^ (x >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+        x = (x ^ (x >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+        return x ^ (x >> np.uint64(31))
+
+
+def owner(ids, world):
+    return (mix64(np.asarray(ids, dtype=np.int64).astype(np.uint64)) % np.uint64(world)).astype(np.int64)
+
+
+def bucket_by_owner(ids, world, keep=None):
+    """Stable bucket sort by owner: (counts [world], perm, bucketed)."""
+    ids = _i64(ids)
+    sel = np.arange(ids.shape[0]) if keep is None else np.nonzero(np.asarray(keep, dtype=bool))[0]
+    own = owner(ids[sel], world)
+    order = np.argsort(own, kind="stable")
+    perm = sel[order].astype(np.int64)
+    counts = np.bincount(own, minlength=world).astype(np.int64)
+    return counts, perm, ids[perm]

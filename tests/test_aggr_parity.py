@@ -1,0 +1,168 @@
+"""Aggregation forward/backward: CUDA library vs the CPU oracle on the same seeded inputs.
+Tolerances are the ones the task states: rtol 1e-5 for fp32 storage, 2e-3 for fp16."""
+import numpy as np
+import pytest
+import torch
+
+from _gen import config1, csr_block
+
+pytestmark = pytest.mark.gpu
+
+RTOL = {torch.float32: 1e-5, torch.float16: 2e-3}
+
+
+def cu(a, dtype=None):
+    if a is None:
+        return None
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def close(got, want, rtol, scale=None):
+    got = got.detach().float().cpu().numpy()
+    want = np.asarray(want, dtype=np.float32)
+    assert got.shape == want.shape
+    # atol scaled to the magnitude of the data: sums of O(1) terms
+    atol = rtol * (scale if scale is not None else max(1.0, float(np.abs(want).max(initial=0.0))))
+    np.testing.assert_allclose(got, want, rtol=rtol, atol=atol)
+
+
+@pytest.mark.parametrize("feat", [1, 4, 31, 32, 33, 64, 100, 128, 256, 768, 1024])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("history", ["none", "aligned", "indexed"])
+def test_fwd_bwd_mean(backend, oracle, feat, dtype, history):
+    rng = np.random.default_rng(feat * 7 + (dtype == torch.float16) + 3 * len(history))
+    num_dst, n_src = 301, 977
+    ptr, idx = csr_block(rng, num_dst, n_src, "mixed")
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    xs = cu(x, dtype)
+    x_exact = xs.float().cpu().numpy()  # what the kernel really reads
+    hmap = hbuf = None
+    indexed = history == "indexed"
+    if history != "none":
+        hmap = np.where(rng.random(num_dst) < 0.3, 0, -1).astype(np.int64)
+        cap = 57 if indexed else num_dst
+        hbuf = rng.standard_normal((cap, feat), dtype=np.float32)
+        hit = hmap != -1
+        hmap[hit] = rng.integers(0, cap, size=int(hit.sum())) if indexed else np.nonzero(hit)[0]
+    hb = cu(hbuf, dtype)
+    hb_exact = None if hb is None else hb.float().cpu().numpy()
+    xs.requires_grad_(True)
+    out = backend.aggr_forward(xs, cu(ptr), cu(idx), num_dst, history_map=cu(hmap),
+                               history_buffer=hb, indexed=indexed)
+    want = oracle.aggr_fwd(ptr, idx, x_exact, num_dst, hmap=hmap, hbuf=hb_exact, h_indexed=indexed)
+    assert out.dtype == torch.float32 and out.requires_grad
+    close(out, want, RTOL[dtype], scale=8.0)
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    score = torch.empty(num_dst, dtype=torch.float32, device="cuda")
+    # second run with the fused score
+    xs2 = xs.detach().clone().requires_grad_(True)
+    out2 = backend.aggr_forward(xs2, cu(ptr), cu(idx), num_dst, history_map=cu(hmap),
+                                history_buffer=hb, indexed=indexed, score_out=score)
+    out2.backward(cu(g))
+    gi, _, _ = oracle.aggr_bwd(ptr, idx, x_exact, num_dst, g, hmap=hmap, want_grad_history=False)
+    close(xs2.grad, gi, RTOL[dtype], scale=8.0)
+    # fused score == standalone score == oracle, bit for bit
+    want_s = oracle.score_rows(g)
+    assert score.cpu().numpy().tobytes() == want_s.tobytes()
+    assert backend.score_rows(cu(g)).cpu().numpy().tobytes() == want_s.tobytes()
+
+
+@pytest.mark.parametrize("feat", [16, 100, 128])
+def test_grad_history_row_aligned(backend, oracle, feat):
+    rng = np.random.default_rng(feat)
+    num_dst, n_src = 200, 500
+    ptr, idx = csr_block(rng, num_dst, n_src, 7)
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.4, np.arange(num_dst), -1).astype(np.int64)
+    hbuf = rng.standard_normal((num_dst + 5, feat), dtype=np.float32)
+    xs, hb = cu(x).requires_grad_(True), cu(hbuf).requires_grad_(True)
+    out = backend.aggr_forward_history(xs, cu(ptr), cu(idx), cu(hmap), hb, feat, num_dst)
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    out.backward(cu(g))
+    gi, gh, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, hmap=hmap, hsize=feat)
+    close(xs.grad, gi, 1e-5, scale=8.0)
+    want_h = np.zeros_like(hbuf)
+    want_h[:num_dst] = gh
+    assert np.array_equal(hb.grad.cpu().numpy(), want_h)  # hit rows are exact copies
+
+
+@pytest.mark.parametrize("feat,heads", [(32, 1), (100, 1), (128, 1), (16, 4), (33, 3)])
+@pytest.mark.parametrize("hist_per_head", [False, True])
+def test_edge_value_variants(backend, oracle, feat, heads, hist_per_head):
+    rng = np.random.default_rng(feat * heads + hist_per_head)
+    num_dst, n_src = 150, 400
+    ptr, idx = csr_block(rng, num_dst, n_src, "mixed")
+    E = int(ptr[-1])
+    multi = heads > 1
+    x = rng.standard_normal((n_src, heads, feat) if multi else (n_src, feat), dtype=np.float32)
+    ev = rng.standard_normal((E, heads) if multi else (E,), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.25, np.arange(num_dst), -1).astype(np.int64)
+    hs = feat * heads if (multi and hist_per_head) else feat
+    hbuf = rng.standard_normal((num_dst, hs), dtype=np.float32)
+    xs, evs = cu(x).requires_grad_(True), cu(ev).requires_grad_(True)
+    hb = cu(hbuf).requires_grad_(True)
+    out = backend.aggr_forward_history_edge_value(xs, cu(ptr), cu(idx), evs, cu(hmap), hb, hs,
+                                                  num_dst)
+    want = oracle.aggr_fwd(ptr, idx, x, num_dst, edge_value=ev, hmap=hmap, hbuf=hbuf)
+    close(out, want, 1e-5, scale=16.0)
+    g = rng.standard_normal(want.shape, dtype=np.float32)
+    out.backward(cu(g))
+    gi, gh, eg = oracle.aggr_bwd(ptr, idx, x, num_dst, g, edge_value=ev, hmap=hmap, hsize=hs,
+                                 want_edge_grad=True)
+    close(xs.grad, gi, 1e-5, scale=16.0)
+    close(evs.grad, eg, 1e-5, scale=4.0 * np.sqrt(feat))
+    close(hb.grad, gh, 1e-5, scale=8.0)
+
+
+def test_config1_single_layer(backend, oracle):
+    """The CPU-runnable single-layer case at its full size: per-source select inside the
+    gather, mean forward, backward w.r.t. the uncached features."""
+    c = config1(seed=1234)
+    feats = cu(c["feats"]).requires_grad_(True)
+    out = backend.aggr_forward(feats, cu(c["ptr"]), cu(c["idx"]), c["num_dst"],
+                               src_map=cu(c["src_map"]), src_alt=cu(c["hist"]))
+    want = oracle.aggr_fwd(c["ptr"], c["idx"], c["feats"], c["num_dst"], src_map=c["src_map"],
+                           src_alt=c["hist"])
+    close(out, want, 1e-5, scale=4.0)
+    out.backward(cu(c["grad_out"]))
+    gi, _, _ = oracle.aggr_bwd(c["ptr"], c["idx"], c["feats"], c["num_dst"], c["grad_out"],
+                               src_map=c["src_map"], src_alt=c["hist"])
+    close(feats.grad, gi, 1e-5, scale=4.0)
+    # cached sources receive exactly nothing
+    assert float(feats.grad[cu(c["src_map"]) != -1].abs().max()) == 0.0
+
+
+def test_empty_and_ragged(backend, oracle):
+    dev = "cuda"
+    x = torch.randn(10, 128, device=dev)
+    # no destination rows
+    out = backend.aggr_forward(x, torch.zeros(1, dtype=torch.int64, device=dev),
+                               torch.zeros(0, dtype=torch.int64, device=dev), 0)
+    assert out.shape == (0, 128)
+    # all rows empty
+    ptr = torch.zeros(6, dtype=torch.int64, device=dev)
+    out = backend.aggr_forward(x, ptr, torch.zeros(0, dtype=torch.int64, device=dev), 5)
+    assert float(out.abs().max()) == 0.0
+    # one row with a very long neighbour list (many 32-chunks), duplicates included
+    rng = np.random.default_rng(5)
+    idx = rng.integers(0, 10, size=1000, dtype=np.int64)
+    ptr = np.array([0, 1000], dtype=np.int64)
+    out = backend.aggr_forward(x, cu(ptr), cu(idx), 1)
+    want = oracle.aggr_fwd(ptr, idx, x.cpu().numpy(), 1)
+    close(out, want, 1e-5, scale=4.0)
+
+
+def test_argument_errors_raise(backend):
+    dev = "cuda"
+    x = torch.randn(4, 8, device=dev)
+    ptr = torch.tensor([0, 1], dtype=torch.int64, device=dev)
+    idx = torch.tensor([0], dtype=torch.int64, device=dev)
+    with pytest.raises(RuntimeError):
+        backend.aggr_forward(x.cpu(), ptr, idx, 1)            # CPU tensor: no fallback
+    with pytest.raises(TypeError):
+        backend.aggr_forward(x, ptr.int(), idx, 1)            # int32 indices
+    with pytest.raises(TypeError):
+        backend.aggr_forward(x.double(), ptr, idx, 1)         # unsupported dtype
+    with pytest.raises(RuntimeError):
+        backend.aggr_forward(x, ptr, idx, 5)                  # ptr too short

@@ -1,0 +1,131 @@
+"""Used masks, structure score, histogram, lookups, row assembly and the exchange helpers:
+bit-exact against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from _gen import layered_batch
+
+pytestmark = pytest.mark.gpu
+
+
+def cu(a):
+    return None if a is None else torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("num_layer,fanouts", [(1, [5]), (2, [4, 3]), (3, [15, 10, 5]), (3, [3, 3, 3])])
+@pytest.mark.parametrize("hit_rate", [0.0, 0.3, 1.0])
+def test_used_masks(backend, oracle, num_layer, fanouts, hit_rate):
+    rng = np.random.default_rng(num_layer * 10 + int(hit_rate * 10))
+    b = layered_batch(rng, 40, fanouts, total_nodes=3000)
+    n_all = int(b["num_node_in_layer"][-1])
+    n1 = int(b["num_node_in_layer"][1])
+    hmap = np.where(rng.random(n1) < hit_rate, rng.integers(0, 99, size=n1), -1).astype(np.int64)
+    got = backend.count_history_reconstruct(cu(b["ptr"]), cu(b["idx"]), cu(hmap), n_all, 40, num_layer)
+    want = oracle.used_masks(b["ptr"], b["idx"], hmap, n_all, 40, num_layer)
+    assert len(got) == num_layer + 1
+    for g, w in zip(got, want):
+        assert g.dtype == torch.bool and np.array_equal(g.cpu().numpy(), w)
+    # empty history map = no history anywhere
+    got0 = backend.count_history_reconstruct(cu(b["ptr"]), cu(b["idx"]), torch.tensor([]), n_all, 40, num_layer)
+    want0 = oracle.used_masks(b["ptr"], b["idx"], None, n_all, 40, num_layer)
+    for g, w in zip(got0, want0):
+        assert np.array_equal(g.cpu().numpy(), w)
+
+
+def test_structure_score_and_count_num(backend, oracle):
+    rng = np.random.default_rng(11)
+    b = layered_batch(rng, 30, [6, 4, 3], total_nodes=800)
+    n_all = int(b["num_node_in_layer"][-1])
+    for L in (0, 1, 2, 3):
+        got = backend.get_graph_structure_score(cu(b["ptr"]), cu(b["idx"]), n_all, 30, L)
+        want = oracle.structure_score(b["ptr"], b["idx"], n_all, 30, L)
+        assert np.array_equal(got.cpu().numpy(), want)
+    arr = rng.integers(0, 7, size=5000, dtype=np.int64)
+    got = backend.count_num(cu(arr), 6)
+    want = oracle.count_num(arr, 6)
+    assert got.dtype == torch.int32 and np.array_equal(got.cpu().numpy(), want)
+    assert want[0] == 0 and want[1:].sum() == (arr != 0).sum()
+
+
+def test_map_lookup_and_gather(backend, oracle):
+    rng = np.random.default_rng(2)
+    N = 5000
+    full2embed = np.full(2 * N + 1, -1, dtype=np.int64)
+    full2embed[rng.choice(2 * N, size=3000, replace=False)] = rng.integers(0, 400, size=3000)
+    sub_to_full = rng.choice(N, size=1200, replace=False).astype(np.int64)
+    want_e, want_f = oracle.cache_lookup(full2embed, sub_to_full, 300, N)
+    m = cu(full2embed)
+    assert np.array_equal(backend.map_lookup(m, cu(sub_to_full[:300])).cpu().numpy(), want_e)
+    assert np.array_equal(backend.map_lookup(m, cu(sub_to_full), offset=N).cpu().numpy(), want_f)
+    # seeds forced to miss (history_table.py:106)
+    f2h = full2embed[:N].copy()
+    s2h, _ = oracle.table_lookup(f2h, sub_to_full, 500, 40)
+    got = backend.map_lookup(cu(f2h), cu(sub_to_full[:500]), force_miss_below=40)
+    assert np.array_equal(got.cpu().numpy(), s2h)
+    for feat, dt in [(256, np.float32), (100, np.float32), (128, np.float16), (33, np.float32)]:
+        table = rng.standard_normal((400, feat)).astype(dt)
+        got = backend.gather_rows(cu(table), cu(want_e))
+        assert np.array_equal(got.cpu().numpy(), oracle.gather_rows(table, want_e))  # -1 -> last row
+        got = backend.gather_rows(cu(table), cu(want_e), zero_missing=True)
+        w = oracle.gather_rows(table, want_e)
+        w[want_e == -1] = 0
+        assert np.array_equal(got.cpu().numpy(), w)
+
+
+@pytest.mark.parametrize("feat,host_dt,x_dt", [(128, np.float16, torch.float16),
+                                               (128, np.float16, torch.float32),
+                                               (100, np.float32, torch.float32),
+                                               (33, np.float32, torch.float32)])
+@pytest.mark.parametrize("pinned", [False, True])
+@pytest.mark.parametrize("with_used", [True, False])
+def test_load_rows(backend, oracle, feat, host_dt, x_dt, pinned, with_used):
+    rng = np.random.default_rng(feat + pinned)
+    N, n = 4000, 1500
+    host = rng.standard_normal((N, feat)).astype(host_dt)
+    cache = rng.standard_normal((300, feat)).astype(np.float32)
+    sub_to_full = rng.choice(N, size=n, replace=False).astype(np.int64)
+    sub2feat = np.where(rng.random(n) < 0.3, rng.integers(0, 300, size=n), -1).astype(np.int64)
+    used = (rng.random(n) < 0.6) if with_used else None
+    ht = torch.from_numpy(host)
+    ht = ht.pin_memory() if pinned else ht.cuda()
+    stats = torch.zeros(2, dtype=torch.int64, device="cuda")
+    x, mask = backend.load_rows(ht, cu(cache), cu(sub_to_full), cu(sub2feat), cu(used),
+                                out_dtype=x_dt, want_mask=True, stats=stats)
+    want_x, want_mask = oracle.load_rows(host, cache, sub_to_full, sub2feat, used)
+    assert np.array_equal(mask.cpu().numpy(), want_mask)
+    if x_dt == torch.float16:
+        want_x = want_x.astype(np.float16).astype(np.float32)
+    assert np.array_equal(x.float().cpu().numpy(), want_x)
+    assert stats.tolist() == [int(want_mask.sum()), int((sub2feat != -1).sum())]
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_bucket_unpermute_owner_lookup(backend, oracle, world):
+    rng = np.random.default_rng(world)
+    n, N, feat = 5000, 100_000, 64
+    ids = rng.choice(N, size=n, replace=False).astype(np.int64)
+    keep = rng.random(n) < 0.7
+    for k in (None, keep):
+        counts, perm, bucketed = backend.bucket_by_owner(cu(ids), world, None if k is None else cu(k))
+        wc, wp, wb = oracle.bucket_by_owner(ids, world, k)
+        m = int(wc.sum())
+        assert np.array_equal(counts.cpu().numpy(), wc)
+        assert np.array_equal(perm.cpu().numpy()[:m], wp)
+        assert np.array_equal(bucketed.cpu().numpy()[:m], wb)
+    assert backend.mix64(12345) == int(oracle.mix64(np.array([12345]))[0])
+    # owner-side lookup + un-permute back to batch order
+    counts, perm, bucketed = backend.bucket_by_owner(cu(ids), world)
+    table = rng.standard_normal((700, feat), dtype=np.float32)
+    f2h = np.full(N, -1, dtype=np.int64)
+    have = rng.choice(ids, size=700, replace=False)
+    f2h[have] = rng.permutation(700)
+    flags, rows = backend.owner_lookup(cu(f2h), bucketed, cu(table))
+    dst = torch.zeros((n, feat), device="cuda")
+    hit = torch.empty(n, dtype=torch.int64, device="cuda")
+    backend.unpermute_rows(rows, perm, flags, dst, hit)
+    want = np.zeros((n, feat), dtype=np.float32)
+    slot = f2h[ids]
+    want[slot != -1] = table[slot[slot != -1]]
+    assert np.array_equal(dst.cpu().numpy(), want)
+    assert np.array_equal((hit.cpu().numpy() != -1), slot != -1)

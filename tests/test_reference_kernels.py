@@ -1,0 +1,140 @@
+"""Pins the oracle against the reference's own CUDA operators.
+
+oracle/_ref/ holds `hiscache_backend` built from the unmodified reference sources for
+sm_100a (oracle/Makefile, target `ref`).  The reference has no CPU implementation and no
+golden vectors, so running its kernels beside the oracle on a GPU is what ties the oracle to
+the reference.  Only feature widths that are multiples of 32 are used: for other widths the
+reference's backward reads past the end of its gradient row (history_aggr.cu:146).
+"""
+import glob
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from _gen import csr_block, layered_batch
+
+pytestmark = pytest.mark.gpu
+
+_REF_DIR = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "_ref")
+
+
+@pytest.fixture(scope="module")
+def ref():
+    so = glob.glob(os.path.join(_REF_DIR, "hiscache_backend*.so"))
+    if not so:
+        pytest.skip("reference operators not built (make -C oracle ref)")
+    spec = importlib.util.spec_from_file_location("hiscache_backend", so[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def close(t, want, rtol=1e-5, scale=8.0):
+    # the reference divides with --use_fast_math (CMakeLists.txt:58): a few ulp
+    np.testing.assert_allclose(t.detach().cpu().numpy(), want, rtol=rtol, atol=rtol * scale)
+
+
+@pytest.mark.parametrize("feat", [32, 128, 256])
+def test_reference_aggr_fwd_bwd(ref, oracle, backend, feat):
+    rng = np.random.default_rng(feat)
+    num_dst, n_src = 500, 1500
+    ptr, idx = csr_block(rng, num_dst, n_src, "mixed")
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.3, np.arange(num_dst), -1).astype(np.int64)
+    hbuf = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    xs, hb = cu(x).requires_grad_(True), cu(hbuf).requires_grad_(True)
+    p, i, hm = cu(ptr), cu(idx), cu(hmap)
+    out_ref = ref.aggr_forward_history(xs, p, i, hm, hb, feat, num_dst)
+    want = oracle.aggr_fwd(ptr, idx, x, num_dst, hmap=hmap, hbuf=hbuf)
+    close(out_ref, want)
+    out_ref.backward(cu(g))
+    torch.cuda.synchronize()
+    gi, gh, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, hmap=hmap, hsize=feat)
+    close(xs.grad, gi)
+    close(hb.grad, gh)
+    # and the new library against the reference directly
+    xs2, hb2 = cu(x).requires_grad_(True), cu(hbuf).requires_grad_(True)
+    out_new = backend.aggr_forward_history(xs2, p, i, hm, hb2, feat, num_dst)
+    close(out_new, out_ref.detach().cpu().numpy())
+    out_new.backward(cu(g))
+    close(xs2.grad, xs.grad.cpu().numpy())
+    assert torch.equal(hb2.grad, hb.grad)
+
+
+@pytest.mark.parametrize("heads", [1, 4])
+def test_reference_edge_value(ref, oracle, heads):
+    rng = np.random.default_rng(heads)
+    feat, num_dst, n_src = 64, 200, 600
+    ptr, idx = csr_block(rng, num_dst, n_src, 9)
+    E = int(ptr[-1])
+    multi = heads > 1
+    x = rng.standard_normal((n_src, heads, feat) if multi else (n_src, feat), dtype=np.float32)
+    ev = rng.standard_normal((E, heads) if multi else (E,), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.2, np.arange(num_dst), -1).astype(np.int64)
+    hbuf = rng.standard_normal((num_dst, feat * heads), dtype=np.float32)
+    xs, evs = cu(x).requires_grad_(True), cu(ev).requires_grad_(True)
+    # ptr / idx / history_map must outlive backward: the reference keeps only their raw
+    # device addresses between forward and backward (history_aggr.cu:406-408, :498-500)
+    p, i, hm, hb = cu(ptr), cu(idx), cu(hmap), cu(hbuf)
+    out = ref.aggr_forward_history_edge_value(xs, p, i, evs, hm, hb, feat * heads, num_dst)
+    want = oracle.aggr_fwd(ptr, idx, x, num_dst, edge_value=ev, hmap=hmap, hbuf=hbuf)
+    close(out, want, scale=16.0)
+    g = rng.standard_normal(want.shape, dtype=np.float32)
+    out.backward(cu(g))
+    torch.cuda.synchronize()
+    gi, _, eg = oracle.aggr_bwd(ptr, idx, x, num_dst, g, edge_value=ev, hmap=hmap,
+                                hsize=feat * heads, want_edge_grad=True)
+    close(xs.grad, gi, scale=16.0)
+    close(evs.grad, eg, scale=64.0)
+
+
+def test_reference_used_masks_and_count(ref, oracle):
+    rng = np.random.default_rng(4)
+    b = layered_batch(rng, 50, [15, 10, 5], total_nodes=20000)
+    n_all, n1 = int(b["num_node_in_layer"][-1]), int(b["num_node_in_layer"][1])
+    hmap = np.where(rng.random(n1) < 0.4, 1, -1).astype(np.int64)
+    got = ref.count_history_reconstruct(cu(b["ptr"]), cu(b["idx"]), cu(hmap), n_all, 50, 3)
+    want = oracle.used_masks(b["ptr"], b["idx"], hmap, n_all, 50, 3)
+    for g, w in zip(got, want):
+        assert np.array_equal(g.cpu().numpy(), w)
+    arr = rng.integers(0, 6, size=4000, dtype=np.int64)
+    assert np.array_equal(ref.count_num(cu(arr), 5).cpu().numpy(), oracle.count_num(arr, 5))
+
+
+def test_reference_record_history_same_up_to_slot_order(ref, oracle):
+    """The reference takes ring slots in warp-scheduling order, so slots may be a permutation
+    of the oracle's; the admitted set, the header, the rows stored for each admitted node and
+    the set of unmapped previous owners must agree."""
+    rng = np.random.default_rng(6)
+    N, cap, hs, n = 8000, 1024, 64, 900
+    f2h = np.full(N, -1, dtype=np.int64)
+    h2f = np.full(cap, -1, dtype=np.int64)
+    chk = np.full(cap, -1, dtype=np.int64)
+    buf = np.zeros((cap, hs), dtype=np.float32)
+    sub_to_full = rng.choice(N, size=n, replace=False).astype(np.int64)
+    s2h = f2h[sub_to_full].copy()
+    used = rng.random(n) < 0.7
+    score = np.abs(rng.standard_normal(n)).astype(np.float32)
+    rows = rng.standard_normal((n, hs), dtype=np.float32)
+    header = np.zeros(1, dtype=np.int64)
+    g = [cu(a) for a in (buf, h2f, f2h, header, chk)]
+    ref.record_history(cu(rows), g[0], cu(used), cu(sub_to_full), cu(s2h), g[1], g[2], g[3],
+                       cu(score), cu(np.array([0.8], dtype=np.float32)), g[4], 3)
+    torch.cuda.synchronize()
+    num = oracle.record_history(rows, buf, used, sub_to_full, s2h, h2f, f2h, header, score, 0.8, chk, 3)
+    assert num < cap  # no wrap in this case, so slot sets are comparable
+    r_f2h, r_h2f, r_buf = g[2].cpu().numpy(), g[1].cpu().numpy(), g[0].cpu().numpy()
+    assert np.array_equal(r_f2h != -1, f2h != -1)             # same admitted set
+    assert int(g[3].item()) == int(header[0])                 # same header
+    assert sorted(r_f2h[r_f2h != -1]) == sorted(f2h[f2h != -1])  # same slots used
+    ids = np.nonzero(f2h != -1)[0]
+    assert np.array_equal(r_buf[r_f2h[ids]], buf[f2h[ids]])   # same rows stored per node
+    assert np.array_equal(r_h2f[r_f2h[ids]], ids)
