@@ -16,8 +16,8 @@
  * the reference's CUDA operators compiled unmodified for sm_100a.
  *
  * Build: gcc -O2 -fopenmp -fPIC -shared -std=c11 -ffp-contract=off
- * (-ffp-contract=off matters: the score reduction and the quantile lerp are
- * defined with separately rounded multiply and add).
+ * (-ffp-contract=off matters: the score reduction is defined with separately
+ * rounded multiply and add; the quantile lerp calls fmaf explicitly).
  */
 #include <math.h>
 #include <stdint.h>
@@ -360,6 +360,19 @@ ORC_API void orc_evict_by_score(const int64_t* sub_to_history, const float* scor
 /* src/cpp/src/grad_check.cu:70-130.  masks: (num_layer+1) x num_node       */
 /* bytes, masks[k] at masks + k*num_node.                                   */
 /* ------------------------------------------------------------------------ */
+/* one launch of count_history_kernel (:70-101); seeds_first marks rows < num_seed in `in` */
+ORC_API void orc_used_mask_step(const int64_t* ptr, const int64_t* idx, int64_t ptr_rows,
+                                const int64_t* hmap, int64_t hmap_len, uint8_t* in, uint8_t* out,
+                                int64_t num_seed, int seeds_first) {
+  for (int64_t row = 0; row < ptr_rows; ++row) {
+    if (seeds_first && row < num_seed) in[row] = 1; /* :79-82 */
+    else if (in[row] != 1) continue;
+    if (hmap && row < hmap_len && hmap[row] != -1) continue; /* :87-90 */
+    out[row] = 1;                                            /* :92-94 */
+    for (int64_t e = ptr[row]; e < ptr[row + 1]; ++e) out[idx[e]] = 1;
+  }
+}
+
 ORC_API void orc_used_masks(const int64_t* ptr, const int64_t* idx, int64_t ptr_rows,
                             const int64_t* history_map, int64_t history_map_len,
                             int64_t num_node, int64_t num_seed, int num_layer, uint8_t* masks) {
@@ -367,14 +380,9 @@ ORC_API void orc_used_masks(const int64_t* ptr, const int64_t* idx, int64_t ptr_
   for (int i = 0; i < num_layer; ++i) {
     uint8_t* in = masks + (int64_t)(num_layer - i) * num_node;
     uint8_t* out = masks + (int64_t)(num_layer - 1 - i) * num_node;
-    const int64_t* hmap = (i == 1) ? history_map : NULL; /* :122-124 */
-    for (int64_t row = 0; row < ptr_rows; ++row) {
-      if (row < num_seed && i == 0) in[row] = 1; /* :79-82 */
-      else if (in[row] != 1) continue;
-      if (hmap && row < history_map_len && hmap[row] != -1) continue; /* :87-90 */
-      out[row] = 1;                                                   /* :92-94 */
-      for (int64_t e = ptr[row]; e < ptr[row + 1]; ++e) out[idx[e]] = 1;
-    }
+    /* the history map is passed to the second launch only (:122-124) */
+    orc_used_mask_step(ptr, idx, ptr_rows, (i == 1) ? history_map : NULL, history_map_len, in,
+                       out, num_seed, i == 0);
   }
 }
 

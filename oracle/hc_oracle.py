@@ -203,6 +203,20 @@ def used_masks(ptr, idx, history_map, num_node, num_seed, num_layer):
     return [masks[k].astype(bool) for k in range(num_layer + 1)]
 
 
+def used_mask_step(ptr, idx, use_in, out_len, hmap=None):
+    """One launch of count_history_kernel (grad_check.cu:70-101) from a given in-mask."""
+    ptr, idx = _i64(ptr), _i64(idx)
+    rows = ptr.shape[0] - 1
+    inm = np.zeros(max(out_len, rows), dtype=np.uint8)
+    inm[:len(use_in)] = np.asarray(use_in, dtype=np.uint8)
+    out = np.zeros(max(out_len, rows), dtype=np.uint8)
+    hm = _i64(hmap)
+    lib().orc_used_mask_step(_p(ptr), _p(idx), C.c_int64(rows), _p(hm),
+                             C.c_int64(0 if hm is None else hm.shape[0]), _p(inm), _p(out),
+                             C.c_int64(0), C.c_int(0))
+    return out[:out_len].astype(bool)
+
+
 def structure_score(ptr, idx, num_node, num_seed, num_layer):
     """grad_check.cu:132-163, level-synchronous reading."""
     ptr, idx = _i64(ptr), _i64(idx)
