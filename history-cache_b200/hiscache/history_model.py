@@ -1,0 +1,259 @@
+"""Models of the history path: HistorySAGE / MySageConvHistory, HistoryRGCN /
+MyRGCNConvHistory2 and get_model, with the reference's constructor and forward signatures
+(hiscache/history_model.py:54-184, :220-278, :329-470).  Aggregation runs on
+libhiscache_b200; the dense layers stay torch.nn.Linear (cuBLAS).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+import hiscache_backend as hb
+
+from .util import cfg_get
+
+
+class MySageConvHistory(torch.nn.Module):
+    """lin_l(aggregate(x)) + lin_r(x[:num_node]) (hiscache/history_model.py:54-100)."""
+
+    def __init__(self, in_channels, hidden_channels, need_grad, root_weight: bool = True,
+                 bias: bool = True):
+        super().__init__()
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.root_weight = root_weight
+        self.lin_l = torch.nn.Linear(in_channels, hidden_channels, bias=bias)
+        if self.root_weight:
+            self.lin_r = torch.nn.Linear(in_channels, hidden_channels, bias=False)
+        self.reset_parameters()
+        self.need_grad = need_grad
+
+    def reset_parameters(self):
+        self.lin_l.reset_parameters()
+        if self.root_weight:
+            self.lin_r.reset_parameters()
+
+    def forward(self, x, ptr, idx, history_map, history_buffer, history_size, num_node,
+                indexed=False, score_out=None):
+        """Same seven leading arguments as the reference.  `indexed=True` means
+        history_buffer is the table itself and history_map holds its row numbers (no
+        row-aligned gather needed); `score_out` receives the admission score in backward."""
+        num_node = int(num_node)
+        if history_size > 0:
+            out = hb.aggr_forward(x, ptr, idx, num_node, history_map=history_map,
+                                  history_buffer=history_buffer, indexed=indexed,
+                                  score_out=score_out)
+        else:
+            # the reference calls cxgnncomp.sage_mean_forward here (:90); same kernel, no history
+            out = hb.aggr_forward(x, ptr, idx, num_node, force_grad=False)
+        his = out
+        if self.need_grad and self.training and history_size > 0:
+            his.retain_grad()
+        out = self.lin_l(out)
+        if self.root_weight:
+            root = x[:num_node] if num_node != 0 else x
+            out = out + self.lin_r(root if root.dtype == out.dtype else root.to(out.dtype))
+        return out, his
+
+
+class HistorySAGE(torch.nn.Module):
+    """hiscache/history_model.py:103-184: the conv at index num_layers-2 reads and produces
+    history while training; every other conv is a plain mean aggregation."""
+
+    def __init__(self, in_channels, hidden_channels, out_channels, num_layers, dropout,
+                 graph_type, config, table, **kwargs):
+        super().__init__()
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.out_channels = out_channels
+        self.graph_type = graph_type
+        self.bns = torch.nn.ModuleList()
+        self.num_layers = num_layers
+        for _ in range(self.num_layers - 1):
+            self.bns.append(torch.nn.BatchNorm1d(hidden_channels))
+        self.dropout = dropout
+        self.table = table
+        self.init_convs(**kwargs)
+
+    def _history_args(self, n):
+        t = self.table
+        if getattr(t, "buffer", None) is not None and hasattr(t, "embedding_table"):
+            score = t.score_sink(n) if (t.method == "grad" and hasattr(t, "score_sink")) else None
+            return t.sub2embed, t.embedding_table, True, score
+        return t.sub2embed, t.cached_embedding, False, None
+
+    def forward(self, batch):
+        x = batch.x
+        nn = batch.num_node_in_layer
+        for i, conv in enumerate(self.convs[:-1]):
+            n = int(nn[self.num_layers - 1 - i])
+            if self.training and i == self.num_layers - 2:
+                hmap, hbuf, indexed, score = self._history_args(n)
+                x, his = conv(x, batch.ptr, batch.idx, hmap, hbuf, self.hidden_channels, n,
+                              indexed=indexed, score_out=score)
+                self.table.produced_embedding = his
+            else:
+                x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
+            x = self.bns[i](x)
+            x = F.relu(x)
+            x = F.dropout(x, p=self.dropout, training=self.training)
+        x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))
+        return x.log_softmax(dim=-1)
+
+    def init_convs(self, **kwargs):
+        need = self.table.method == "grad"
+        self.convs = torch.nn.ModuleList()
+        self.convs.append(self.init_history_conv(self.in_channels, self.hidden_channels, need_grad=need, **kwargs))
+        for _ in range(self.num_layers - 2):
+            self.convs.append(self.init_history_conv(self.hidden_channels, self.hidden_channels, need_grad=need, **kwargs))
+        if self.num_layers > 1:
+            self.last_layer_history = False
+            self.convs.append(self.init_history_conv(self.hidden_channels, self.out_channels, need_grad=need, **kwargs))
+
+    def init_history_conv(self, in_channels, out_channels, **kwargs):
+        assert "need_grad" in kwargs
+        return MySageConvHistory(in_channels, out_channels, **kwargs)
+
+    def reset_parameters(self):
+        for conv in self.convs:
+            conv.reset_parameters()
+        for bn in self.bns:
+            bn.reset_parameters()
+
+
+class MyRGCNConvHistory2(torch.nn.Module):
+    """out[d] = (1/deg(d)) * sum_e x[src_e] @ W[rel_e], history rows overriding
+    (hiscache/history_model.py:220-278).  The reference sorts edges by relation and calls
+    cxgnncomp.RGCNOP_sorted, which is not part of the project; here each relation is a
+    masked weighted-sum aggregation (edge value 1 on the relation's edges) followed by one
+    dense product, normalised by the total in-degree as the reference does (:245,272)."""
+
+    def __init__(self, in_channels, hidden_channels, num_rel, need_grad):
+        super().__init__()
+        self.in_channels = in_channels
+        self.hidden_channels = hidden_channels
+        self.num_rel = num_rel
+        self.linear = torch.nn.Parameter(torch.empty(num_rel, in_channels, hidden_channels))
+        self.reset_parameters()
+        self.need_grad = need_grad
+
+    def reset_parameters(self):
+        # glorot (torch_geometric.nn.inits.glorot in the reference, :240)
+        a = math.sqrt(6.0 / (self.linear.size(-2) + self.linear.size(-1)))
+        with torch.no_grad():
+            self.linear.uniform_(-a, a)
+
+    def forward(self, x, ptr, idx, edge_types, count, history_map, history_buffer, used_mask,
+                history_size, num_node, indexed=False, score_out=None):
+        num_node = int(num_node)
+        num_edge = int(ptr[num_node])
+        deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(torch.float32)
+        src = idx[:num_edge]
+        rel = edge_types[:num_edge]
+        if used_mask is not None:
+            rel = torch.where(used_mask[src], rel, torch.full_like(rel, self.num_rel))  # :250
+        out = None
+        xf = x if x.dtype in (torch.float32, torch.float16) else x.float()
+        for r in range(self.num_rel):
+            w = (rel == r).to(torch.float32)
+            agg = hb.aggr_forward(xf, ptr, idx, num_node, edge_value=w, force_grad=False)
+            term = agg @ self.linear[r]
+            out = term if out is None else out + term
+        out = out / deg.unsqueeze(-1)
+        if history_size > 0 and history_map is not None and history_map.numel() > 0:
+            hit = history_map[:num_node] != -1
+            rows = hb.gather_rows(history_buffer, history_map[:num_node] if indexed else
+                                  torch.where(hit, torch.arange(num_node, device=x.device), -1),
+                                  zero_missing=True, out_dtype=torch.float32)
+            out = torch.where(hit.unsqueeze(-1), rows, out)
+        his = out
+        if self.need_grad and self.training and history_size > 0:
+            his.retain_grad()
+        return out, his
+
+
+class HistoryRGCN(torch.nn.Module):
+    """hiscache/history_model.py:329-431."""
+
+    def __init__(self, in_channels, hidden_channels, out_channels, num_layers, dropout,
+                 graph_type, config, table, **kwargs):
+        super().__init__()
+        self.in_channels, self.hidden_channels, self.out_channels = in_channels, hidden_channels, out_channels
+        self.graph_type = graph_type
+        self.num_layers = num_layers
+        self.bns = torch.nn.ModuleList(torch.nn.BatchNorm1d(hidden_channels) for _ in range(num_layers - 1))
+        self.dropout = dropout
+        self.table = table
+        self.num_rel = kwargs["num_rel"]
+        self.dataset_name = kwargs.get("dataset_name", "")
+        self.init_convs(num_rel=self.num_rel)
+
+    def forward(self, batch):
+        x = batch.x
+        nn, ne = batch.num_node_in_layer, batch.num_edge_in_layer
+        L = self.num_layers
+        etypes = batch.edge_type
+        if etypes is None:  # :363-366
+            etypes = torch.randint(0, self.num_rel, (int(ne[L - 1]),), device=x.device)
+        um = self.table.used_masks
+        for i, conv in enumerate(self.convs[:-1]):
+            n = int(nn[L - 1 - i])
+            et = etypes[:int(ne[L - 1 - i])]
+            used = um[i] if um is not None else None
+            if self.training and i == L - 2:
+                t = self.table
+                if getattr(t, "buffer", None) is not None and hasattr(t, "embedding_table"):
+                    hmap, hbuf, indexed = t.sub2embed, t.embedding_table, True
+                else:
+                    hmap, hbuf, indexed = t.sub2embed, t.cached_embedding, False
+                x, his = conv(x, batch.ptr, batch.idx, et, None, hmap, hbuf, used,
+                              self.hidden_channels, n, indexed=indexed)
+                self.table.produced_embedding = his
+                self.table.produced_embedding.retain_grad()
+            else:
+                x, his = conv(x, batch.ptr, batch.idx, et, None, None, None, used, 0, n)
+            x = self.bns[i](x)
+            x = F.relu(x)
+            x = F.dropout(x, p=self.dropout, training=self.training)
+        x, his = self.convs[-1](x, batch.ptr, batch.idx, etypes[:int(ne[0])], None, None, None,
+                                um[-2] if um is not None else None, 0, int(nn[0]))
+        return x.log_softmax(dim=-1)
+
+    def init_convs(self, **kwargs):
+        need = self.table.method == "grad"
+        self.convs = torch.nn.ModuleList()
+        self.convs.append(MyRGCNConvHistory2(self.in_channels, self.hidden_channels, need_grad=need, **kwargs))
+        for _ in range(self.num_layers - 2):
+            self.convs.append(MyRGCNConvHistory2(self.hidden_channels, self.hidden_channels, need_grad=need, **kwargs))
+        if self.num_layers > 1:
+            self.last_layer_history = False
+            self.convs.append(MyRGCNConvHistory2(self.hidden_channels, self.out_channels, need_grad=need, **kwargs))
+
+    def reset_parameters(self):
+        for conv in self.convs:
+            conv.reset_parameters()
+        for bn in self.bns:
+            bn.reset_parameters()
+
+
+model_dict = {"sage": HistorySAGE, "rgcn": HistoryRGCN}
+graph_type_dict = {"cxg": "CSR_Layer", "dgl": "DGL"}
+
+
+def get_model(config, table):
+    """hiscache/history_model.py:446-470."""
+    in_channel = config.dl.dataset.feature_dim
+    out_channel = config.dl.dataset.num_classes
+    hidden_channel = config.train.model.hidden_dim
+    num_layers = config.train.model.num_layers
+    dropout = config.train.model.dropout
+    graph_type = graph_type_dict[config.train.type.lower()]
+    kind = config.train.model.type.lower()
+    if kind == "rgcn":
+        return model_dict[kind](in_channel, hidden_channel, out_channel, num_layers, dropout,
+                                graph_type, config, table, num_rel=config.train.model.num_rel,
+                                dataset_name=str(cfg_get(config, "dl.dataset.name", "")).lower())
+    return model_dict[kind](in_channel, hidden_channel, out_channel, num_layers, dropout,
+                            graph_type, config, table)

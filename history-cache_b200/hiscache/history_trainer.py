@@ -1,0 +1,137 @@
+"""Single-GPU trainer (hiscache/history_trainer.py:15-255 of the reference).
+
+The reference subclasses cxgnncomp.Trainer and takes loader, optimiser, scheduler, loss and
+evaluator from cxgnndl / cxgnncomp, none of which belong to the project.  Here the loader is
+hiscache.sampler.get_loader over a synthetic graph, the feature store is
+hiscache.feature_store.HostFeatureStore, the optimiser is Adam, the loss is NLL on the
+model's log-softmax output and the metric is accuracy.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+from .feature_store import HostFeatureStore
+from .history_cache import HistoryCache
+from .history_model import get_model
+from .sampler import get_loader
+from .util import cfg_get, log
+
+
+class HistoryTrainer:
+
+    def __init__(self, config, graph=None, uvm=None, loader=None, storage_dtype=torch.float32,
+                 feature_dtype=torch.float32, seed=0):
+        self.config = config
+        self.device = torch.device(config.dl.device)
+        torch.cuda.set_device(self.device)
+        self.loader = loader if loader is not None else get_loader(config.dl, graph=graph, seed=seed)
+        self.feat_mode = config.dl.loading.feat_mode
+        if uvm is None and self.feat_mode != "memory":
+            g = self.loader.graph
+            uvm = HostFeatureStore.synthetic(g.num_nodes, config.dl.dataset.feature_dim,
+                                             dtype=feature_dtype, seed=seed, device=self.device)
+        self.uvm = uvm
+        self.table = HistoryCache(uvm=self.uvm, config=config, mode=self.feat_mode,
+                                  total_num_node=self.loader.graph.num_nodes,
+                                  sorted_indices=self.loader.graph.sorted_indices,
+                                  storage_dtype=storage_dtype)
+        self.model = get_model(config, self.table).to(self.device)
+        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3))
+        self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
+        self.loss_fn = F.nll_loss
+        self.type = config.train.type.lower()
+        self.load_type = config.dl.type.lower()
+        self.glb_iter = 0
+        self.prof = cfg_get(config, "dl.performance.prof", False)
+        self.val_metrics, self.test_metrics = [], []
+        self.best_metric = 0
+        self.phase_ms = {}
+
+    # one iteration of cxg_train_epoch (history_trainer.py:183-191)
+    def train_step(self, batch):
+        self.optimizer.zero_grad(set_to_none=True)
+        self.table.lookup_and_load(batch, len(self.model.convs))
+        out = self.model(batch)
+        loss = self.loss_fn(out, batch.y)
+        loss.backward()
+        self.optimizer.step()
+        self.scheduler.step()
+        self.table.update_history(batch, self.glb_iter)
+        self.glb_iter += 1
+        return loss
+
+    def cxg_train_epoch(self):
+        self.model.train()
+        tepoch = time.time()
+        n = 0
+        for batch in self.loader.train_loader:
+            self.train_step(batch)
+            n += 1
+        torch.cuda.synchronize()
+        log.info(f"epoch time: {time.time() - tepoch} ({n} iterations)")
+
+    def cxg_train_epoch_prof(self):
+        """Per-phase device times (history_trainer.py:77-132 uses host clocks around
+        synchronize; CUDA events here)."""
+        self.model.train()
+        names = ["load", "forward", "backward", "step", "update"]
+        acc = {k: 0.0 for k in names}
+        for batch in self.loader.train_loader:
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+            self.optimizer.zero_grad(set_to_none=True)
+            ev[0].record()
+            self.table.lookup_and_load(batch, len(self.model.convs))
+            ev[1].record()
+            out = self.model(batch)
+            loss = self.loss_fn(out, batch.y)
+            ev[2].record()
+            loss.backward()
+            ev[3].record()
+            self.optimizer.step()
+            self.scheduler.step()
+            ev[4].record()
+            self.table.update_history(batch, self.glb_iter)
+            ev[5].record()
+            self.glb_iter += 1
+            torch.cuda.synchronize()
+            for i, k in enumerate(names):
+                acc[k] += ev[i].elapsed_time(ev[i + 1])
+        self.phase_ms = acc
+        log.info("phase ms: %s", acc)
+
+    @torch.no_grad()
+    def cxg_eval_epoch(self, split="val"):
+        self.model.eval()
+        correct = total = 0
+        loader = self.loader.val_loader if split == "val" else self.loader.test_loader
+        for batch in loader:
+            self.table.lookup_and_load(batch, len(self.model.convs), feature_cache_only=True)
+            out = self.model(batch)
+            correct += int((out.argmax(-1) == batch.y).sum())
+            total += batch.y.shape[0]
+        self.metric = correct / max(total, 1)
+        log.info(f"{split}-metric: {self.metric}")
+        if split == "val":
+            self.best_metric = max(self.best_metric, self.metric)
+            self.val_metrics.append(self.metric)
+        else:
+            self.test_metrics.append(self.metric)
+
+    def train(self):
+        for epoch in range(self.config.train.train.num_epochs):
+            log.info(f"Epoch {epoch}/{self.config.train.train.num_epochs}")
+            if self.prof:
+                self.cxg_train_epoch_prof()
+            else:
+                self.cxg_train_epoch()
+            if epoch >= self.config.train.train.eval_begin:
+                self.cxg_eval_epoch(split="val")
+                self.cxg_eval_epoch(split="test")
+        if len(self.val_metrics) > 0:
+            v, t = np.array(self.val_metrics), np.array(self.test_metrics)
+            log.info(f"best-val-metrics: {v.max()} at epoch {v.argmax()}")
+            log.info(f"best-test-metrics: {t.max()} valided test-metric {t[v.argmax()]}")

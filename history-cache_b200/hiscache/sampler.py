@@ -1,0 +1,194 @@
+"""Synthetic graphs and a GPU neighbour sampler: the stand-in for `cxgnndl.get_loader`
+(hiscache/history_trainer.py:19).  That loader is not part of the reference project; what the
+hot path needs from it is the batch layout, which is inferred from its uses
+(hiscache/history_model.py:120-153, hiscache/history_cache.py:307-324):
+
+    batch.ptr, batch.idx   one CSR (int64, batch-local ids) shared by all layers; nodes are
+                           ordered seeds first, then each hop's new nodes, so layer k's
+                           destinations are rows [0, num_node_in_layer[k])
+    batch.sub_to_full      local -> global id, unique
+    batch.y                labels of the seeds
+    batch.num_node_in_layer, batch.num_edge_in_layer   L+1 / L entries (CPU tensors)
+    batch.x                filled by HistoryCache.lookup_and_load
+
+Fan-outs are listed from the seeds outwards (fanouts[0] neighbours per seed).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+
+class Batch:
+    __slots__ = ("ptr", "idx", "sub_to_full", "y", "num_node_in_layer", "num_edge_in_layer", "x",
+                 "edge_type", "typed_num_node_in_layer", "mask")
+
+    def __init__(self):
+        self.x = None
+        self.edge_type = None
+        self.typed_num_node_in_layer = None
+        self.mask = None
+
+    def to(self, device, non_blocking=True):
+        b = Batch()
+        for k in ("ptr", "idx", "sub_to_full", "y"):
+            setattr(b, k, getattr(self, k).to(device, non_blocking=non_blocking))
+        b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
+        return b
+
+    def pin(self):
+        b = Batch()
+        for k in ("ptr", "idx", "sub_to_full", "y"):
+            setattr(b, k, getattr(self, k).cpu().pin_memory())
+        b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
+        return b
+
+    def nbytes(self):
+        return sum(getattr(self, k).numel() * getattr(self, k).element_size()
+                   for k in ("ptr", "idx", "sub_to_full", "y"))
+
+
+class SyntheticGraph:
+    """Power-law graph in CSR on one device: out-degree ~ Zipf(exponent) scaled to a mean,
+    edge targets drawn with a power-law popularity so that a degree-ordered feature cache has
+    something to win (uniform targets would make every node equally cold)."""
+
+    def __init__(self, num_nodes, mean_degree, exponent, num_classes, seed=0, device="cuda:0",
+                 num_train=None, popularity=3.0, max_degree=100_000, chunk=1 << 27):
+        dev = torch.device(device)
+        g = torch.Generator(device=dev)
+        g.manual_seed(int(seed))
+        N = int(num_nodes)
+        self.num_nodes, self.num_classes, self.device = N, int(num_classes), dev
+        u = torch.rand(N, generator=g, device=dev, dtype=torch.float64).clamp_(min=1e-12)
+        raw = u.pow_(-1.0 / (exponent - 1.0)).clamp_(max=float(max_degree))
+        scale = mean_degree / float(raw.mean())
+        deg = (raw * scale).floor_().clamp_(min=1).to(torch.int64)
+        del raw, u
+        self.ptr = torch.zeros(N + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(deg, 0, out=self.ptr[1:])
+        E = int(self.ptr[-1].item())
+        self.num_edges = E
+        self.idx = torch.empty(E, dtype=torch.int64, device=dev)
+        indeg = torch.zeros(N, dtype=torch.int64, device=dev)
+        for b in range(0, E, chunk):
+            e = min(E, b + chunk)
+            t = torch.rand(e - b, generator=g, device=dev, dtype=torch.float64)
+            t = (t.pow_(popularity) * N).to(torch.int64).clamp_(max=N - 1)
+            self.idx[b:e] = t
+            indeg += torch.bincount(t, minlength=N)
+            del t
+        # ascending in-degree, hottest nodes last (the layout of sorted_indices.dat that
+        # HistoryCache.fill reads, hiscache/history_cache.py:124-134)
+        self.sorted_indices = torch.argsort(indeg, stable=True)
+        del indeg, deg
+        self.labels = torch.randint(0, self.num_classes, (N,), generator=g, device=dev, dtype=torch.int64)
+        n_train = N if num_train is None else int(num_train)
+        self.train_ids = torch.randperm(N, generator=g, device=dev)[:n_train] if n_train < N \
+            else torch.arange(N, device=dev)
+
+
+class NeighborSampler:
+    """Uniform neighbour sampling with replacement (min(fanout, degree) draws per node),
+    de-duplicated into the layered single-CSR layout."""
+
+    def __init__(self, graph: SyntheticGraph, fanouts, seed=0):
+        self.g = graph
+        self.fanouts = [int(f) for f in fanouts]
+        self.gen = torch.Generator(device=graph.device)
+        self.gen.manual_seed(int(seed))
+        # global -> local id of the batch being built (-1 outside a batch)
+        self.local = torch.full((graph.num_nodes,), -1, dtype=torch.int32, device=graph.device)
+
+    @torch.no_grad()
+    def sample(self, seeds: torch.Tensor) -> Batch:
+        g, dev = self.g, self.g.device
+        seeds = seeds.to(dev)
+        n_seed = seeds.shape[0]
+        self.local[seeds] = torch.arange(n_seed, dtype=torch.int32, device=dev)
+        nodes = [seeds]
+        n_total = n_seed
+        frontier = seeds
+        counts_all, nbr_all = [], []
+        layer_nodes, layer_edges = [n_seed], []
+        n_edges = 0
+        for f in self.fanouts:
+            start = g.ptr[frontier]
+            deg = g.ptr[frontier + 1] - start
+            k = deg.clamp(max=f)
+            rep = torch.repeat_interleave(torch.arange(frontier.shape[0], device=dev), k)
+            r = torch.rand(rep.shape[0], generator=self.gen, device=dev, dtype=torch.float64)
+            pick = start[rep] + (r * deg[rep]).to(torch.int64)
+            pick = torch.minimum(pick, start[rep] + deg[rep] - 1)
+            nbr = g.idx[pick]
+            loc = self.local[nbr]
+            new = torch.unique(nbr[loc < 0])
+            self.local[new] = torch.arange(n_total, n_total + new.shape[0], dtype=torch.int32, device=dev)
+            nodes.append(new)
+            n_total += int(new.shape[0])
+            counts_all.append(k)
+            nbr_all.append(self.local[nbr].to(torch.int64))
+            n_edges += int(nbr.shape[0])
+            layer_nodes.append(n_total)
+            layer_edges.append(n_edges)
+            frontier = new
+        sub_to_full = torch.cat(nodes)
+        self.local[sub_to_full] = -1
+        counts = torch.cat(counts_all)
+        b = Batch()
+        b.ptr = torch.zeros(counts.shape[0] + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(counts, 0, out=b.ptr[1:])
+        b.idx = torch.cat(nbr_all)
+        b.sub_to_full = sub_to_full
+        b.y = g.labels[seeds]
+        b.num_node_in_layer = torch.tensor(layer_nodes, dtype=torch.int64)
+        b.num_edge_in_layer = torch.tensor(layer_edges, dtype=torch.int64)
+        return b
+
+
+class Loader:
+    """`loader.train_loader` / `val_loader` / `test_loader` as the trainers iterate them
+    (hiscache/history_trainer.py:179-181,199-202)."""
+
+    def __init__(self, graph, fanouts, batch_size, feat_mode, seed=0, rank=0, world=1,
+                 iters_per_epoch=None):
+        self.graph, self.feat_mode = graph, feat_mode
+        self.sampler = NeighborSampler(graph, fanouts, seed=seed * 1009 + rank)
+        self.batch_size = int(batch_size)
+        ids = graph.train_ids
+        self.train_ids = ids[rank::world] if world > 1 else ids
+        self.iters_per_epoch = iters_per_epoch or max(1, math.ceil(self.train_ids.shape[0] / self.batch_size))
+        self._gen = torch.Generator(device=graph.device)
+        self._gen.manual_seed(int(seed) * 7919 + rank)
+
+    def _iterate(self, n_iters):
+        n = self.train_ids.shape[0]
+        for _ in range(n_iters):
+            sel = torch.randint(0, n, (self.batch_size,), generator=self._gen, device=self.graph.device)
+            seeds = torch.unique(self.train_ids[sel])
+            yield self.sampler.sample(seeds)
+
+    @property
+    def train_loader(self):
+        return self._iterate(self.iters_per_epoch)
+
+    @property
+    def val_loader(self):
+        return self._iterate(max(1, self.iters_per_epoch // 10))
+
+    test_loader = val_loader
+
+
+def get_loader(dl_config, graph=None, rank=0, world=1, seed=0, iters_per_epoch=None):
+    """Counterpart of cxgnndl.get_loader(config.dl) for synthetic graphs: needs either a
+    ready SyntheticGraph or dl.dataset.{num_nodes, mean_degree, exponent}."""
+    from .util import cfg_get
+    if graph is None:
+        ds = dl_config.dataset
+        graph = SyntheticGraph(ds.num_nodes, cfg_get(ds, "mean_degree", 15.0), cfg_get(ds, "exponent", 2.0),
+                               ds.num_classes, seed=seed, device=dl_config.device,
+                               num_train=cfg_get(ds, "num_train", None))
+    return Loader(graph, cfg_get(dl_config, "sampler.fanouts", [15, 10, 5]),
+                  cfg_get(dl_config, "sampler.batch_size", 1000), dl_config.loading.feat_mode,
+                  seed=seed, rank=rank, world=world, iters_per_epoch=iters_per_epoch)

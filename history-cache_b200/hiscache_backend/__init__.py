@@ -33,20 +33,80 @@ __all__ = [
     "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
     "aggr_forward", "score_rows", "select_threshold", "cache_admit", "evict_stale",
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
-    "unpermute_rows", "owner_lookup", "mix64", "launch_count",
+    "unpermute_rows", "owner_lookup", "mix64", "launch_count", "ScoreSink", "KernelTimer",
+    "set_kernel_timer",
 ]
 
 _launches = 0
 
 
 def launch_count() -> int:
-    """Number of library entry points called so far in this process."""
+    """Number of kernels of this library launched so far in this process."""
     return _launches
 
 
 def _called(n=1):
     global _launches
     _launches += n
+
+
+class KernelTimer:
+    """Collects CUDA-event pairs around library calls (set with set_kernel_timer)."""
+
+    def __init__(self):
+        self.records = []
+
+    def summary(self):
+        torch.cuda.synchronize()
+        agg = {}
+        for name, e0, e1 in self.records:
+            a = agg.setdefault(name, {"launches": 0, "ms_total": 0.0})
+            a["launches"] += 1
+            a["ms_total"] += e0.elapsed_time(e1)
+        return agg
+
+
+_timer = None
+
+
+def set_kernel_timer(t):
+    """While a KernelTimer is set, every library call is bracketed by two CUDA events on the
+    stream it launches on."""
+    global _timer
+    _timer = t
+
+
+class _span:
+    __slots__ = ("name", "dev", "e0")
+
+    def __init__(self, name, dev):
+        self.name, self.dev, self.e0 = name, dev, None
+
+    def __enter__(self):
+        if _timer is not None:
+            self.e0 = torch.cuda.Event(enable_timing=True)
+            self.e0.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, *exc):
+        if self.e0 is not None:
+            e1 = torch.cuda.Event(enable_timing=True)
+            e1.record(torch.cuda.current_stream(self.dev))
+            _timer.records.append((self.name, self.e0, e1))
+        return False
+
+
+def _tag(name, t):
+    return f"{name}[{'f16' if t.dtype == torch.float16 else 'f32'},F={t.shape[-1]}]"
+
+
+class ScoreSink:
+    """Where the aggregation's backward pass leaves the per-row admission score.
+    `fresh` turns True when a backward pass has written `tensor` since the last reset."""
+
+    def __init__(self, tensor):
+        self.tensor = tensor
+        self.fresh = False
 
 
 def _empty(t):
@@ -110,7 +170,7 @@ class _AggrFunction(torch.autograd.Function):
         shape = (num_node, inp.shape[1], inp.shape[2]) if multi else (num_node, inp.shape[1])
         out = torch.empty(shape, dtype=torch.float32, device=dev)
         a = _aggr_args(inp, ptr_t, idx_t, num_node, edge_value, hmap, hbuf, h_indexed, src_map, src_alt)
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), _span(_tag("hc_aggr_fwd", inp), dev):
             check(lib.hc_aggr_fwd(C.byref(a), ptr(out), stream_of(dev)), "hc_aggr_fwd")
         _called()
         ctx.save_for_backward(inp, ptr_t, idx_t, edge_value, hmap, hbuf, src_map, src_alt)
@@ -139,15 +199,18 @@ class _AggrFunction(torch.autograd.Function):
         if need_h:
             g_h = torch.zeros(hbuf.shape, dtype=torch.float32, device=dev)
             a.hsize = hbuf.shape[-1]  # grad_history is dense
-        score = ctx.score_out
+        sink = ctx.score_out
+        score = sink.tensor if isinstance(sink, ScoreSink) else sink
         if score is not None and (inp.dim() == 3):
             score = None
         if not (need_in or need_ev or need_h or score is not None):
             return (None,) * 12
-        with torch.cuda.device(dev):
+        with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd", inp), dev):
             check(lib.hc_aggr_bwd(C.byref(a), ptr(grad_out), ptr(g_in), 1, ptr(g_h), ptr(g_ev),
                                   ptr(score), ctx.score_kind, stream_of(dev)), "hc_aggr_bwd")
         _called()
+        if score is not None and isinstance(sink, ScoreSink):
+            sink.fresh = True
         if g_in is not None and g_in.dtype != inp.dtype:
             g_in = g_in.to(inp.dtype)
         if g_h is not None and g_h.dtype != hbuf.dtype:
@@ -157,16 +220,17 @@ class _AggrFunction(torch.autograd.Function):
 
 def aggr_forward(input, ptr, idx, num_node=0, *, history_map=None, history_buffer=None,
                  indexed=False, edge_value=None, src_map=None, src_alt=None, score_out=None,
-                 score_kind=HC_SCORE_L2):
+                 score_kind=HC_SCORE_L2, force_grad=True):
     """History-aware aggregation.
 
     out[r] = history row if history_map[r] != -1 else mean (or edge-weighted sum) of the
     source rows of r's neighbours.  `indexed=True` reads row history_map[r] of
     `history_buffer` (the table itself); otherwise row r (a row-aligned gather, the
     reference layout).  `src_map`/`src_alt` choose, per source, a cached row instead of the
-    fresh one.  If `score_out` (fp32 [num_node]) is given, the backward pass writes the
-    per-row admission score of the incoming gradient into it.
-    The result always requires grad (history_aggr.cu:604).
+    fresh one.  If `score_out` (fp32 [num_node], or a ScoreSink holding one) is given, the
+    backward pass writes the per-row admission score of the incoming gradient into it.
+    With force_grad (the default) the result requires grad even when no input does
+    (history_aggr.cu:604), which is what lets a caller retain_grad() it.
     """
     if num_node == 0:
         num_node = ptr.shape[0] - 1
@@ -179,7 +243,7 @@ def aggr_forward(input, ptr, idx, num_node=0, *, history_map=None, history_buffe
     out = _AggrFunction.apply(input, ptr, idx, edge_value, history_map, history_buffer,
                               int(num_node), bool(indexed), src_map, src_alt, score_out,
                               int(score_kind))
-    if not out.requires_grad:
+    if force_grad and not out.requires_grad:
         out.requires_grad_(True)
     return out
 
@@ -224,7 +288,7 @@ def score_rows(x, kind=HC_SCORE_L2, out=None):
     n, F = x.shape
     if out is None:
         out = torch.empty(n, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_score_rows", dev):
         check(lib.hc_score_rows(ptr(x), n, F, x.stride(0) if n > 1 else F, kind, ptr(out),
                                 stream_of(dev)), "hc_score_rows")
     _called()
@@ -237,7 +301,7 @@ def select_threshold(score, q, out=None):
     score = score.contiguous()
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_select_threshold", dev):
         check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
                                       stream_of(dev)), "hc_select_threshold")
     _called()
@@ -273,7 +337,7 @@ def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_histor
         raise RuntimeError("record_history: per-row arguments shorter than buffer_new")
     thres = thres.reshape(-1).float()
     sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_record_history", dev):
         check(lib.hc_record_history(
             ptr(buffer_new), buffer_new.stride(0) if n > 1 else hs, n, ptr(buffer_all),
             dtype_code(buffer_all), buffer_all.shape[0], hs, ptr(used_mask),
@@ -281,7 +345,7 @@ def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_histor
             ptr(full_to_history), ptr(header), ptr(score.contiguous().float()), ptr(thres),
             ptr(checkin_iter), int(glb_iter), ptr(n_admitted), ptr(sc), stream_of(dev)),
             "hc_record_history")
-    _called()
+    _called(4)
 
 
 def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, sub2embed, score,
@@ -296,20 +360,20 @@ def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, 
     n = produced.shape[0]
     sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
     f2f_len = 0 if feat2full is None else feat2full.shape[0]
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_cache_admit", dev):
         check(lib.hc_cache_admit(
             ptr(produced), produced.stride(0) if n > 1 else hidden, n, ptr(buffer),
             dtype_code(buffer), hidden, in_feat, embed_capacity, ptr(i64c(sub_to_full)),
             ptr(i64c(sub2embed)), ptr(score), ptr(thres), ptr(full2embed), total_num_node,
             ptr(embed2full), ptr(feat2full), f2f_len, ptr(header), 1 if reset_header else 0,
             ptr(n_admitted), ptr(sc), stream_of(dev)), "hc_cache_admit")
-    _called()
+    _called(4)
 
 
 def evict_stale(checkin_iter, history_to_full, full_to_history, glb_iter, limit):
     """hiscache/history_table.py:189-200."""
     dev = require_cuda(checkin_iter, history_to_full, full_to_history)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_evict_stale", dev):
         check(lib.hc_evict_stale(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
                                  checkin_iter.shape[0], int(glb_iter), int(limit),
                                  stream_of(dev)), "hc_evict_stale")
@@ -320,7 +384,7 @@ def evict_by_score(sub_to_history, score, thres, checkin_iter, history_to_full, 
     """hiscache/history_table.py:234-241."""
     dev = require_cuda(sub_to_history, score, thres, checkin_iter)
     n = min(sub_to_history.shape[0], score.shape[0])
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_evict_by_score", dev):
         check(lib.hc_evict_by_score(ptr(i64c(sub_to_history)), ptr(score.contiguous()),
                                     ptr(thres.reshape(-1)), n, ptr(checkin_iter),
                                     ptr(history_to_full), ptr(full_to_history), stream_of(dev)),
@@ -338,11 +402,11 @@ def count_history_reconstruct(ptr_t, idx_t, history_maps, num_node, num_seed, nu
     ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
     hm = None if _empty(history_maps) else i64c(history_maps, "history_maps")
     buf = torch.empty((num_layer + 1, num_node), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_used_masks", dev):
         check(lib.hc_used_masks(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, ptr(hm),
                                 0 if hm is None else hm.shape[0], num_node, num_seed, num_layer,
                                 ptr(buf), stream_of(dev)), "hc_used_masks")
-    _called()
+    _called(num_layer)
     b = buf.view(torch.bool)
     return [b[k] for k in range(num_layer + 1)]
 
@@ -353,7 +417,7 @@ def get_graph_structure_score(ptr_t, idx_t, num_node, num_seed, num_layer):
     ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
     out = torch.empty(num_node, dtype=torch.int64, device=dev)
     sc = torch.empty(num_node, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_structure_score", dev):
         check(lib.hc_structure_score(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, num_node,
                                      num_seed, num_layer, ptr(out), ptr(sc), stream_of(dev)),
               "hc_structure_score")
@@ -366,7 +430,7 @@ def count_num(arr, mmax):
     dev = require_cuda(arr)
     arr = i64c(arr, "arr")
     out = torch.empty(int(mmax) + 1, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_count_num", dev):
         check(lib.hc_count_num(ptr(arr), arr.shape[0], int(mmax), ptr(out), stream_of(dev)),
               "hc_count_num")
     _called()
@@ -383,7 +447,7 @@ def map_lookup(map_t, ids, offset=0, force_miss_below=0, out=None):
     n = ids.shape[0]
     if out is None:
         out = torch.empty(n, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_map_lookup", dev):
         check(lib.hc_map_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, int(offset),
                                 int(force_miss_below), ptr(out), stream_of(dev)), "hc_map_lookup")
     _called()
@@ -397,7 +461,7 @@ def gather_rows(table, rows, zero_missing=False, out_dtype=None):
     rows = i64c(rows, "rows")
     n, F = rows.shape[0], table.shape[1]
     out = torch.empty((n, F), dtype=out_dtype or table.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_gather_rows", dev):
         check(lib.hc_gather_rows(ptr(table), dtype_code(table), table.shape[0],
                                  table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows), n,
                                  1 if zero_missing else 0, ptr(out), dtype_code(out), F,
@@ -428,7 +492,7 @@ def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=Non
         feat_cache = rows2d(feat_cache)
         cd, cr = dtype_code(feat_cache), feat_cache.shape[0]
         cs = feat_cache.stride(0) if cr > 1 else F
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_load_rows", dev):
         check(lib.hc_load_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
                                host_table.stride(0) if host_table.shape[0] > 1 else F,
                                ptr(feat_cache), cd, cr, cs, F, ptr(sub_to_full), ptr(sub2feat),
@@ -456,10 +520,10 @@ def bucket_by_owner(ids, world, keep=None):
     sc = scratch(dev, lib.hc_bucket_scratch_bytes(n, world), "bucket")
     if keep is not None:
         keep = keep.contiguous()
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_bucket_by_owner", dev):
         check(lib.hc_bucket_by_owner(ptr(ids), ptr(keep), n, world, ptr(counts), ptr(perm),
                                      ptr(bucketed), ptr(sc), stream_of(dev)), "hc_bucket_by_owner")
-    _called()
+    _called(3)
     return counts, perm, bucketed
 
 
@@ -470,7 +534,7 @@ def unpermute_rows(src, perm, flags, dst, hit_out=None):
     F = 0 if src is None else src.shape[1]
     if flags is not None:
         flags = flags.contiguous()
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_unpermute_rows", dev):
         check(lib.hc_unpermute_rows(ptr(src), HC_F32 if src is None else dtype_code(src),
                                     0 if src is None else (src.stride(0) if n > 1 else F), F,
                                     ptr(i64c(perm)), ptr(flags), n, ptr(dst),
@@ -488,7 +552,7 @@ def owner_lookup(map_t, ids, table, rows_out=None):
     F = table.shape[1]
     if rows_out is None:
         rows_out = torch.empty((n, F), dtype=table.dtype, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("hc_owner_lookup", dev):
         check(lib.hc_owner_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, ptr(table),
                                   dtype_code(table), table.shape[0],
                                   table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows_out),
