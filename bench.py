@@ -322,53 +322,22 @@ def run_ours(args):
 
 
 def large_block_roofline(device, peak, measured):
-    """The same aggregation kernels on a block larger than L2 (fp16 dim 128): 2 M destination
-    rows x 10 neighbours drawn from 16 M source rows (4 GB of rows)."""
-    import hiscache_backend as hb
-    n_src, n_dst, deg, F = 16_000_000, 2_000_000, 10, 128
-    g = torch.Generator(device=device)
-    g.manual_seed(1)
-    x = torch.randn((n_src, F), device=device, dtype=torch.float16)
-    idx = torch.randint(0, n_src, (n_dst * deg,), generator=g, device=device)
-    ptr = torch.arange(0, n_dst * deg + 1, deg, device=device)
+    """The same aggregation kernels on blocks larger than L2 (history-cache_b200/kernel_bench.py):
+    forward fp16 dim 128, 2 M destination rows x 10 neighbours from 16 M source rows; backward
+    fp32 dim 256, 1 M rows x 10 neighbours into 4 M source rows."""
+    import kernel_bench as kb
     res = {}
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-    for _ in range(3):
-        out = hb.aggr_forward(x, ptr, idx, n_dst, force_grad=False)
-    torch.cuda.synchronize()
-    reps = 10
-    ev[0].record()
-    for _ in range(reps):
-        out = hb.aggr_forward(x, ptr, idx, n_dst, force_grad=False)
-    ev[1].record()
-    torch.cuda.synchronize()
-    ms = ev[0].elapsed_time(ev[1]) / reps
-    byts = n_dst * deg * F * 2 + n_dst * F * 4 + 8 * (n_dst + 1 + n_dst * deg)
+    ms, byts = kb.bench_fwd(2_000_000, 10, 16_000_000, 128, torch.float16, 10, dev=device)
     res["fwd"] = {"achieved": round(byts / ms / 1e6, 1), "frac": round(byts / ms / 1e6 / peak, 4),
-                  "ms": round(ms, 4), "bytes": byts}
-    # backward: fp32 grads scattered into fp32 grad_input of a 4 M-row source set
-    n_src_b = 4_000_000
-    xb = torch.zeros((n_src_b, F), device=device, dtype=torch.float32, requires_grad=True)
-    idxb = torch.randint(0, n_src_b, (n_dst * deg,), generator=g, device=device)
-    go = torch.randn((n_dst, F), device=device)
-    del x, out
-    o = hb.aggr_forward(xb, ptr, idxb, n_dst)
-    for _ in range(2):
-        o.backward(go, retain_graph=True)
-    torch.cuda.synchronize()
-    xb.grad = None
-    ev[0].record()
-    for _ in range(reps):
-        o.backward(go, retain_graph=True)
-    ev[1].record()
-    torch.cuda.synchronize()
-    ms = ev[0].elapsed_time(ev[1]) / reps
-    byts = n_dst * F * 4 + n_dst * deg * F * 4 + n_src_b * F * 4 + 8 * (n_dst + 1 + n_dst * deg)
+                  "ms": round(ms, 4), "bytes": byts, "shape": "2M dst x 10 nbrs, 16M src rows, fp16 F=128"}
+    torch.cuda.empty_cache()
+    ms, byts = kb.bench_bwd(1_000_000, 10, 4_000_000, 256, 10, dev=device)
     res["bwd"] = {"achieved": round(byts / ms / 1e6, 1), "frac": round(byts / ms / 1e6 / peak, 4),
-                  "ms": round(ms, 4), "bytes": byts,
-                  "note": "includes the zero-fill of grad_input and torch's gradient accumulation"}
+                  "ms": round(ms, 4), "bytes": byts, "shape": "1M dst x 10 nbrs, 4M src rows, fp32 F=256",
+                  "note": "includes the zero-fill of grad_input and the fused row score"}
+    torch.cuda.empty_cache()
     res.update({"bound": "hbm", "peak": peak, "peak_source": "measured" if measured else "fallback",
-                "unit": "GB/s", "shape": "2M dst x 10 nbrs, 16M (fwd) / 4M (bwd) src rows, F=128"})
+                "unit": "GB/s"})
     return res
 
 

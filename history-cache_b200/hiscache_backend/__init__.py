@@ -34,7 +34,7 @@ __all__ = [
     "aggr_forward", "score_rows", "select_threshold", "cache_admit", "evict_stale",
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
     "unpermute_rows", "owner_lookup", "mix64", "launch_count", "ScoreSink", "KernelTimer",
-    "set_kernel_timer",
+    "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd",
 ]
 
 _launches = 0
@@ -246,6 +246,39 @@ def aggr_forward(input, ptr, idx, num_node=0, *, history_map=None, history_buffe
     if force_grad and not out.requires_grad:
         out.requires_grad_(True)
     return out
+
+
+class PreparedAggr:
+    """A filled hc_aggr_args plus references that keep its tensors alive."""
+
+    def __init__(self, args, keep, dev, tag):
+        self.args, self.keep, self.dev, self.tag = args, keep, dev, tag
+
+
+def prepare_aggr(input, ptr, idx, num_node, *, history_map=None, history_buffer=None,
+                 indexed=False, edge_value=None, src_map=None, src_alt=None):
+    """Descriptor for run_aggr_fwd / run_aggr_bwd: the operators without autograd."""
+    dev = require_cuda(input, ptr, idx, edge_value, history_map, history_buffer, src_map, src_alt)
+    a = _aggr_args(input, ptr, idx, int(num_node), edge_value, history_map, history_buffer, indexed,
+                   src_map, src_alt)
+    return PreparedAggr(a, (input, ptr, idx, edge_value, history_map, history_buffer, src_map, src_alt),
+                        dev, _tag("", input))
+
+
+def run_aggr_fwd(p: PreparedAggr, out):
+    with torch.cuda.device(p.dev), _span("hc_aggr_fwd" + p.tag, p.dev):
+        check(lib.hc_aggr_fwd(C.byref(p.args), ptr(out), stream_of(p.dev)), "hc_aggr_fwd")
+    _called()
+    return out
+
+
+def run_aggr_bwd(p: PreparedAggr, grad_out, grad_input=None, grad_history=None, edge_grad=None,
+                 score=None, score_kind=HC_SCORE_L2, zero=True):
+    with torch.cuda.device(p.dev), _span("hc_aggr_bwd" + p.tag, p.dev):
+        check(lib.hc_aggr_bwd(C.byref(p.args), ptr(grad_out), ptr(grad_input), 1 if zero else 0,
+                              ptr(grad_history), ptr(edge_grad), ptr(score), score_kind,
+                              stream_of(p.dev)), "hc_aggr_bwd")
+    _called()
 
 
 def aggr_forward_history(input, ptr, idx, history_map, history_buffer, history_size, num_node):

@@ -1,0 +1,120 @@
+"""Micro-benchmark of the libhiscache_b200 kernels on synthetic blocks.
+
+    python history-cache_b200/kernel_bench.py --op fwd --dst 2000000 --deg 10 --src 16000000 \
+        --feat 128 --dtype f16 --reps 10
+
+Prints one JSON line per run: achieved GB/s computed from the ALGORITHMIC bytes of the
+operation (rows gathered counted once per edge, outputs once, index arrays once) and the
+CUDA-event time per launch.  Inputs larger than the 126 MB L2 make the figure a DRAM figure.
+This is also the command the ncu captures under profiles/ were taken with.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import torch  # noqa: E402
+
+import hiscache_backend as hb  # noqa: E402
+
+
+def time_launches(fn, reps, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def block(n_dst, deg, n_src, dev, seed=1):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    idx = torch.randint(0, n_src, (n_dst * deg,), generator=g, device=dev)
+    ptr = torch.arange(0, n_dst * deg + 1, deg, device=dev)
+    return ptr, idx
+
+
+def bench_fwd(n_dst, deg, n_src, feat, dtype, reps, hit_rate=0.0, dev="cuda:0"):
+    """Aggregation forward (mean).  bytes = E_m*F*s + N_h*F*s + N_d*F*4 + 8*(N_d+1+E_m) + 8*N_d[hmap]."""
+    es = 2 if dtype == torch.float16 else 4
+    x = torch.randn((n_src, feat), device=dev, dtype=torch.float32).to(dtype)
+    ptr, idx = block(n_dst, deg, n_src, dev)
+    hmap = table = None
+    n_hit = 0
+    if hit_rate > 0:
+        cap = max(1, n_dst // 4)
+        hit = torch.rand(n_dst, device=dev) < hit_rate
+        hmap = torch.where(hit, torch.randint(0, cap, (n_dst,), device=dev), -1)
+        table = torch.randn((cap, feat), device=dev).to(dtype)
+        n_hit = int(hit.sum())
+    a = hb.prepare_aggr(x, ptr, idx, n_dst, history_map=hmap, history_buffer=table, indexed=True)
+    out = torch.empty((n_dst, feat), device=dev)
+    ms = time_launches(lambda: hb.run_aggr_fwd(a, out), reps)
+    e_m = (n_dst - n_hit) * deg
+    byts = e_m * feat * es + n_hit * feat * es + n_dst * feat * 4 + 8 * (n_dst + 1 + e_m) + (8 * n_dst if hmap is not None else 0)
+    return ms, byts
+
+
+def bench_bwd(n_dst, deg, n_src, feat, reps, dev="cuda:0", with_score=True):
+    """Aggregation backward (scatter) incl. the zero-fill of grad_input and the fused score.
+    bytes = N_d*F*4 + E*F*4 + N_s*F*4 + 8*(N_d+1+E) + 4*N_d[score]."""
+    x = torch.empty((n_src, feat), device=dev)
+    ptr, idx = block(n_dst, deg, n_src, dev)
+    go = torch.randn((n_dst, feat), device=dev)
+    gi = torch.empty((n_src, feat), device=dev)
+    score = torch.empty(n_dst, device=dev) if with_score else None
+    a = hb.prepare_aggr(x, ptr, idx, n_dst)
+    ms = time_launches(lambda: hb.run_aggr_bwd(a, go, gi, score=score), reps)
+    e = n_dst * deg
+    byts = n_dst * feat * 4 + e * feat * 4 + n_src * feat * 4 + 8 * (n_dst + 1 + e) + (4 * n_dst if with_score else 0)
+    return ms, byts
+
+
+def bench_load(n, n_table, feat, dtype, reps, host, cache_frac=0.0, dev="cuda:0"):
+    """batch.x assembly.  bytes = rows read (F*s each) + rows written (F*s) + 8*n ids (+ 8*n map)."""
+    es = 2 if dtype == torch.float16 else 4
+    if host:
+        table = torch.empty((n_table, feat), dtype=dtype, pin_memory=True)
+        table.normal_()
+    else:
+        table = torch.randn((n_table, feat), device=dev).to(dtype)
+    ids = torch.randint(0, n_table, (n,), device=dev)
+    ms = time_launches(lambda: hb.load_rows(table, None, ids, None, None), reps)
+    return ms, n * feat * es * 2 + 8 * n
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "load"])
+    ap.add_argument("--dst", type=int, default=2_000_000)
+    ap.add_argument("--deg", type=int, default=10)
+    ap.add_argument("--src", type=int, default=16_000_000)
+    ap.add_argument("--feat", type=int, default=128)
+    ap.add_argument("--dtype", default="f16", choices=["f16", "f32"])
+    ap.add_argument("--hit-rate", type=float, default=0.0)
+    ap.add_argument("--host", action="store_true", help="load: table in pinned host memory")
+    ap.add_argument("--reps", type=int, default=10)
+    args = ap.parse_args()
+    dt = torch.float16 if args.dtype == "f16" else torch.float32
+    if args.op == "fwd":
+        ms, byts = bench_fwd(args.dst, args.deg, args.src, args.feat, dt, args.reps, args.hit_rate)
+    elif args.op == "bwd":
+        ms, byts = bench_bwd(args.dst, args.deg, args.src, args.feat, args.reps)
+    else:
+        ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host)
+    print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
+                      "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate,
+                      "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1)}))
+
+
+if __name__ == "__main__":
+    main()
