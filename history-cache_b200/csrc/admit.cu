@@ -511,3 +511,64 @@ extern "C" int hc_evict_by_score(const int64_t* sub_to_history, const float* sco
   HC_LAUNCH_OK();
   return 0;
 }
+
+
+// ---------------------------------------------------------------------------
+// Ring admission with built-in scratch (no allocation by anybody)
+// ---------------------------------------------------------------------------
+// hc_record_history needs a few KB of device scratch that the caller allocates.  Some
+// callers have nothing to allocate with: a plain-C, cgo or JNI host that was only handed the
+// input and output buffers and holds no handle to the framework's device allocator, or a
+// training loop whose memory is entirely owned by a caching allocator and in which a raw
+// cudaMalloc / cudaFree would stall the device.  For them the scratch lives in this
+// file-scope array, which every GPU that loads the library carries until the process exits.
+namespace hc {
+
+constexpr int64_t kNoAllocMaxRows = 1 << 20;  // HC_NOALLOC_MAX_ROWS
+constexpr int64_t kNoAllocBytes = (8 + 2 * (kNoAllocMaxRows / kAdmitBlock)) * (int64_t)sizeof(int64_t);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+// Device address of g_noalloc_scratch per device ordinal.  In host code the array's name is
+// only a handle for the runtime, never an address a kernel may be given; the address comes
+// from cudaGetSymbolAddress, asked once per device with that device current.
+static void* g_noalloc_addr[kNoAllocMaxDevices];
+
+static int noalloc_scratch(void** out) {
+  int dev = -1;
+  HC_CUDA(cudaGetDevice(&dev));
+  HC_REQUIRE(dev >= 0 && dev < kNoAllocMaxDevices, HC_ERR_SIZE);
+  void* p = __atomic_load_n(&g_noalloc_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    HC_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    HC_REQUIRE(p != nullptr, HC_ERR_NULL);
+    __atomic_store_n(&g_noalloc_addr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return 0;
+}
+
+}  // namespace hc
+
+extern "C" int64_t hc_noalloc_max_rows(void) { return hc::kNoAllocMaxRows; }
+
+extern "C" int hc_record_history_noalloc(const float* buffer_new, int64_t new_stride, int64_t n,
+                                         void* buffer_all, int32_t table_dtype, int64_t capacity,
+                                         int32_t history_size, const uint8_t* used_mask,
+                                         const int64_t* sub_to_full,
+                                         const int64_t* sub_to_history, int64_t* history_to_full,
+                                         int64_t* full_to_history, int64_t* header,
+                                         const float* score, const float* thres,
+                                         int64_t* checkin_iter, int64_t glb_iter,
+                                         int64_t* n_admitted, void* stream) {
+  if (n > hc::kNoAllocMaxRows) return -HC_ERR_LIMIT;
+  void* scratch = nullptr;
+  const int rc = hc::noalloc_scratch(&scratch);
+  if (rc != 0) return rc;
+  // every scratch word that is read was written earlier in the same call, so the contents
+  // left by the previous call need no clearing
+  return hc_record_history(buffer_new, new_stride, n, buffer_all, table_dtype, capacity,
+                           history_size, used_mask, sub_to_full, sub_to_history, history_to_full,
+                           full_to_history, header, score, thres, checkin_iter, glb_iter,
+                           n_admitted, scratch, stream);
+}

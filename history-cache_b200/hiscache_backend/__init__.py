@@ -31,7 +31,7 @@ from ._capi import (HC_F16, HC_F32, HC_SCORE_L1, HC_SCORE_L2, AggrArgs, check, d
 __all__ = [
     "record_history", "count_history_reconstruct", "count_num", "get_graph_structure_score",
     "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
-    "aggr_forward", "score_rows", "select_threshold", "cache_admit", "evict_stale",
+    "aggr_forward", "score_rows", "record_history_noalloc", "select_threshold", "cache_admit", "evict_stale",
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
     "unpermute_rows", "owner_lookup", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd",
@@ -378,6 +378,32 @@ def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_histor
             ptr(full_to_history), ptr(header), ptr(score.contiguous().float()), ptr(thres),
             ptr(checkin_iter), int(glb_iter), ptr(n_admitted), ptr(sc), stream_of(dev)),
             "hc_record_history")
+    _called(4)
+
+
+def record_history_noalloc(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_history,
+                           history_to_full, full_to_history, header, score, thres, checkin_iter,
+                           glb_iter, n_admitted=None):
+    """record_history through the entry point that carries its own scratch
+    (hc_record_history_noalloc): for hosts that cannot allocate device memory themselves.
+    This wrapper allocates nothing either; every argument must already be a contiguous CUDA
+    tensor of the right dtype (fp32 rows / scores / thres, int64 maps, bool mask).  At most
+    hc_noalloc_max_rows() candidate rows; calls on one device must not overlap on the GPU."""
+    dev = require_cuda(buffer_new, buffer_all, sub_to_full, sub_to_history, history_to_full,
+                       full_to_history, header, score, thres, checkin_iter)
+    n, hs = buffer_new.shape
+    for t in (buffer_new, buffer_all, sub_to_full, sub_to_history, history_to_full, full_to_history,
+              header, score, thres, checkin_iter):
+        if not t.is_contiguous():
+            raise RuntimeError("record_history_noalloc: arguments must be contiguous")
+    if buffer_new.dtype != torch.float32 or score.dtype != torch.float32 or thres.dtype != torch.float32:
+        raise TypeError("record_history_noalloc: rows, score and thres must be float32")
+    with torch.cuda.device(dev):
+        check(lib.hc_record_history_noalloc(
+            ptr(buffer_new), hs, n, ptr(buffer_all), dtype_code(buffer_all), buffer_all.shape[0], hs,
+            ptr(used_mask), ptr(sub_to_full), ptr(sub_to_history), ptr(history_to_full),
+            ptr(full_to_history), ptr(header), ptr(score), ptr(thres), ptr(checkin_iter),
+            int(glb_iter), ptr(n_admitted), stream_of(dev)), "hc_record_history_noalloc")
     _called(4)
 
 

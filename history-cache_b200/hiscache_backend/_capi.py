@@ -52,6 +52,9 @@ _SIGS = {
     "hc_admit_scratch_bytes": (i64, [i64]),
     "hc_record_history": (C.c_int, [vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp, vp, vp, vp,
                                     vp, vp, i64, vp, vp, vp]),
+    "hc_noalloc_max_rows": (i64, []),
+    "hc_record_history_noalloc": (C.c_int, [vp, i64, i64, vp, i32, i64, i32, vp, vp, vp, vp, vp, vp,
+                                            vp, vp, vp, i64, vp, vp]),
     "hc_cache_admit": (C.c_int, [vp, i64, i64, vp, i32, i32, i32, i64, vp, vp, vp, vp, vp, i64,
                                  vp, vp, i64, vp, i32, vp, vp, vp]),
     "hc_evict_stale": (C.c_int, [vp, vp, vp, i64, i64, i64, vp]),

@@ -48,6 +48,7 @@ extern "C" {
 #define HC_ERR_ALIGN 4     /* pointer not aligned to its element type         */
 #define HC_ERR_UNSUPPORTED 5 /* combination of options not implemented        */
 #define HC_ERR_STRUCT 6    /* args->struct_size does not match this build     */
+#define HC_ERR_LIMIT 7     /* more rows than a fixed-scratch entry point takes */
 
 /* score kinds */
 #define HC_SCORE_L2 0 /* sqrt(sum x^2): HistoryCache.update_history, history_cache.py:205 */
@@ -191,6 +192,39 @@ int hc_record_history(const float* buffer_new, int64_t new_stride, int64_t n,
                       int64_t* header, const float* score, const float* thres,
                       int64_t* checkin_iter, int64_t glb_iter,
                       int64_t* n_admitted, void* scratch, void* stream);
+
+/*
+ * hc_record_history for callers that cannot allocate device memory.  (No
+ * counterpart in the reference, whose op allocates nothing because its kernel
+ * takes slots with an atomic counter.)  Who needs it: a plain-C / cgo / JNI
+ * host that only holds the buffers it was handed and has no way to reach the
+ * framework's device allocator for the scratch argument, and loops whose
+ * device memory is wholly owned by a caching allocator, where a raw
+ * cudaMalloc / cudaFree would fail or stall the device.  Same arguments and
+ * result as hc_record_history minus `scratch`: the scratch is a 16 KB array
+ * inside the library image (each GPU that loads the library holds it until
+ * exit).  Limits and rules:
+ *   - n <= HC_NOALLOC_MAX_ROWS (hc_noalloc_max_rows()); more returns
+ *     -HC_ERR_LIMIT and nothing is launched;
+ *   - calls no cudaMalloc / cudaFree / allocating routine;
+ *   - the first call on a device looks the array's device address up
+ *     (cudaGetSymbolAddress, with the caller's current device) and remembers
+ *     it; make that first call with the right device current and before any
+ *     stream capture begins;
+ *   - all calls on one device share the array: two calls whose kernels can
+ *     overlap on the GPU (different streams) race; serialise them.  Nothing
+ *     in the array needs clearing between calls.
+ */
+#define HC_NOALLOC_MAX_ROWS (1 << 20)
+int64_t hc_noalloc_max_rows(void);
+int hc_record_history_noalloc(const float* buffer_new, int64_t new_stride, int64_t n,
+                              void* buffer_all, int32_t table_dtype, int64_t capacity,
+                              int32_t history_size, const uint8_t* used_mask,
+                              const int64_t* sub_to_full, const int64_t* sub_to_history,
+                              int64_t* history_to_full, int64_t* full_to_history,
+                              int64_t* header, const float* score, const float* thres,
+                              int64_t* checkin_iter, int64_t glb_iter,
+                              int64_t* n_admitted, void* stream);
 
 /*
  * Admission of the unified-buffer cache path; restatement of
