@@ -1,3 +1,179 @@
-"""placeholder, replaced below"""
-class MultiGpuHistoryTrainer:  # noqa
-    pass
+"""Data-parallel trainer, one process per GPU (torchrun), NCCL over NVLink / NVSwitch.
+
+The reference drives N GPUs from one Python thread: N model replicas, N private caches, one
+`torch.cuda.nccl.all_reduce` per parameter, divide by N (hiscache/multi_gpu_history_trainer.py:
+60-133).  Here each rank owns one replica and one shard of a node-partitioned embedding
+history (hiscache/sharded.py); gradients travel in one flat bucket.
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+import hiscache_backend as hb
+
+from .feature_store import HostFeatureStore
+from .history_cache import HistoryCache
+from .history_model import get_model
+from .sampler import get_loader
+from .sharded import ShardedHistoryTable
+from .util import cfg_get, log
+
+
+class ShardedHistoryCache(HistoryCache):
+    """HistoryCache whose embedding history lives in a ShardedHistoryTable; the raw-feature
+    cache stays private to the GPU, as in the reference."""
+
+    def __init__(self, uvm=None, config=None, mode=None, device_id=-1, *, group=None,
+                 embed_capacity=None, ops=None, **kw):
+        super().__init__(uvm=uvm, config=config, mode=mode, device_id=device_id, **kw)
+        cap = embed_capacity if embed_capacity is not None else max(
+            1024, int(cfg_get(config, "history.shard_capacity", 1 << 20)))
+        self.table = ShardedHistoryTable(self.total_num_node, self.hidden_channels, cap,
+                                         dtype=self.storage_dtype, device=self.device, group=group,
+                                         ops=ops, staleness=self.staleness_thres)
+        self._rows = None
+
+    @property
+    def embedding_table(self):
+        return self._rows
+
+    @property
+    def header(self):
+        return int(self.table.header.item())
+
+    def lookup_and_load(self, batch, num_layer=None, feature_cache_only=False):
+        if feature_cache_only or "history" not in self.feat_mode:
+            return super().lookup_and_load(batch, num_layer, feature_cache_only)
+        if num_layer is None:
+            num_layer = self.num_layers_all
+        n1 = int(batch.num_node_in_layer[1])
+        self.sub2embed, self._rows = self.table.lookup(batch.sub_to_full[:n1])
+        self._cached_embedding = None
+        self.sub2feat = hb.map_lookup(self.full2embed, batch.sub_to_full, offset=self.total_num_node)
+        self.used_masks = hb.count_history_reconstruct(batch.ptr, batch.idx, self.sub2embed,
+                                                       batch.sub_to_full.shape[0], batch.y.shape[0],
+                                                       num_layer)
+        self.glb_iter += 1
+        batch.x = hb.load_rows(self.uvm.buffer, self.buffer.view(-1, self.in_channels),
+                               batch.sub_to_full, self.sub2feat, self.used_masks[0],
+                               out_dtype=self.uvm.buffer.dtype, stats=self.load_stats)
+        return None
+
+    @property
+    def cached_embedding(self):
+        if self._cached_embedding is None and self.sub2embed is not None and self._rows is not None:
+            self._cached_embedding = hb.gather_rows(self._rows, self.sub2embed, zero_missing=True)
+        return self._cached_embedding
+
+    @torch.no_grad()
+    def update_history(self, batch, glb_iter):
+        if "history" not in self.feat_mode or self.staleness_thres == 0 or glb_iter < self.start_history:
+            return
+        n = int(batch.num_node_in_layer[1])
+        prod = self.produced_embedding
+        if prod is None:
+            raise RuntimeError("produced embedding is None")
+        sink = self._sink
+        if self.method == "grad" and sink is not None and sink.fresh and sink.tensor.shape[0] == n:
+            score = sink.tensor
+        elif self.method == "grad" and prod.grad is not None:
+            score = hb.score_rows(prod.grad, hb.HC_SCORE_L2)
+        else:
+            score = torch.randn([n], device=self.device)
+        self._sink = None
+        prod.grad = None
+        hb.select_threshold(score, self.rate, out=self._thres)
+        mask = (score < self._thres) & (self.sub2embed == -1)
+        self.table.evict_stale(glb_iter)
+        self.table.admit(batch.sub_to_full[:n], prod.detach(), mask, glb_iter)
+        self.produced_embedding = None
+
+
+class MultiGpuHistoryTrainer:
+
+    def __init__(self, config, graph=None, uvm=None, loader=None, storage_dtype=torch.float32,
+                 feature_dtype=torch.float32, seed=0, group=None):
+        if not dist.is_initialized():
+            raise RuntimeError("MultiGpuHistoryTrainer runs one process per GPU: launch with "
+                               "torchrun and call torch.distributed.init_process_group first")
+        self.config, self.group = config, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.num_device = self.world
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.loader = loader if loader is not None else get_loader(config.dl, graph=graph, seed=seed,
+                                                                   rank=self.rank, world=self.world)
+        if uvm is None:
+            g = self.loader.graph
+            uvm = HostFeatureStore.synthetic(g.num_nodes, config.dl.dataset.feature_dim,
+                                             dtype=feature_dtype, seed=seed, device=self.device)
+        self.uvm = uvm
+        cfg = config
+        cfg.dl.device = str(self.device)
+        self.table = ShardedHistoryCache(uvm=self.uvm, config=cfg, mode=config.dl.loading.feat_mode,
+                                         device_id=self.device.index, group=group,
+                                         total_num_node=self.loader.graph.num_nodes,
+                                         sorted_indices=self.loader.graph.sorted_indices,
+                                         storage_dtype=storage_dtype)
+        self.tables = [self.table]
+        torch.manual_seed(seed)      # same initial weights on every rank
+        self.model = get_model(config, self.table).to(self.device)
+        self.models = [self.model]
+        self.num_layer = len(self.model.convs)
+        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3))
+        self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
+        self.loss_fn = F.nll_loss
+        self.glb_iter = 0
+        # one flat gradient bucket: every parameter's .grad is a view into it
+        params = [p for p in self.model.parameters() if p.requires_grad]
+        self.flat_grad = torch.zeros(sum(p.numel() for p in params), device=self.device)
+        off = 0
+        for p in params:
+            p.grad = self.flat_grad[off:off + p.numel()].view_as(p)
+            off += p.numel()
+
+    # the five phases of the reference's step (multi_gpu_history_trainer.py:60-133)
+    def load(self, batch):
+        self.flat_grad.zero_()
+        self.table.lookup_and_load(batch, self.num_layer)
+
+    def run_forward(self, batch):
+        return self.model(batch)
+
+    def run_backward(self, batch, out):
+        loss = self.loss_fn(out, batch.y)
+        loss.backward()
+        return loss
+
+    def update_grad(self):
+        dist.all_reduce(self.flat_grad, group=self.group)
+        self.flat_grad.div_(self.world)
+        self.optimizer.step()
+        self.scheduler.step()
+
+    def update_history(self, batch):
+        self.table.update_history(batch, self.glb_iter)
+        self.glb_iter += 1
+
+    def train_step(self, batch):
+        self.load(batch)
+        out = self.run_forward(batch)
+        loss = self.run_backward(batch, out)
+        self.update_grad()
+        self.update_history(batch)
+        return loss
+
+    def cxg_train_epoch(self):
+        self.model.train()
+        t0 = time.time()
+        for batch in self.loader.train_loader:
+            self.train_step(batch)
+        torch.cuda.synchronize()
+        log.info(f"epoch time: {time.time() - t0}")
+
+    def train(self):
+        for _ in range(self.config.train.train.num_epochs):
+            self.cxg_train_epoch()

@@ -1,0 +1,120 @@
+"""Host logic of the node-partitioned history table with two CPU ranks over gloo.
+
+Each rank runs hiscache.sharded.ShardedHistoryTable with the CPU stand-in operators and
+compares, step by step, against one logical table that receives every rank's admissions in
+(rank, row) order (last copy of an id wins; ids already present are skipped; entries older
+than the staleness limit are dropped before a step's admissions)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+
+
+def _inputs(step, rank, N, n, hidden):
+    rng = np.random.default_rng(1000 * step + rank)
+    # a small id range makes ranks collide on ids
+    ids = rng.choice(N, size=n, replace=False).astype(np.int64)
+    rows = rng.standard_normal((n, hidden)).astype(np.float32)
+    mask = rng.random(n) < 0.5
+    return ids, rows, mask
+
+
+def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"):
+    for p in (os.path.join(ROOT, "history-cache_b200"), os.path.join(ROOT, "oracle"), HERE):
+        sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if backend == "nccl":
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        dev, ops = torch.device("cuda", rank), None     # None = the CUDA operator module
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import _cpu_ops
+        dev, ops = torch.device("cpu"), _cpu_ops
+    try:
+        from hiscache.sharded import ShardedHistoryTable
+        table = ShardedHistoryTable(N, hidden, capacity=4096, device=dev, ops=ops,
+                                    staleness=staleness)
+        assert table.world == world and table.rank == rank
+        logical = {}   # id -> (row, checkin)
+        for t in range(steps):
+            ids, rows, mask = _inputs(t, rank, N, n, hidden)
+            hit_map, got = table.lookup(torch.from_numpy(ids).to(dev))
+            hit_map, got = hit_map.cpu().numpy(), got.cpu()
+            want_hit = np.array([i in logical for i in ids])
+            assert np.array_equal(hit_map != -1, want_hit), f"rank {rank} step {t}: hit sets differ"
+            for r in np.nonzero(want_hit)[0]:
+                assert np.array_equal(got[hit_map[r]].numpy(), logical[int(ids[r])][0])
+            table.evict_stale(t)
+            table.admit(torch.from_numpy(ids).to(dev), torch.from_numpy(rows).to(dev),
+                        torch.from_numpy(mask).to(dev), t)
+            # the logical table, same step for all ranks
+            for k in [k for k, v in logical.items() if v[1] <= t - staleness]:
+                del logical[k]
+            before = set(logical)
+            for r in range(world):
+                ids_r, rows_r, mask_r = _inputs(t, r, N, n, hidden)
+                for j in np.nonzero(mask_r)[0]:
+                    if int(ids_r[j]) not in before:
+                        logical[int(ids_r[j])] = (rows_r[j], t)
+            # owner-side state equals the owned part of the logical table
+            import hc_oracle as O
+            mine = {k for k in logical if int(O.owner([k], world)[0]) == rank}
+            have = set(np.nonzero(table.full_to_slot.cpu().numpy() != -1)[0].tolist())
+            assert have == mine, f"rank {rank} step {t}: owned set differs"
+        q.put((rank, "ok", len(logical)))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "fail", traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_sharded_table_two_cpu_ranks(world, oracle):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, status, info in res:
+        assert status == "ok", f"rank {rank}:\n{info}"
+    assert res[0][2] == res[1][2] > 0
+
+
+def test_single_rank_equals_plain_ring(oracle):
+    """world == 1 takes no collective and must behave exactly like the ring admission."""
+    sys.path.insert(0, HERE)
+    import _cpu_ops
+    from hiscache.sharded import ShardedHistoryTable
+    N, n, hidden = 2000, 300, 4
+    table = ShardedHistoryTable(N, hidden, capacity=256, device="cpu", ops=_cpu_ops, staleness=0)
+    f2h = np.full(N, -1, dtype=np.int64)
+    h2f = np.full(256, -1, dtype=np.int64)
+    chk = np.full(256, -1, dtype=np.int64)
+    buf = np.zeros((256, hidden), dtype=np.float32)
+    hdr = np.zeros(1, dtype=np.int64)
+    for t in range(4):
+        ids, rows, mask = _inputs(t, 0, N, n, hidden)
+        hit_map, got = table.lookup(torch.from_numpy(ids))
+        assert np.array_equal(hit_map.numpy() != -1, f2h[ids] != -1)
+        table.admit(torch.from_numpy(ids), torch.from_numpy(rows), torch.from_numpy(mask), t)
+        sel = np.nonzero(mask)[0]
+        oracle.record_history(rows[sel], buf, None, ids[sel], f2h[ids[sel]].copy(), h2f, f2h, hdr,
+                              np.zeros(len(sel), np.float32), 0.0, chk, t)
+        assert np.array_equal(table.full_to_slot.numpy(), f2h)
+        assert np.array_equal(table.slot_to_full.numpy(), h2f)
+        assert np.array_equal(table.buffer.numpy(), buf)
+        assert int(table.header[0]) == int(hdr[0])
