@@ -43,14 +43,26 @@ __device__ __forceinline__ void copy_history_row(const hc_aggr_args& a, int64_t 
 //   G   lanes that share one source row (G < 32: 32/G edges per request)
 //   V   16-byte vectors per lane
 //   EV  weighted sum with edge values instead of mean
+//   IDX32  source ids fit 31 bits (n_src < 2^31): they travel in one shuffle
 // ---------------------------------------------------------------------------
-template <typename T, int G, int V, bool EV>
-__global__ void __launch_bounds__(256)
+// Tuning, measured on B200 with 2 M x 10-neighbour blocks larger than L2: throughput follows
+// the bytes in flight per SM (resident warps x U x 16 B per lane).  Six independent loads
+// per lane cover a sampled row (<= 12 edges of 256 B, <= 6 of 512 B) in one batch, and 48
+// registers keep five blocks resident; more unrolling or forcing more blocks spills and
+// loses (U=4: 4.3 TB/s, U=6 @5 blocks: 5.1 TB/s, U=8: 3.8 TB/s for fp16 dim-128 rows).
+#ifndef HC_FWD_MINBLOCKS
+#define HC_FWD_MINBLOCKS 5
+#endif
+#ifndef HC_FWD_U1
+#define HC_FWD_U1 6
+#endif
+template <typename T, int G, int V, bool EV, bool IDX32>
+__global__ void __launch_bounds__(256, HC_FWD_MINBLOCKS)
     aggr_fwd_vec_kernel(const hc_aggr_args a, float* __restrict__ out, const int nvec,
                         const int h_vec) {
   constexpr int EL = Vec16<T>::kElems;
   constexpr int EPW = kWarp / G;
-  constexpr int U = V <= 2 ? 4 : (V <= 4 ? 2 : 1);
+  constexpr int U = V == 1 ? HC_FWD_U1 : (V == 2 ? 4 : (V <= 4 ? 2 : 1));
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= a.num_node) return;
@@ -91,7 +103,7 @@ __global__ void __launch_bounds__(256)
       for (int u = 0; u < U; ++u) {
         const int jj = j + u * EPW + sub;
         const int from = jj & 31;
-        const int64_t s = shfl64(my_s, from);
+        const int64_t s = IDX32 ? (int64_t)__shfl_sync(kFull, (int)my_s, from) : shfl64(my_s, from);
         const int64_t al = has_map ? shfl64(my_alt, from) : -1;
         w[u] = EV ? __shfl_sync(kFull, my_w, from) : 1.f;
         const bool ok = jj < cnt;
@@ -104,14 +116,21 @@ __global__ void __launch_bounds__(256)
         }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u)
+      for (int u = 0; u < U; ++u) {
+        if (j + u * EPW < cnt) {  // warp-uniform: slots past the end of the chunk do nothing
 #pragma unroll
-        for (int k = 0; k < V; ++k) {
-          float f[EL];
-          Vec16<T>::unpack(buf[u][k], f);
+          for (int k = 0; k < V; ++k) {
+            if (EV) {
+              float f[EL];
+              Vec16<T>::unpack(buf[u][k], f);
 #pragma unroll
-          for (int e = 0; e < EL; ++e) acc[k][e] = EV ? fmaf(w[u], f[e], acc[k][e]) : acc[k][e] + f[e];
+              for (int e = 0; e < EL; ++e) acc[k][e] = fmaf(w[u], f[e], acc[k][e]);
+            } else {
+              accumulate_vec<T>(acc[k], buf[u][k]);
+            }
+          }
         }
+      }
     }
   }
 
@@ -127,11 +146,11 @@ __global__ void __launch_bounds__(256)
 
   const int64_t deg = end - begin;
   if (!EV && deg > 0) {
-    const float d = (float)deg;
+    const float inv = __frcp_rn((float)deg);  // one correctly rounded reciprocal per row
 #pragma unroll
     for (int k = 0; k < V; ++k)
 #pragma unroll
-      for (int e = 0; e < EL; ++e) acc[k][e] = __fdiv_rn(acc[k][e], d);
+      for (int e = 0; e < EL; ++e) acc[k][e] *= inv;
   }
 #pragma unroll
   for (int k = 0; k < V; ++k) {
@@ -241,13 +260,13 @@ __global__ void __launch_bounds__(256)
   const int64_t deg = end - begin;
   if (deg == 0) return;
   if (!EV) {
-    const float d = (float)deg;
+    const float inv = __frcp_rn((float)deg);
 #pragma unroll
     for (int k = 0; k < V; ++k) {
-      g[k].x = __fdiv_rn(g[k].x, d);
-      g[k].y = __fdiv_rn(g[k].y, d);
-      g[k].z = __fdiv_rn(g[k].z, d);
-      g[k].w = __fdiv_rn(g[k].w, d);
+      g[k].x *= inv;
+      g[k].y *= inv;
+      g[k].z *= inv;
+      g[k].w *= inv;
     }
   }
   const bool has_map = a.src_map != nullptr;
@@ -399,10 +418,12 @@ static int vec_shape(int nvec, int* G, int* V) {
 template <typename T, bool EV>
 static void launch_fwd_vec(int G, int V, dim3 grid, cudaStream_t st, const hc_aggr_args& a,
                            float* out, int nvec, int h_vec) {
-#define HC_FWD_CASE(g, v)                                                              \
-  if (G == g && V == v) {                                                              \
-    aggr_fwd_vec_kernel<T, g, v, EV><<<grid, 256, 0, st>>>(a, out, nvec, h_vec);       \
-    return;                                                                            \
+  const bool idx32 = a.n_src < 0x7fffffffLL;
+#define HC_FWD_CASE(g, v)                                                                     \
+  if (G == g && V == v) {                                                                     \
+    if (idx32) aggr_fwd_vec_kernel<T, g, v, EV, true><<<grid, 256, 0, st>>>(a, out, nvec, h_vec);  \
+    else aggr_fwd_vec_kernel<T, g, v, EV, false><<<grid, 256, 0, st>>>(a, out, nvec, h_vec);  \
+    return;                                                                                   \
   }
   HC_FWD_CASE(8, 1) HC_FWD_CASE(16, 1) HC_FWD_CASE(32, 1) HC_FWD_CASE(32, 2)
   HC_FWD_CASE(32, 3) HC_FWD_CASE(32, 4) HC_FWD_CASE(32, 6) HC_FWD_CASE(32, 8)

@@ -83,6 +83,31 @@ struct Vec16<__half> {
   }
 };
 
+// acc[0..EL) += the EL elements of a 16-byte vector of T.  For fp16 this uses the
+// mixed-precision add of sm_100 (f32 += f16 in one instruction; the widening is exact, so
+// the result equals convert-then-add).
+template <typename T>
+__device__ __forceinline__ void accumulate_vec(float* acc, const uint4& v);
+template <>
+__device__ __forceinline__ void accumulate_vec<float>(float* acc, const uint4& v) {
+  acc[0] += __uint_as_float(v.x);
+  acc[1] += __uint_as_float(v.y);
+  acc[2] += __uint_as_float(v.z);
+  acc[3] += __uint_as_float(v.w);
+}
+#define HC_MIXED_ADD2(a0, a1, word)                                                   \
+  asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %2; add.f32.f16 %0, lo, %0; "             \
+      "add.f32.f16 %1, hi, %1;}"                                                      \
+      : "+f"(a0), "+f"(a1)                                                            \
+      : "r"(word))
+template <>
+__device__ __forceinline__ void accumulate_vec<__half>(float* acc, const uint4& v) {
+  HC_MIXED_ADD2(acc[0], acc[1], v.x);
+  HC_MIXED_ADD2(acc[2], acc[3], v.y);
+  HC_MIXED_ADD2(acc[4], acc[5], v.z);
+  HC_MIXED_ADD2(acc[6], acc[7], v.w);
+}
+
 // Vectorised fp32 reduction into global memory (one 16-byte transaction).
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b),
