@@ -6,6 +6,8 @@
 // masked host read followed by two more full-width passes; here one kernel
 // decides per row between the host-resident table, the raw-feature cache in
 // HBM and zeros, and writes the row once.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace hc {
@@ -144,6 +146,150 @@ __global__ void __launch_bounds__(256) load_rows_kernel(const LoadArgs a) {
       if (h) atomicAdd(a.stats, (unsigned long long)h);
       if (c) atomicAdd(a.stats + 1, (unsigned long long)c);
     }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// batch.x assembly with the rows staged through shared memory by the bulk-copy
+// engine (TMA, untiled cp.async.bulk): one copy instruction per row instead of
+// one 16-byte load per lane, one bulk store per tile of 32 rows.  Used when no
+// conversion is needed (table, cache and batch share a dtype, rows are multiples
+// of 16 bytes and the batch rows are contiguous).  Every wait is bounded; a warp
+// whose wait runs out stops using the engine and finishes with plain loads.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem),
+               "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+constexpr int kBulkWarps = 4;      // warps per block
+constexpr int kBulkTile = 32;      // rows per tile = one row per lane
+constexpr int kBulkSpin = 1 << 22; // bound of every wait loop
+
+__global__ void __launch_bounds__(kBulkWarps * 32)
+    load_rows_bulk_kernel(const LoadArgs a, const int row_bytes, const int64_t tiles) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[kBulkWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char* buf[2];
+  buf[0] = smem + (size_t)(warp * 2) * kBulkTile * row_bytes;
+  buf[1] = buf[0] + (size_t)kBulkTile * row_bytes;
+  const uint32_t bar = smem_u32(&bars[warp]);
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const int es = a.x_dtype == HC_F16 ? 2 : 4;
+  bool engine_ok = true;
+  uint32_t phase = 0;
+  unsigned long long n_host = 0, n_cache = 0;
+  int which = 0;
+  const int64_t warps_total = (int64_t)gridDim.x * kBulkWarps;
+  for (int64_t t = (int64_t)blockIdx.x * kBulkWarps + warp; t < tiles; t += warps_total) {
+    const int64_t i = t * kBulkTile + lane;
+    const bool live = i < a.n;
+    const void* src = nullptr;
+    bool load = false, from_cache = false;
+    if (live) {
+      const int64_t sf = a.sub2feat ? a.sub2feat[i] : -1;
+      const bool used = a.used == nullptr || a.used[i] != 0;
+      load = used && sf == -1;
+      if (load) {
+        const int64_t g = a.sub_to_full[i];
+        if (g >= 0 && g < a.host_rows)
+          src = reinterpret_cast<const char*>(a.host_table) + g * a.host_stride * es;
+      } else if (sf != -1) {
+        const int64_t r = sf < 0 ? sf + a.cache_rows : sf;
+        if (r >= 0 && r < a.cache_rows) src = reinterpret_cast<const char*>(a.feat_cache) + r * a.cache_stride * es;
+        from_cache = true;
+      }
+      if (a.load_mask_out) a.load_mask_out[i] = load ? 1 : 0;
+    }
+    n_host += __popc(__ballot_sync(kFull, load));
+    n_cache += __popc(__ballot_sync(kFull, from_cache));
+    const int64_t left = a.n - t * kBulkTile;
+    const int rows_here = (int)(left < kBulkTile ? left : kBulkTile);
+    char* xrow = reinterpret_cast<char*>(a.x) + i * (int64_t)row_bytes;
+    if (engine_ok) {
+      unsigned char* stage = buf[which];
+      // the store that last read this buffer must be done with it
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      const unsigned has = __ballot_sync(kFull, src != nullptr);
+      if (lane == 0 && has) mbar_expect_tx(bar, (uint32_t)__popc(has) * (uint32_t)row_bytes);
+      __syncwarp();
+      if (src) {
+        bulk_load(smem_u32(stage + (size_t)lane * row_bytes), src, (uint32_t)row_bytes, bar);
+      } else if (live) {
+        uint4* z = reinterpret_cast<uint4*>(stage + (size_t)lane * row_bytes);
+        for (int v = 0; v < row_bytes / 16; ++v) z[v] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (has) {
+        int spins = 0;
+        while (!mbar_try_wait(bar, phase)) {
+          if (++spins > kBulkSpin) { engine_ok = false; break; }
+        }
+        phase ^= 1u;
+      }
+      engine_ok = __all_sync(kFull, engine_ok);
+      if (engine_ok) {
+        // zeros written by lanes must be visible to the bulk store
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0)
+          bulk_store(reinterpret_cast<char*>(a.x) + t * kBulkTile * (int64_t)row_bytes,
+                     smem_u32(stage), (uint32_t)rows_here * (uint32_t)row_bytes);
+        which ^= 1;
+        continue;
+      }
+      // the wait ran out: finish this tile and all later ones with plain loads
+    }
+    if (live) {
+      for (int v = 0; v < row_bytes / 16; ++v)
+        reinterpret_cast<uint4*>(xrow)[v] = src ? ldg16(reinterpret_cast<const char*>(src) + 16 * v)
+                                                : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  // shared memory must outlive the stores that read it
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  if (!engine_ok) {
+    // copies issued before the wait ran out may still be landing: give them one more
+    // bounded wait before the block's shared memory is released
+    int spins = 0;
+    while (!mbar_try_wait(bar, phase ^ 1u) && ++spins < kBulkSpin) {
+    }
+  }
+  if (a.stats && lane == 0) {
+    if (n_host) atomicAdd(a.stats, n_host);
+    if (n_cache) atomicAdd(a.stats + 1, n_cache);
   }
 }
 
@@ -292,10 +438,27 @@ extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t 
   a.cache_mode = feat_cache ? move_mode(feat_cache, a.cache_dtype, cache_stride, x, x_dtype, x_stride, feat) : a.zero_mode;
   int worst = a.zero_mode < a.host_mode ? a.zero_mode : a.host_mode;
   if (a.cache_mode < worst) worst = a.cache_mode;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int row_bytes = feat * dtype_size(x_dtype);
+  static const bool bulk_enabled = [] {
+    const char* e = getenv("HC_LOAD_BULK");
+    return e == nullptr || e[0] != '0';
+  }();
+  if (bulk_enabled && worst == 2 && x_stride == feat && row_bytes <= 512 && n >= kBulkTile) {
+    const int64_t tiles = ceil_div(n, kBulkTile);
+    const size_t smem = (size_t)kBulkWarps * 2 * kBulkTile * row_bytes;
+    int64_t blocks = ceil_div(tiles, kBulkWarps);
+    const int64_t cap = 148 * 8;
+    if (blocks > cap) blocks = cap;
+    if (smem > 48 * 1024)
+      HC_CUDA(cudaFuncSetAttribute(load_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    load_rows_bulk_kernel<<<(unsigned)blocks, kBulkWarps * 32, smem, st>>>(a, row_bytes, tiles);
+    HC_LAUNCH_OK();
+    return 0;
+  }
   const int G = group_width(feat, worst, x_dtype);
   const int64_t blocks = ceil_div(n * G, 256);
   HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   HC_DISPATCH_G(G, load_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(a));
   HC_LAUNCH_OK();
   return 0;

@@ -40,7 +40,8 @@ class HistoryTrainer:
                                   sorted_indices=self.loader.graph.sorted_indices,
                                   storage_dtype=storage_dtype)
         self.model = get_model(config, self.table).to(self.device)
-        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3))
+        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
+                                          fused=True)
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
         self.type = config.train.type.lower()

@@ -123,7 +123,8 @@ class MultiGpuHistoryTrainer:
         self.model = get_model(config, self.table).to(self.device)
         self.models = [self.model]
         self.num_layer = len(self.model.convs)
-        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3))
+        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
+                                          fused=True)
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
         self.glb_iter = 0

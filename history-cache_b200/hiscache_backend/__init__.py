@@ -51,10 +51,12 @@ def _called(n=1):
 
 
 class KernelTimer:
-    """Collects CUDA-event pairs around library calls (set with set_kernel_timer)."""
+    """Collects CUDA-event pairs around library calls (set with set_kernel_timer).
+    `only`: record just the calls whose tag starts with this prefix."""
 
-    def __init__(self):
+    def __init__(self, only=None):
         self.records = []
+        self.only = only
 
     def summary(self):
         torch.cuda.synchronize()
@@ -83,7 +85,7 @@ class _span:
         self.name, self.dev, self.e0 = name, dev, None
 
     def __enter__(self):
-        if _timer is not None:
+        if _timer is not None and (_timer.only is None or self.name.startswith(_timer.only)):
             self.e0 = torch.cuda.Event(enable_timing=True)
             self.e0.record(torch.cuda.current_stream(self.dev))
         return self
