@@ -50,6 +50,10 @@ __device__ __forceinline__ void copy_history_row(const hc_aggr_args& a, int64_t 
 // per lane cover a sampled row (<= 12 edges of 256 B, <= 6 of 512 B) in one batch, and 48
 // registers keep five blocks resident; more unrolling or forcing more blocks spills and
 // loses (U=4: 4.3 TB/s, U=6 @5 blocks: 5.1 TB/s, U=8: 3.8 TB/s for fp16 dim-128 rows).
+// Two other layouts were built and measured on the same block and lost: staging each block's
+// idx slice in shared memory with one lane group per row (3.7 TB/s), and fetching every
+// source row with the bulk-copy engine into a double-buffered shared-memory ring (4.1 TB/s:
+// the engine tops out near 13 G row copies/s, below the 16 G rows/s the register path moves).
 #ifndef HC_FWD_MINBLOCKS
 #define HC_FWD_MINBLOCKS 5
 #endif
