@@ -84,9 +84,112 @@ __global__ void __launch_bounds__(kBucketBlock)
   }
 }
 
+// ---- fixed-shape exchange: every (source, destination) pair carries exactly `slots` ids ----
+
+// ids in bucket order -> [world, slots] padded with -1; ids that do not fit are counted
+__global__ void __launch_bounds__(256)
+    bucket_pad_kernel(const int64_t* __restrict__ bucketed, const int64_t* __restrict__ counts,
+                      int64_t n, int world, int64_t slots, int64_t* __restrict__ out,
+                      unsigned long long* overflow) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= (int64_t)world * slots) return;
+  const int b = (int)(k / slots);
+  const int64_t pos = k % slots;
+  int64_t start = 0;
+  for (int w = 0; w < b; ++w) start += counts[w];
+  const int64_t c = counts[b];
+  out[k] = pos < c ? bucketed[start + pos] : -1;
+  if (pos == 0 && c > slots && overflow) atomicAdd(overflow, (unsigned long long)(c - slots));
+}
+
+// hit_out[perm[k]] = row of the padded answer that holds bucket-order entry k, or -1
+__global__ void __launch_bounds__(256)
+    unpad_hits_kernel(const int64_t* __restrict__ perm, const int64_t* __restrict__ counts,
+                      int64_t n_total, int world, int64_t slots,
+                      const uint8_t* __restrict__ flags_back, int64_t* __restrict__ hit_out,
+                      int64_t* __restrict__ slot_of) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n_total) return;
+  int b = 0;
+  int64_t start = 0;
+  for (; b < world; ++b) {
+    const int64_t c = counts[b];
+    if (k < start + c) break;
+    start += c;
+  }
+  if (b >= world) return;  // entry was left out of the buckets (keep mask)
+  const int64_t pos = k - start;
+  const int64_t where = (int64_t)b * slots + pos;
+  const int64_t p = perm[k];
+  if (slot_of) slot_of[p] = pos < slots ? where : -1;
+  if (hit_out) hit_out[p] = (pos < slots && flags_back[where]) ? where : -1;
+}
+
+__global__ void last_claim_kernel(const int64_t* __restrict__ ids, int64_t n, int* claim, int64_t map_len) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int64_t id = ids[k];
+  if (id >= 0 && id < map_len) atomicMax(claim + id, (int)k);
+}
+__global__ void last_mark_kernel(const int64_t* __restrict__ ids, int64_t n, const int* claim,
+                                 int64_t map_len, uint8_t* winners) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int64_t id = ids[k];
+  winners[k] = (id >= 0 && id < map_len && claim[id] == (int)k) ? 1 : 0;
+}
+__global__ void last_reset_kernel(const int64_t* __restrict__ ids, int64_t n, int* claim, int64_t map_len) {
+  const int64_t k = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (k >= n) return;
+  const int64_t id = ids[k];
+  if (id >= 0 && id < map_len) claim[id] = -1;
+}
+
 }  // namespace hc
 
 using namespace hc;
+
+extern "C" int hc_bucket_pad(const int64_t* bucketed, const int64_t* counts, int64_t n, int32_t world,
+                             int64_t slots, int64_t* out, int64_t* overflow, void* stream) {
+  HC_REQUIRE(n >= 0 && world >= 1 && world <= kMaxWorld && slots >= 1, HC_ERR_SIZE);
+  HC_REQUIRE(counts && out && (bucketed || n == 0), HC_ERR_NULL);
+  const int64_t total = (int64_t)world * slots;
+  const int64_t blocks = ceil_div(total, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  bucket_pad_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      bucketed, counts, n, world, slots, out, reinterpret_cast<unsigned long long*>(overflow));
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_unpad_hits(const int64_t* perm, const int64_t* counts, int64_t n, int32_t world,
+                             int64_t slots, const uint8_t* flags_back, int64_t* hit_out,
+                             int64_t* slot_of, void* stream) {
+  HC_REQUIRE(n >= 0 && world >= 1 && world <= kMaxWorld && slots >= 1, HC_ERR_SIZE);
+  if (n == 0) return 0;
+  HC_REQUIRE(perm && counts && (hit_out || slot_of), HC_ERR_NULL);
+  HC_REQUIRE(hit_out == nullptr || flags_back != nullptr, HC_ERR_NULL);
+  const int64_t blocks = ceil_div(n, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  unpad_hits_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      perm, counts, n, world, slots, flags_back, hit_out, slot_of);
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_last_occurrence(const int64_t* ids, int64_t n, int32_t* claim, int64_t map_len,
+                                  uint8_t* winners, void* stream) {
+  HC_REQUIRE(n >= 0 && n < 0x7fffffffLL && map_len >= 0, HC_ERR_SIZE);
+  if (n == 0) return 0;
+  HC_REQUIRE(ids && claim && winners, HC_ERR_NULL);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const unsigned blocks = (unsigned)ceil_div(n, 256);
+  last_claim_kernel<<<blocks, 256, 0, st>>>(ids, n, claim, map_len);
+  last_mark_kernel<<<blocks, 256, 0, st>>>(ids, n, claim, map_len, winners);
+  last_reset_kernel<<<blocks, 256, 0, st>>>(ids, n, claim, map_len);
+  HC_LAUNCH_OK();
+  return 0;
+}
 
 extern "C" int hc_abi_version(void) { return HC_ABI_VERSION; }
 

@@ -32,9 +32,11 @@ class ShardedHistoryCache(HistoryCache):
         super().__init__(uvm=uvm, config=config, mode=mode, device_id=device_id, **kw)
         cap = embed_capacity if embed_capacity is not None else max(
             1024, int(cfg_get(config, "history.shard_capacity", 1 << 20)))
+        fan = cfg_get(config, "dl.sampler.fanouts", [15])
+        max_ids = int(cfg_get(config, "dl.sampler.batch_size", 1000)) * (1 + int(fan[0]))
         self.table = ShardedHistoryTable(self.total_num_node, self.hidden_channels, cap,
                                          dtype=self.storage_dtype, device=self.device, group=group,
-                                         ops=ops, staleness=self.staleness_thres)
+                                         ops=ops, staleness=self.staleness_thres, max_ids=max_ids)
         self._rows = None
 
     @property

@@ -33,7 +33,7 @@ __all__ = [
     "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
     "aggr_forward", "score_rows", "record_history_noalloc", "select_threshold", "cache_admit", "evict_stale",
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
-    "unpermute_rows", "owner_lookup", "mix64", "launch_count", "ScoreSink", "KernelTimer",
+    "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd",
 ]
 
@@ -586,6 +586,45 @@ def bucket_by_owner(ids, world, keep=None):
                                      ptr(bucketed), ptr(sc), stream_of(dev)), "hc_bucket_by_owner")
     _called(3)
     return counts, perm, bucketed
+
+
+def bucket_pad(bucketed, counts, world, slots, overflow=None, out=None):
+    """[world, slots] ids padded with -1 from bucket-ordered ids (no host sizes needed)."""
+    dev = require_cuda(bucketed, counts)
+    if out is None:
+        out = torch.empty((world, slots), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev), _span("hc_bucket_pad", dev):
+        check(lib.hc_bucket_pad(ptr(bucketed), ptr(counts), bucketed.shape[0], world, slots, ptr(out),
+                                ptr(overflow), stream_of(dev)), "hc_bucket_pad")
+    _called()
+    return out
+
+
+def unpad_hits(perm, counts, world, slots, flags_back=None, want_slots=False):
+    """(hit_map, slot_of): row of the padded answer per original position, -1 for a miss."""
+    dev = require_cuda(perm, counts)
+    n = perm.shape[0]
+    hit = torch.empty(n, dtype=torch.int64, device=dev) if flags_back is not None else None
+    slot_of = torch.full((n,), -1, dtype=torch.int64, device=dev) if want_slots else None
+    with torch.cuda.device(dev), _span("hc_unpad_hits", dev):
+        check(lib.hc_unpad_hits(ptr(perm), ptr(counts), n, world, slots, ptr(flags_back), ptr(hit),
+                                ptr(slot_of), stream_of(dev)), "hc_unpad_hits")
+    _called()
+    return hit, slot_of
+
+
+def last_occurrence(ids, claim):
+    """uint8 mask: 1 where ids[k] >= 0 does not appear again later.  claim: int32 [N] of -1."""
+    dev = require_cuda(ids, claim)
+    ids = i64c(ids, "ids")
+    if claim.dtype != torch.int32:
+        raise TypeError("claim must be int32")
+    win = torch.empty(ids.shape[0], dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev), _span("hc_last_occurrence", dev):
+        check(lib.hc_last_occurrence(ptr(ids), ids.shape[0], ptr(claim), claim.shape[0], ptr(win),
+                                     stream_of(dev)), "hc_last_occurrence")
+    _called(3)
+    return win
 
 
 def unpermute_rows(src, perm, flags, dst, hit_out=None):

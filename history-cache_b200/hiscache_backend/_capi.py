@@ -69,6 +69,9 @@ _SIGS = {
     "hc_mix64": (C.c_uint64, [C.c_uint64]),
     "hc_bucket_scratch_bytes": (i64, [i64, i32]),
     "hc_bucket_by_owner": (C.c_int, [vp, vp, i64, i32, vp, vp, vp, vp, vp]),
+    "hc_bucket_pad": (C.c_int, [vp, vp, i64, i32, i64, vp, vp, vp]),
+    "hc_unpad_hits": (C.c_int, [vp, vp, i64, i32, i64, vp, vp, vp, vp]),
+    "hc_last_occurrence": (C.c_int, [vp, i64, vp, i64, vp, vp]),
     "hc_unpermute_rows": (C.c_int, [vp, i32, i64, i32, vp, vp, i64, vp, i64, vp, vp]),
     "hc_owner_lookup": (C.c_int, [vp, i64, vp, i64, vp, i32, i64, i64, i32, vp, i64, vp, vp]),
 }

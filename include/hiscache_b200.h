@@ -375,6 +375,30 @@ int hc_bucket_by_owner(const int64_t* ids, const uint8_t* keep, int64_t n,
                        int64_t* bucketed, void* scratch, void* stream);
 
 /*
+ * Fixed-shape form of the exchange, which needs no sizes on the host: every
+ * (source, destination) pair carries exactly `slots` ids.
+ * hc_bucket_pad: out[w*slots + p] = p-th id of bucket w (bucket order and
+ *   counts from hc_bucket_by_owner) or -1; ids beyond `slots` in a bucket are
+ *   dropped and added to overflow[0] (device int64, may be NULL).
+ * hc_unpad_hits: for bucket-order entry k < n (position p in bucket w):
+ *   slot_of[perm[k]] = w*slots + p (or -1 if dropped); hit_out[perm[k]] = that
+ *   row when flags_back[row] != 0, else -1.  Entries past the sum of counts
+ *   (left out by the keep mask) are not written.
+ * hc_last_occurrence: winners[k] = 1 iff ids[k] >= 0 and no later entry of ids
+ *   has the same value (the admissions of one step: last copy wins).  claim:
+ *   int32 [map_len], all -1 on entry and again on return.  n < 2^31.
+ * No reference counterpart (the reference's exchange is one-process peer copies,
+ * hiscache/comm.py:48-85).
+ */
+int hc_bucket_pad(const int64_t* bucketed, const int64_t* counts, int64_t n, int32_t world,
+                  int64_t slots, int64_t* out, int64_t* overflow, void* stream);
+int hc_unpad_hits(const int64_t* perm, const int64_t* counts, int64_t n, int32_t world,
+                  int64_t slots, const uint8_t* flags_back, int64_t* hit_out, int64_t* slot_of,
+                  void* stream);
+int hc_last_occurrence(const int64_t* ids, int64_t n, int32_t* claim, int64_t map_len,
+                       uint8_t* winners, void* stream);
+
+/*
  * dst[perm[k], :] = src[k, :] for k < n where flags == NULL or flags[k] != 0
  * (post_transfer of hiscache/comm.py:146-151, by rows instead of by feature
  * slices).  hit_out (int64 [*], may be NULL): hit_out[perm[k]] = flags[k] ?

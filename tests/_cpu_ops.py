@@ -63,3 +63,45 @@ def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_histor
 
 def evict_stale(checkin_iter, history_to_full, full_to_history, glb_iter, limit):
     O.evict_stale(checkin_iter.numpy(), history_to_full.numpy(), full_to_history.numpy(), glb_iter, limit)
+
+
+def bucket_pad(bucketed, counts, world, slots, overflow=None, out=None):
+    b, c = _np(bucketed), _np(counts)
+    res = np.full((world, slots), -1, dtype=np.int64)
+    start = 0
+    for w in range(world):
+        k = min(int(c[w]), slots)
+        res[w, :k] = b[start:start + k]
+        if overflow is not None and c[w] > slots:
+            overflow[0] += int(c[w]) - slots
+        start += int(c[w])
+    return torch.from_numpy(res)
+
+
+def unpad_hits(perm, counts, world, slots, flags_back=None, want_slots=False):
+    p, c = _np(perm), _np(counts)
+    n = p.shape[0]
+    hit = np.full(n, -1, dtype=np.int64)
+    slot_of = np.full(n, -1, dtype=np.int64)
+    fb = None if flags_back is None else _np(flags_back)
+    start = 0
+    for w in range(world):
+        for pos in range(int(c[w])):
+            k = start + pos
+            if pos < slots:
+                slot_of[p[k]] = w * slots + pos
+                if fb is not None and fb[w * slots + pos]:
+                    hit[p[k]] = w * slots + pos
+        start += int(c[w])
+    return (torch.from_numpy(hit) if fb is not None else None), (torch.from_numpy(slot_of) if want_slots else None)
+
+
+def last_occurrence(ids, claim):
+    a = _np(ids)
+    win = np.zeros(a.shape[0], dtype=np.uint8)
+    seen = set()
+    for k in range(a.shape[0] - 1, -1, -1):
+        if a[k] >= 0 and int(a[k]) not in seen:
+            win[k] = 1
+            seen.add(int(a[k]))
+    return torch.from_numpy(win)

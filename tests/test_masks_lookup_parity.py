@@ -129,3 +129,31 @@ def test_bucket_unpermute_owner_lookup(backend, oracle, world):
     want[slot != -1] = table[slot[slot != -1]]
     assert np.array_equal(dst.cpu().numpy(), want)
     assert np.array_equal((hit.cpu().numpy() != -1), slot != -1)
+
+
+@pytest.mark.parametrize("world,slots", [(1, 600), (2, 300), (4, 100), (8, 90)])
+def test_fixed_shape_exchange_helpers(backend, oracle, world, slots):
+    """bucket_pad / unpad_hits / last_occurrence against their numpy statements, with buckets
+    that overflow their slots in some of the cases."""
+    import _cpu_ops
+    rng = np.random.default_rng(world * 7 + slots)
+    n, N = 500, 40_000
+    ids = rng.choice(N, size=n, replace=False).astype(np.int64)
+    keep = rng.random(n) < 0.8
+    counts, perm, bucketed = backend.bucket_by_owner(cu(ids), world, cu(keep))
+    ovf = torch.zeros(1, dtype=torch.int64, device="cuda")
+    padded = backend.bucket_pad(bucketed, counts, world, slots, ovf)
+    ovf_cpu = torch.zeros(1, dtype=torch.int64)
+    want = _cpu_ops.bucket_pad(bucketed.cpu(), counts.cpu(), world, slots, ovf_cpu)
+    assert torch.equal(padded.cpu(), want) and int(ovf.item()) == int(ovf_cpu.item())
+    flags_back = torch.from_numpy((rng.random(world * slots) < 0.5).astype(np.uint8))
+    hit, slot_of = backend.unpad_hits(perm, counts, world, slots, flags_back.cuda(), want_slots=True)
+    whit, wslot = _cpu_ops.unpad_hits(perm.cpu(), counts.cpu(), world, slots, flags_back, want_slots=True)
+    kept = torch.from_numpy(keep)
+    assert torch.equal(hit.cpu()[kept], whit[kept]) and torch.equal(slot_of.cpu()[kept], wslot[kept])
+    # last occurrence, with duplicates and -1 padding
+    dup = np.concatenate([ids[:200], ids[100:300], np.full(50, -1), ids[:50]]).astype(np.int64)
+    claim = torch.full((N,), -1, dtype=torch.int32, device="cuda")
+    win = backend.last_occurrence(cu(dup), claim)
+    assert torch.equal(win.cpu(), _cpu_ops.last_occurrence(torch.from_numpy(dup), None))
+    assert int((claim != -1).sum()) == 0   # the claim map is left clean

@@ -42,7 +42,7 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
     try:
         from hiscache.sharded import ShardedHistoryTable
         table = ShardedHistoryTable(N, hidden, capacity=4096, device=dev, ops=ops,
-                                    staleness=staleness)
+                                    staleness=staleness, max_ids=n)
         assert table.world == world and table.rank == rank
         logical = {}   # id -> (row, checkin)
         for t in range(steps):
@@ -70,6 +70,7 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
             mine = {k for k in logical if int(O.owner([k], world)[0]) == rank}
             have = set(np.nonzero(table.full_to_slot.cpu().numpy() != -1)[0].tolist())
             assert have == mine, f"rank {rank} step {t}: owned set differs"
+        assert table.overflow_count == 0
         q.put((rank, "ok", len(logical)))
     except Exception as e:  # noqa: BLE001
         import traceback
@@ -100,7 +101,8 @@ def test_single_rank_equals_plain_ring(oracle):
     import _cpu_ops
     from hiscache.sharded import ShardedHistoryTable
     N, n, hidden = 2000, 300, 4
-    table = ShardedHistoryTable(N, hidden, capacity=256, device="cpu", ops=_cpu_ops, staleness=0)
+    table = ShardedHistoryTable(N, hidden, capacity=256, device="cpu", ops=_cpu_ops, staleness=0,
+                                max_ids=n)
     f2h = np.full(N, -1, dtype=np.int64)
     h2f = np.full(256, -1, dtype=np.int64)
     chk = np.full(256, -1, dtype=np.int64)
