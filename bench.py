@@ -254,6 +254,17 @@ def run_ours(args):
     ms_e2e = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop()
 
+    # ---- the same step with the batch sampled inside it (hc_sample_* / hc_relabel kernels)
+    n_samp = min(args.steps, 30)
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(n_samp):
+        trainer.train_step(next(it))
+    s1.record()
+    barrier()
+    ms_samp = max_over_ranks(s0.elapsed_time(s1))
+
     # ---- untimed pass with every library call bracketed by events: per-kernel table
     full = hb.KernelTimer()
     hb.set_kernel_timer(full)
@@ -304,12 +315,14 @@ def run_ours(args):
                    "l2": "inputs of each step are produced by the step's own kernels; no flush "
                          "(the large-block roofline uses inputs larger than L2)",
                    "batches": "pre-sampled pool (the loader's job); sampling alone takes "
-                              f"{t_sample * 1e3:.2f} ms/batch with the torch-op sampler",
+                              f"{t_sample * 1e3:.2f} ms/batch with the library's sampling kernels",
                    "prep": prep},
         "e2e": {"value": round(world * args.steps / (ms_e2e * 1e-3), 2), "unit": "iters/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
                 "host_link_feature_bytes_per_step": int(host_rows_per_step * feat_bytes),
                 "mean_loss": round(loss_sum / args.steps, 4)},
+        "with_sampling": {"value": round(world * n_samp / (ms_samp * 1e-3), 2), "unit": "iters/s",
+                          "note": "each step also samples its batch on the GPU (sizes read back per hop)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt_all.items())},

@@ -91,7 +91,56 @@ class SyntheticGraph:
 
 class NeighborSampler:
     """Uniform neighbour sampling with replacement (min(fanout, degree) draws per node),
-    de-duplicated into the layered single-CSR layout."""
+    de-duplicated into the layered single-CSR layout, by the library's sampling kernels
+    (hc_sample_counts / hc_sample_picks / hc_relabel).  New nodes are numbered in order of
+    first occurrence; every draw is a function of (seed, batch number, position, draw)."""
+
+    def __init__(self, graph: SyntheticGraph, fanouts, seed=0):
+        import hiscache_backend as hb
+        self.hb = hb
+        self.g = graph
+        self.fanouts = [int(f) for f in fanouts]
+        self.seed = int(seed)
+        self.batch_no = 0
+        self.local = torch.full((graph.num_nodes,), hb.ABSENT, dtype=torch.int32, device=graph.device)
+
+    @torch.no_grad()
+    def sample(self, seeds: torch.Tensor) -> Batch:
+        hb, g, dev = self.hb, self.g, self.g.device
+        seeds = seeds.to(dev).contiguous()
+        batch_seed = hb.mix64(self.seed * 1_000_003 + self.batch_no)
+        self.batch_no += 1
+        hb.relabel_seed(seeds, self.local)
+        nodes, ptrs, idxs = [seeds], [], []
+        n_total, base, n_edges = seeds.shape[0], 0, 0
+        layer_nodes, layer_edges = [n_total], []
+        frontier = seeds
+        for f in self.fanouts:
+            out_ptr, nbr = hb.sample_hop(g.ptr, g.idx, frontier, f, batch_seed, base)
+            new, loc = hb.relabel(nbr, self.local, n_total)
+            ptrs.append(out_ptr[1:] + n_edges)
+            idxs.append(loc)
+            base += frontier.shape[0]
+            n_edges += nbr.shape[0]
+            n_total += new.shape[0]
+            nodes.append(new)
+            layer_nodes.append(n_total)
+            layer_edges.append(n_edges)
+            frontier = new
+        b = Batch()
+        b.sub_to_full = torch.cat(nodes)
+        hb.relabel_reset(b.sub_to_full, self.local)
+        b.ptr = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev)] + ptrs)
+        b.idx = torch.cat(idxs)
+        b.y = g.labels[seeds]
+        b.num_node_in_layer = torch.tensor(layer_nodes, dtype=torch.int64)
+        b.num_edge_in_layer = torch.tensor(layer_edges, dtype=torch.int64)
+        return b
+
+
+class TorchNeighborSampler:
+    """The same batch layout built from torch operators only (new nodes numbered in id
+    order).  Runs on any device; used to exercise the host logic where there is no GPU."""
 
     def __init__(self, graph: SyntheticGraph, fanouts, seed=0):
         self.g = graph
@@ -154,7 +203,8 @@ class Loader:
     def __init__(self, graph, fanouts, batch_size, feat_mode, seed=0, rank=0, world=1,
                  iters_per_epoch=None):
         self.graph, self.feat_mode = graph, feat_mode
-        self.sampler = NeighborSampler(graph, fanouts, seed=seed * 1009 + rank)
+        cls = NeighborSampler if graph.device.type == "cuda" else TorchNeighborSampler
+        self.sampler = cls(graph, fanouts, seed=seed * 1009 + rank)
         self.batch_size = int(batch_size)
         ids = graph.train_ids
         self.train_ids = ids[rank::world] if world > 1 else ids

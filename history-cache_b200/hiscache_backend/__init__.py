@@ -33,7 +33,8 @@ __all__ = [
     "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
     "aggr_forward", "score_rows", "record_history_noalloc", "select_threshold", "cache_admit", "evict_stale",
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
-    "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "mix64", "launch_count", "ScoreSink", "KernelTimer",
+    "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "sample_hop", "relabel", "relabel_seed",
+    "relabel_reset", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd",
 ]
 
@@ -660,6 +661,65 @@ def owner_lookup(map_t, ids, table, rows_out=None):
               "hc_owner_lookup")
     _called()
     return flags, rows_out
+
+
+# ---------------------------------------------------------------------------
+# neighbour sampling (stand-in for the external loader)
+# ---------------------------------------------------------------------------
+ABSENT = -(1 << 31)  # local_map value of a node outside the batch
+
+
+def sample_hop(gptr, gidx, frontier, fanout, seed, base):
+    """One hop of uniform sampling with replacement: (out_ptr [nf+1], nbr [total]) with
+    min(fanout, degree) draws per frontier node.  Reads one size back from the device."""
+    dev = require_cuda(gptr, gidx, frontier)
+    frontier = i64c(frontier, "frontier")
+    nf = frontier.shape[0]
+    out_ptr = torch.zeros(nf + 1, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev), _span("hc_sample_counts", dev):
+        check(lib.hc_sample_counts(ptr(gptr), ptr(frontier), nf, int(fanout), ptr(out_ptr[1:]),
+                                   stream_of(dev)), "hc_sample_counts")
+    torch.cumsum(out_ptr[1:], 0, out=out_ptr[1:])
+    total = int(out_ptr[-1]) if nf > 0 else 0
+    nbr = torch.empty(total, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev), _span("hc_sample_picks", dev):
+        check(lib.hc_sample_picks(ptr(gptr), ptr(gidx), ptr(frontier), nf, int(fanout), ptr(out_ptr),
+                                  C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), int(base), ptr(nbr),
+                                  stream_of(dev)), "hc_sample_picks")
+    _called(2)
+    return out_ptr, nbr
+
+
+def relabel_seed(seeds, local_map):
+    dev = require_cuda(seeds, local_map)
+    with torch.cuda.device(dev):
+        check(lib.hc_relabel_seed(ptr(i64c(seeds)), seeds.shape[0], ptr(local_map), stream_of(dev)),
+              "hc_relabel_seed")
+    _called()
+
+
+def relabel_reset(nodes, local_map):
+    dev = require_cuda(nodes, local_map)
+    with torch.cuda.device(dev):
+        check(lib.hc_relabel_reset(ptr(i64c(nodes)), nodes.shape[0], ptr(local_map), stream_of(dev)),
+              "hc_relabel_reset")
+    _called()
+
+
+def relabel(nbr, local_map, n_total):
+    """(new_nodes [n_new], local ids of nbr): new nodes numbered from n_total in order of first
+    occurrence.  Reads n_new back from the device."""
+    dev = require_cuda(nbr, local_map)
+    m = nbr.shape[0]
+    new_nodes = torch.empty(max(m, 1), dtype=torch.int64, device=dev)
+    n_new = torch.zeros(1, dtype=torch.int64, device=dev)
+    out_idx = torch.empty(m, dtype=torch.int64, device=dev)
+    sc = scratch(dev, lib.hc_relabel_scratch_bytes(m), "relabel")
+    with torch.cuda.device(dev), _span("hc_relabel", dev):
+        check(lib.hc_relabel(ptr(nbr), m, ptr(local_map), int(n_total), ptr(new_nodes), ptr(n_new),
+                             ptr(out_idx), ptr(sc), stream_of(dev)), "hc_relabel")
+    _called(6)
+    return new_nodes[:int(n_new)], out_idx
 
 
 # ---------------------------------------------------------------------------

@@ -69,6 +69,12 @@ _SIGS = {
     "hc_mix64": (C.c_uint64, [C.c_uint64]),
     "hc_bucket_scratch_bytes": (i64, [i64, i32]),
     "hc_bucket_by_owner": (C.c_int, [vp, vp, i64, i32, vp, vp, vp, vp, vp]),
+    "hc_sample_counts": (C.c_int, [vp, vp, i64, i32, vp, vp]),
+    "hc_sample_picks": (C.c_int, [vp, vp, vp, i64, i32, vp, C.c_uint64, i64, vp, vp]),
+    "hc_relabel_seed": (C.c_int, [vp, i64, vp, vp]),
+    "hc_relabel_reset": (C.c_int, [vp, i64, vp, vp]),
+    "hc_relabel_scratch_bytes": (i64, [i64]),
+    "hc_relabel": (C.c_int, [vp, i64, vp, i64, vp, vp, vp, vp, vp]),
     "hc_bucket_pad": (C.c_int, [vp, vp, i64, i32, i64, vp, vp, vp]),
     "hc_unpad_hits": (C.c_int, [vp, vp, i64, i32, i64, vp, vp, vp, vp]),
     "hc_last_occurrence": (C.c_int, [vp, i64, vp, i64, vp, vp]),

@@ -420,6 +420,40 @@ int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids,
                     void* rows_out, int64_t out_stride, uint8_t* flags,
                     void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Neighbour sampling (stand-in for the external loader)                    */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * The reference takes its batches from cxgnndl.get_loader
+ * (hiscache/history_trainer.py:19), a project of its own.  These entry points
+ * produce the batch layout the hot path consumes (hiscache/history_model.py:
+ * 120-153): uniform sampling with replacement of min(fanout, degree) neighbours
+ * per frontier node, then relabelling into batch-local ids in order of first
+ * occurrence.  gptr / gidx: the full graph in CSR.  Draw j of frontier position
+ * i is gidx[gptr[v] + mix64(seed ^ mix64((base+i)*fanout + j)) mod deg(v)].
+ *   hc_sample_counts: counts[i] = min(fanout, deg(frontier[i])).
+ *   hc_sample_picks : nbr[out_ptr[i] + j] for j < out_ptr[i+1]-out_ptr[i]
+ *                     (out_ptr = exclusive scan of counts).
+ *   local_map: int32 [num_nodes], INT32_MIN for nodes outside the batch.
+ *   hc_relabel_seed : local_map[seeds[i]] = i.
+ *   hc_relabel      : nodes of nbr without a local id get n_total, n_total+1, ..
+ *                     in order of first occurrence; new_nodes[r] (capacity m) and
+ *                     n_new[0] (device) receive them; out_idx[p] = local id of
+ *                     nbr[p].  scratch >= hc_relabel_scratch_bytes(m).
+ *   hc_relabel_reset: local_map[nodes[i]] = INT32_MIN (end of a batch).
+ */
+int hc_sample_counts(const int64_t* gptr, const int64_t* frontier, int64_t nf, int32_t fanout,
+                     int64_t* counts, void* stream);
+int hc_sample_picks(const int64_t* gptr, const int64_t* gidx, const int64_t* frontier, int64_t nf,
+                    int32_t fanout, const int64_t* out_ptr, uint64_t seed, int64_t base,
+                    int64_t* nbr, void* stream);
+int hc_relabel_seed(const int64_t* seeds, int64_t n, int32_t* local_map, void* stream);
+int hc_relabel_reset(const int64_t* nodes, int64_t n, int32_t* local_map, void* stream);
+int64_t hc_relabel_scratch_bytes(int64_t m);
+int hc_relabel(const int64_t* nbr, int64_t m, int32_t* local_map, int64_t n_total,
+               int64_t* new_nodes, int64_t* n_new, int64_t* out_idx, void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

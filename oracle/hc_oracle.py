@@ -298,3 +298,42 @@ def bucket_by_owner(ids, world, keep=None):
     perm = sel[order].astype(np.int64)
     counts = np.bincount(own, minlength=world).astype(np.int64)
     return counts, perm, ids[perm]
+
+
+# ---------------------------------------------------------------------------
+# neighbour sampling (restates hc_sample_* / hc_relabel of the CUDA library; the
+# reference takes its batches from the external cxgnndl loader)
+# ---------------------------------------------------------------------------
+def sample_batch(gptr, gidx, seeds, fanouts, batch_seed):
+    """Returns dict(ptr, idx, sub_to_full, num_node_in_layer, num_edge_in_layer)."""
+    gptr, gidx, seeds = _i64(gptr), _i64(gidx), _i64(seeds)
+    local = {int(v): i for i, v in enumerate(seeds)}
+    nodes = list(seeds)
+    ptr, idx = [0], []
+    layer_nodes, layer_edges = [len(nodes)], []
+    frontier, base = seeds, 0
+    bs = np.uint64(batch_seed)
+    for f in fanouts:
+        new = []
+        for i, v in enumerate(frontier):
+            b, deg = int(gptr[v]), int(gptr[v + 1] - gptr[v])
+            k = min(f, deg)
+            if k:
+                keys = (np.uint64(base + i) * np.uint64(f) + np.arange(k, dtype=np.uint64))
+                u = mix64(bs ^ mix64(keys))
+                for g in gidx[b + (u % np.uint64(deg)).astype(np.int64)]:
+                    g = int(g)
+                    if g not in local:
+                        local[g] = len(nodes) + len(new)
+                        new.append(g)
+                    idx.append(local[g])
+            ptr.append(len(idx))
+        base += len(frontier)
+        nodes.extend(new)
+        layer_nodes.append(len(nodes))
+        layer_edges.append(len(idx))
+        frontier = np.asarray(new, dtype=np.int64)
+    return dict(ptr=np.asarray(ptr, dtype=np.int64), idx=np.asarray(idx, dtype=np.int64),
+                sub_to_full=np.asarray(nodes, dtype=np.int64),
+                num_node_in_layer=np.asarray(layer_nodes, dtype=np.int64),
+                num_edge_in_layer=np.asarray(layer_edges, dtype=np.int64))
