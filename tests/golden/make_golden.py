@@ -1,6 +1,6 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own Python code on CPU tensors.
 
-    python tests/golden/make_golden.py [--ref /root/reference]
+    python tests/golden/make_golden.py [--ref <reference tree>]
 
 The reference package cannot be imported as a whole (it needs cxgnndl, cxgnncomp, dgl,
 torch_geometric, matplotlib, hydra and a CUDA device), but the methods on the hot path are
