@@ -383,6 +383,13 @@ def large_block_roofline(device, peak, measured):
                   "ms": round(ms, 4), "bytes": byts, "shape": "1M dst x 10 nbrs, 4M src rows, fp32 F=256",
                   "note": "includes the zero-fill of grad_input and the fused row score"}
     torch.cuda.empty_cache()
+    ms, byts, ms_t = kb.bench_bwd_gather(1_000_000, 10, 4_000_000, 256, 10, dev=device)
+    res["bwd_gather"] = {"achieved": round(byts / ms / 1e6, 1), "frac": round(byts / ms / 1e6 / peak, 4),
+                         "ms": round(ms, 4), "transpose_ms": round(ms_t, 4), "bytes": byts,
+                         "shape": "same block as bwd",
+                         "note": "backward as a gather over the transposed block (what autograd uses for "
+                                 "blocks of this size); same algorithmic bytes as the scatter"}
+    torch.cuda.empty_cache()
     res.update({"bound": "hbm", "peak": peak, "peak_source": "measured" if measured else "fallback",
                 "unit": "GB/s"})
     return res

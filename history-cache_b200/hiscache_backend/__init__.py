@@ -21,6 +21,7 @@ device-side threshold and admission, row assembly from host-resident features.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -35,7 +36,7 @@ __all__ = [
     "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
     "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "sample_hop", "relabel", "relabel_seed",
     "relabel_reset", "mix64", "launch_count", "ScoreSink", "KernelTimer",
-    "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd",
+    "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd", "transpose_block", "run_aggr_bwd_gather",
 ]
 
 _launches = 0
@@ -198,6 +199,17 @@ class _AggrFunction(torch.autograd.Function):
                        src_map, src_alt)
         g_in = torch.empty(inp.shape, dtype=torch.float32, device=dev) if need_in else None
         g_ev = torch.empty_like(edge_value) if need_ev else None
+        # large blocks: gather over the transposed block instead of the atomic scatter
+        gathered = False
+        if (need_in and edge_value is None and inp.dim() == 2 and inp.shape[1] % 4 == 0
+                and GATHER_MIN_FEAT <= inp.shape[1] <= 1024
+                and idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES):
+            t_ptr, t_dst, t_w = transpose_block(PreparedAggr(a, None, dev, ""), idx_t.numel())
+            with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd_gather", inp), dev):
+                check(lib.hc_aggr_bwd_gather(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(grad_out),
+                                             ptr(g_in), stream_of(dev)), "hc_aggr_bwd_gather")
+            _called()
+            gathered = True
         g_h = None
         if need_h:
             g_h = torch.zeros(hbuf.shape, dtype=torch.float32, device=dev)
@@ -208,10 +220,12 @@ class _AggrFunction(torch.autograd.Function):
             score = None
         if not (need_in or need_ev or need_h or score is not None):
             return (None,) * 12
-        with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd", inp), dev):
-            check(lib.hc_aggr_bwd(C.byref(a), ptr(grad_out), ptr(g_in), 1, ptr(g_h), ptr(g_ev),
-                                  ptr(score), ctx.score_kind, stream_of(dev)), "hc_aggr_bwd")
-        _called()
+        if not gathered or need_h or score is not None:
+            with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd", inp), dev):
+                check(lib.hc_aggr_bwd(C.byref(a), ptr(grad_out), None if gathered else ptr(g_in), 1,
+                                      ptr(g_h), ptr(g_ev), ptr(score), ctx.score_kind, stream_of(dev)),
+                      "hc_aggr_bwd")
+            _called()
         if score is not None and isinstance(sink, ScoreSink):
             sink.fresh = True
         if g_in is not None and g_in.dtype != inp.dtype:
@@ -281,6 +295,37 @@ def run_aggr_bwd(p: PreparedAggr, grad_out, grad_input=None, grad_history=None, 
         check(lib.hc_aggr_bwd(C.byref(p.args), ptr(grad_out), ptr(grad_input), 1 if zero else 0,
                               ptr(grad_history), ptr(edge_grad), ptr(score), score_kind,
                               stream_of(p.dev)), "hc_aggr_bwd")
+    _called()
+
+
+# blocks whose scatter would move at least this many bytes take the transposed-gather
+# backward (the scatter is faster below: fewer launches, and its lines stay in L2)
+GATHER_MIN_BYTES = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_BYTES", 64 << 20))
+# measured on B200 (1 M x 10 edges, transpose included): 1 KB gradient rows 3.0 ms against
+# 4.2 ms for the scatter; 512-byte rows 5.3 ms against 4.3 ms, so narrow rows keep the scatter
+GATHER_MIN_FEAT = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_FEAT", 256))
+
+
+def transpose_block(p: PreparedAggr, max_edges):
+    """(t_ptr [n_src+1], t_dst [max_edges], t_w [max_edges]): per source the ascending list of
+    miss destination rows that have it as a neighbour, with the weight 1/deg of each."""
+    dev, a = p.dev, p.args
+    n_src = int(a.n_src)
+    t_ptr = torch.empty(n_src + 1, dtype=torch.int64, device=dev)
+    t_dst = torch.empty(max(int(max_edges), 1), dtype=torch.int64, device=dev)
+    t_w = torch.empty(max(int(max_edges), 1), dtype=torch.float32, device=dev)
+    sc = scratch(dev, lib.hc_transpose_scratch_bytes(n_src), "transpose")
+    with torch.cuda.device(dev), _span("hc_transpose_block", dev):
+        check(lib.hc_transpose_block(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(sc),
+                                     stream_of(dev)), "hc_transpose_block")
+    _called(7)
+    return t_ptr, t_dst, t_w
+
+
+def run_aggr_bwd_gather(p: PreparedAggr, t_ptr, t_dst, t_w, grad_out, grad_input):
+    with torch.cuda.device(p.dev), _span("hc_aggr_bwd_gather" + p.tag, p.dev):
+        check(lib.hc_aggr_bwd_gather(C.byref(p.args), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(grad_out),
+                                     ptr(grad_input), stream_of(p.dev)), "hc_aggr_bwd_gather")
     _called()
 
 

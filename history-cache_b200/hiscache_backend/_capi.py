@@ -46,6 +46,9 @@ _SIGS = {
     "hc_error_string": (C.c_char_p, [C.c_int]),
     "hc_aggr_fwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp]),
     "hc_aggr_bwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp, i32, vp, vp, vp, i32, vp]),
+    "hc_transpose_scratch_bytes": (i64, [i64]),
+    "hc_transpose_block": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, vp, vp]),
+    "hc_aggr_bwd_gather": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, vp, vp, vp]),
     "hc_score_rows": (C.c_int, [vp, i64, i32, i64, i32, vp, vp]),
     "hc_select_scratch_bytes": (i64, [i64]),
     "hc_select_threshold": (C.c_int, [vp, i64, f32, vp, vp, vp]),

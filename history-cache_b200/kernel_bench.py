@@ -79,6 +79,22 @@ def bench_bwd(n_dst, deg, n_src, feat, reps, dev="cuda:0", with_score=True):
     return ms, byts
 
 
+def bench_bwd_gather(n_dst, deg, n_src, feat, reps, dev="cuda:0"):
+    """Backward as a gather over the transposed block.  Same algorithmic bytes as the scatter
+    (so the two figures compare directly); the transpose is timed separately."""
+    x = torch.empty((n_src, feat), device=dev)
+    ptr, idx = block(n_dst, deg, n_src, dev)
+    go = torch.randn((n_dst, feat), device=dev)
+    gi = torch.empty((n_src, feat), device=dev)
+    a = hb.prepare_aggr(x, ptr, idx, n_dst)
+    ms_t = time_launches(lambda: hb.transpose_block(a, idx.numel()), max(2, reps // 2), warmup=1)
+    t_ptr, t_dst, t_w = hb.transpose_block(a, idx.numel())
+    ms = time_launches(lambda: hb.run_aggr_bwd_gather(a, t_ptr, t_dst, t_w, go, gi), reps)
+    e = n_dst * deg
+    byts = n_dst * feat * 4 + e * feat * 4 + n_src * feat * 4 + 8 * (n_dst + 1 + e)
+    return ms, byts, ms_t
+
+
 def bench_load(n, n_table, feat, dtype, reps, host, cache_frac=0.0, dev="cuda:0"):
     """batch.x assembly.  bytes = rows read (F*s each) + rows written (F*s) + 8*n ids (+ 8*n map)."""
     es = 2 if dtype == torch.float16 else 4
@@ -95,7 +111,7 @@ def bench_load(n, n_table, feat, dtype, reps, host, cache_frac=0.0, dev="cuda:0"
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "load"])
+    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "bwd_gather", "load"])
     ap.add_argument("--dst", type=int, default=2_000_000)
     ap.add_argument("--deg", type=int, default=10)
     ap.add_argument("--src", type=int, default=16_000_000)
@@ -106,15 +122,19 @@ def main():
     ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args()
     dt = torch.float16 if args.dtype == "f16" else torch.float32
+    extra = {}
     if args.op == "fwd":
         ms, byts = bench_fwd(args.dst, args.deg, args.src, args.feat, dt, args.reps, args.hit_rate)
     elif args.op == "bwd":
         ms, byts = bench_bwd(args.dst, args.deg, args.src, args.feat, args.reps)
+    elif args.op == "bwd_gather":
+        ms, byts, ms_t = bench_bwd_gather(args.dst, args.deg, args.src, args.feat, args.reps)
+        extra = {"transpose_ms": round(ms_t, 4)}
     else:
         ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host)
     print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
                       "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate,
-                      "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1)}))
+                      "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1), **extra}))
 
 
 if __name__ == "__main__":

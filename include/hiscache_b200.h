@@ -134,6 +134,27 @@ int hc_aggr_bwd(const hc_aggr_args* a, const float* grad_out, float* grad_input,
                 int32_t zero_grad_input, float* grad_history, float* edge_grad,
                 float* row_score, int32_t score_kind, void* stream);
 
+/*
+ * Backward as a gather over the transposed block (mean aggregation, one head,
+ * no edge values): the alternative to the atomic scatter of hc_aggr_bwd for
+ * blocks whose grad_input does not fit L2.  No reference counterpart (the
+ * reference only scatters, history_aggr.cu:127-168).
+ *   hc_transpose_block: t_ptr [n_src+1], t_dst / t_w [<= number of edges]: for
+ *     every source s the ascending list of destination rows r < num_node with
+ *     hmap[r] == -1 that have s as a neighbour (once per edge) and, beside each,
+ *     the weight 1/deg(r); sources with src_map[s] != -1 are left empty.
+ *     scratch >= hc_transpose_scratch_bytes(n_src).
+ *   hc_aggr_bwd_gather: grad_input[s, :] = sum over that list of
+ *     t_w * grad_out[r, :]; every row of grad_input is written (zeros for
+ *     empty lists), so it needs no clearing, and the result is deterministic.
+ *     feat must be a multiple of 4 and <= 1024.
+ */
+int64_t hc_transpose_scratch_bytes(int64_t n_src);
+int hc_transpose_block(const hc_aggr_args* a, int64_t* t_ptr, int64_t* t_dst, float* t_w,
+                       void* scratch, void* stream);
+int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, const int64_t* t_dst,
+                       const float* t_w, const float* grad_out, float* grad_input, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Scores and thresholds                                                    */
 /* ------------------------------------------------------------------------ */

@@ -166,3 +166,66 @@ def test_argument_errors_raise(backend):
         backend.aggr_forward(x.double(), ptr, idx, 1)         # unsupported dtype
     with pytest.raises(RuntimeError):
         backend.aggr_forward(x, ptr, idx, 5)                  # ptr too short
+
+
+@pytest.mark.parametrize("feat", [4, 64, 100, 128, 256, 1024])
+@pytest.mark.parametrize("with_hist,with_map", [(False, False), (True, False), (True, True)])
+def test_backward_gather_matches_oracle_and_scatter(backend, oracle, feat, with_hist, with_map):
+    """The transposed-gather backward: equal to the oracle within tolerance, bit-identical from
+    run to run, and equal to the scatter path within tolerance."""
+    rng = np.random.default_rng(feat + with_hist * 2 + with_map)
+    num_dst, n_src = 700, 1500
+    ptr, idx = csr_block(rng, num_dst, n_src, "mixed")
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.3, np.arange(num_dst), -1).astype(np.int64) if with_hist else None
+    src_map = np.where(rng.random(n_src) < 0.25, rng.integers(0, 50, size=n_src), -1).astype(np.int64) if with_map else None
+    alt = rng.standard_normal((50, feat), dtype=np.float32) if with_map else None
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    hb_t = cu(np.zeros((num_dst, feat), dtype=np.float32)) if with_hist else None
+    p = backend.prepare_aggr(cu(x), cu(ptr), cu(idx), num_dst, history_map=cu(hmap), history_buffer=hb_t,
+                             src_map=cu(src_map), src_alt=cu(alt))
+    t_ptr, t_dst, t_w = backend.transpose_block(p, len(idx))
+    gi = torch.full((n_src, feat), float("nan"), device="cuda")   # must be fully overwritten
+    backend.run_aggr_bwd_gather(p, t_ptr, t_dst, t_w, cu(g), gi)
+    want, _, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, hmap=hmap, src_map=src_map, src_alt=alt,
+                                 want_grad_history=False)
+    close(gi, want, 1e-5, scale=8.0)
+    gi2 = torch.empty_like(gi)
+    t_ptr2, t_dst2, t_w2 = backend.transpose_block(p, len(idx))
+    backend.run_aggr_bwd_gather(p, t_ptr2, t_dst2, t_w2, cu(g), gi2)
+    assert torch.equal(gi, gi2) and torch.equal(t_dst[:int(t_ptr[-1])], t_dst2[:int(t_ptr2[-1])])
+    gs = torch.empty_like(gi)
+    backend.run_aggr_bwd(p, cu(g), gs)
+    close(gs, gi.cpu().numpy(), 1e-5, scale=8.0)
+    # transposed lists: ascending destinations, one entry per counted edge
+    tp, td = t_ptr.cpu().numpy(), t_dst.cpu().numpy()
+    deg = np.diff(ptr)
+    dst = np.repeat(np.arange(num_dst), deg)
+    ok = np.ones(len(idx), bool)
+    if hmap is not None:
+        ok &= hmap[dst] == -1
+    if src_map is not None:
+        ok &= src_map[idx] == -1
+    assert tp[-1] == ok.sum()
+    for s in rng.integers(0, n_src, size=50):
+        assert np.array_equal(td[tp[s]:tp[s + 1]], np.sort(dst[ok & (idx == s)]))
+
+
+def test_autograd_switches_to_gather_for_large_blocks(backend, oracle, monkeypatch):
+    monkeypatch.setattr(backend, "GATHER_MIN_BYTES", 1)
+    monkeypatch.setattr(backend, "GATHER_MIN_FEAT", 4)
+    rng = np.random.default_rng(3)
+    num_dst, n_src, feat = 400, 900, 128
+    ptr, idx = csr_block(rng, num_dst, n_src, 6)
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    hmap = np.where(rng.random(num_dst) < 0.3, 0, -1).astype(np.int64)
+    table = rng.standard_normal((4, feat), dtype=np.float32)
+    xs = cu(x).requires_grad_(True)
+    score = torch.empty(num_dst, device="cuda")
+    out = backend.aggr_forward(xs, cu(ptr), cu(idx), num_dst, history_map=cu(hmap), history_buffer=cu(table),
+                               indexed=True, score_out=score)
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    out.backward(cu(g))
+    want, _, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, hmap=hmap, want_grad_history=False)
+    close(xs.grad, want, 1e-5, scale=8.0)
+    assert score.cpu().numpy().tobytes() == oracle.score_rows(g).tobytes()
