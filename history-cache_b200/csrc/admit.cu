@@ -71,10 +71,21 @@ __device__ uint32_t block_radix_select(const float* __restrict__ score, int64_t 
 }
 
 __global__ void __launch_bounds__(1024)
-    select_threshold_kernel(const float* __restrict__ score, int64_t n, float q,
+    select_threshold_kernel(const float* __restrict__ score, int64_t n_all, const int64_t* n_dev, float q,
                             float* __restrict__ thres) {
   __shared__ uint32_t hist[256];
   __shared__ uint32_t bcast[4];
+  // with n_dev the quantile is taken over the *n_dev smallest of the n_all scores: the caller
+  // sets the scores of padding rows to +inf, which sorts them last
+  int64_t n = n_all;
+  if (n_dev) {
+    n = n_dev[0];
+    if (n > n_all) n = n_all;
+    if (n < 1) {
+      if (threadIdx.x == 0) thres[0] = __int_as_float(0x7fc00000);
+      return;
+    }
+  }
   // rank = q * (n - 1) in fp32; weights = rank - floor(rank)
   const float pos = __fmul_rn(q, (float)(n - 1));
   int64_t k_lo = (int64_t)pos;  // truncation, pos >= 0
@@ -86,10 +97,10 @@ __global__ void __launch_bounds__(1024)
   const float w = __fsub_rn(pos, (float)k_lo);
   // NaN anywhere makes the quantile NaN
   int has_nan = 0;
-  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) has_nan |= (score[i] != score[i]);
+  for (int64_t i = threadIdx.x; i < n_all; i += blockDim.x) has_nan |= (score[i] != score[i]);
   has_nan = __syncthreads_or(has_nan);
-  const uint32_t key_lo = block_radix_select(score, n, k_lo, hist, bcast);
-  const uint32_t key_hi = (k_hi == k_lo) ? key_lo : block_radix_select(score, n, k_hi, hist, bcast);
+  const uint32_t key_lo = block_radix_select(score, n_all, k_lo, hist, bcast);
+  const uint32_t key_hi = (k_hi == k_lo) ? key_lo : block_radix_select(score, n_all, k_hi, hist, bcast);
   if (threadIdx.x == 0) {
     float r;
     if (has_nan) {
@@ -137,10 +148,8 @@ struct AdmitArgs {
 __device__ __forceinline__ bool admit_flag(const AdmitArgs& a, int64_t i, float thres) {
   if (i >= a.n) return false;
   if (a.sub_map[i] != -1) return false;
-  if (a.mode == 0) {
-    if (thres != 0.f && a.score[i] > thres) return false;
-    return a.used == nullptr || a.used[i] != 0;
-  }
+  if (a.used != nullptr && a.used[i] == 0) return false;
+  if (a.mode == 0) return !(thres != 0.f && a.score[i] > thres);
   return a.score[i] < thres;
 }
 
@@ -401,8 +410,19 @@ extern "C" int hc_select_threshold(const float* score, int64_t n, float q, float
   HC_REQUIRE(n > 0, HC_ERR_SIZE);
   HC_REQUIRE(score && thres, HC_ERR_NULL);
   HC_REQUIRE(q >= 0.f && q <= 1.f, HC_ERR_SIZE);
-  select_threshold_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(score, n, q,
-                                                                                  thres);
+  select_threshold_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(score, n, nullptr,
+                                                                                  q, thres);
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_select_threshold_counted(const float* score, int64_t n, const int64_t* n_valid,
+                                           float q, float* thres, void* stream) {
+  HC_REQUIRE(n > 0, HC_ERR_SIZE);
+  HC_REQUIRE(score && thres && n_valid, HC_ERR_NULL);
+  HC_REQUIRE(q >= 0.f && q <= 1.f, HC_ERR_SIZE);
+  select_threshold_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(score, n, n_valid,
+                                                                                  q, thres);
   HC_LAUNCH_OK();
   return 0;
 }
@@ -452,8 +472,8 @@ extern "C" int hc_cache_admit(const float* produced, int64_t prod_stride, int64_
                               const int64_t* sub2embed, const float* score, const float* thres,
                               int64_t* full2embed, int64_t total_num_node, int64_t* embed2full,
                               const int64_t* feat2full, int64_t feat2full_len, int64_t* header,
-                              int32_t reset_header, int64_t* n_admitted, void* scratch,
-                              void* stream) {
+                              int32_t reset_header, const uint8_t* valid, int64_t* n_admitted,
+                              void* scratch, void* stream) {
   HC_REQUIRE(n >= 0 && embed_capacity >= 0 && hidden > 0 && in_feat > 0 && total_num_node >= 0 &&
                  feat2full_len >= 0,
              HC_ERR_SIZE);
@@ -472,7 +492,7 @@ extern "C" int hc_cache_admit(const float* produced, int64_t prod_stride, int64_
   a.slot_to_full = embed2full; a.full_to_slot = full2embed; a.header = header;
   a.in_feat = in_feat; a.total_num_node = total_num_node;
   a.feat2full = feat2full_len > 0 ? feat2full : nullptr; a.feat2full_len = feat2full_len;
-  a.reset_header = reset_header; a.n_admitted = n_admitted;
+  a.reset_header = reset_header; a.n_admitted = n_admitted; a.used = valid;
   if (n == 0 && reset_header) {
     // nothing to admit, but the ring still restarts
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -417,8 +417,15 @@ extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t 
     int64_t blocks = ceil_div(tiles, kBulkWarps);
     const int64_t cap = 148 * 8;
     if (blocks > cap) blocks = cap;
-    if (smem > 48 * 1024)
-      HC_CUDA(cudaFuncSetAttribute(load_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // raised once per device (not a stream operation, so keep it out of stream captures)
+    static bool smem_raised[64] = {};
+    int devno = 0;
+    HC_CUDA(cudaGetDevice(&devno));
+    if (smem > 48 * 1024 && devno >= 0 && devno < 64 && !smem_raised[devno]) {
+      HC_CUDA(cudaFuncSetAttribute(load_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)((size_t)kBulkWarps * 2 * kBulkTile * 512)));
+      smem_raised[devno] = true;
+    }
     load_rows_bulk_kernel<<<(unsigned)blocks, kBulkWarps * 32, smem, st>>>(a, row_bytes, tiles);
     HC_LAUNCH_OK();
     return 0;

@@ -195,14 +195,16 @@ class HistoryCache:
         return self._sink
 
     @torch.no_grad()
-    def update_history(self, batch, glb_iter):
-        """hiscache/history_cache.py:180-254, without host round trips."""
+    def update_history(self, batch, glb_iter, reset=None):
+        """hiscache/history_cache.py:180-254, without host round trips.  `reset` overrides the
+        ring-restart decision (a captured step restarts the ring outside the capture)."""
         if "history" not in self.feat_mode or self.staleness_thres == 0:
             return
         if glb_iter < self.start_history:
             return
         num_node = int(batch.num_node_in_layer[1])
-        reset = (glb_iter % self.staleness_thres) == 0
+        if reset is None:
+            reset = (glb_iter % self.staleness_thres) == 0
         if self.produced_embedding is None:
             raise RuntimeError("produced embedding is None")
         prod = self.produced_embedding
@@ -216,9 +218,19 @@ class HistoryCache:
             score = torch.randn([num_node], device=self.device)
         self._sink = None
         prod.grad = None
-        hb.select_threshold(score, self.rate, out=self._thres)
+        valid = None
+        mask = getattr(batch, "mask", None)
+        if mask is not None:
+            # fixed-shape batch: padding rows never count towards the quantile or get admitted
+            valid = mask[:num_node]
+            score = torch.where(valid, score, torch.full_like(score, float("inf")))
+            hb.select_threshold(score, self.rate, out=self._thres,
+                                n_valid=valid.sum(dtype=torch.int64).reshape(1))
+        else:
+            hb.select_threshold(score, self.rate, out=self._thres)
         hb.cache_admit(prod.detach(), self.buffer, self.hidden_channels, self.in_channels,
                        self.overall_embed_num, batch.sub_to_full[:num_node], self.sub2embed, score,
                        self._thres, self.full2embed, self.total_num_node, self.embed2full,
-                       self.feat2full, self._header, reset_header=reset, n_admitted=self._n_admitted)
+                       self.feat2full, self._header, reset_header=reset, n_admitted=self._n_admitted,
+                       valid=valid)
         self.produced_embedding = None

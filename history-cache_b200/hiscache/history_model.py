@@ -15,6 +15,32 @@ import hiscache_backend as hb
 from .util import cfg_get
 
 
+class MaskedBatchNorm1d(torch.nn.BatchNorm1d):
+    """BatchNorm1d whose batch statistics ignore padding rows.  With mask=None it is the
+    stock module (same parameters and buffers, so state dicts are interchangeable); with a
+    row mask the mean / variance are taken over the masked rows only, which is what a
+    fixed-shape (padded) batch needs to train exactly like the unpadded one."""
+
+    def forward(self, x, mask=None):
+        if mask is None or not self.training:
+            return super().forward(x)
+        m = mask.to(x.dtype).unsqueeze(1)
+        n = m.sum()
+        mean = (x * m).sum(0) / n
+        d = (x - mean) * m
+        var = (d * d).sum(0) / n
+        if self.track_running_stats:
+            with torch.no_grad():
+                mom = self.momentum if self.momentum is not None else 0.1
+                self.running_mean.mul_(1 - mom).add_(mean.detach() * mom)
+                self.running_var.mul_(1 - mom).add_(var.detach() * (n / (n - 1).clamp(min=1)) * mom)
+                self.num_batches_tracked.add_(1)
+        y = (x - mean) * torch.rsqrt(var + self.eps)
+        if self.affine:
+            y = y * self.weight + self.bias
+        return y
+
+
 class MySageConvHistory(torch.nn.Module):
     """lin_l(aggregate(x)) + lin_r(x[:num_node]) (hiscache/history_model.py:54-100)."""
 
@@ -72,7 +98,7 @@ class HistorySAGE(torch.nn.Module):
         self.bns = torch.nn.ModuleList()
         self.num_layers = num_layers
         for _ in range(self.num_layers - 1):
-            self.bns.append(torch.nn.BatchNorm1d(hidden_channels))
+            self.bns.append(MaskedBatchNorm1d(hidden_channels))
         self.dropout = dropout
         self.table = table
         self.init_convs(**kwargs)
@@ -96,7 +122,8 @@ class HistorySAGE(torch.nn.Module):
                 self.table.produced_embedding = his
             else:
                 x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
-            x = self.bns[i](x)
+            mask = getattr(batch, "mask", None)   # fixed-shape batches carry a row mask
+            x = self.bns[i](x, None if mask is None else mask[:n])
             x = F.relu(x)
             x = F.dropout(x, p=self.dropout, training=self.training)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))

@@ -41,7 +41,7 @@ class HistoryTrainer:
                                   storage_dtype=storage_dtype)
         self.model = get_model(config, self.table).to(self.device)
         self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
-                                          fused=True)
+                                          fused=True, capturable=True)
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
         self.type = config.train.type.lower()
@@ -51,19 +51,41 @@ class HistoryTrainer:
         self.val_metrics, self.test_metrics = [], []
         self.best_metric = 0
         self.phase_ms = {}
+        self.graphed = None
 
     # one iteration of cxg_train_epoch (history_trainer.py:183-191)
     def train_step(self, batch):
+        g = self.graphed
+        if g is not None and g.fits(batch):
+            # the ring restart is decided on the host, so it happens outside the captured step
+            if self.table.staleness_thres > 0 and (self.glb_iter % self.table.staleness_thres) == 0:
+                self.table._header.zero_()
+            loss = g.run(batch)
+            self.table.glb_iter += 1
+        else:
+            loss = self._step_body(batch, reset=None)
+        self.scheduler.step()
+        self.glb_iter += 1
+        return loss
+
+    def _step_body(self, batch, reset=False):
+        """Everything of one iteration that runs on the device; with reset=False it contains no
+        host-side decision and can be captured in a CUDA graph."""
         self.optimizer.zero_grad(set_to_none=True)
         self.table.lookup_and_load(batch, len(self.model.convs))
         out = self.model(batch)
         loss = self.loss_fn(out, batch.y)
         loss.backward()
         self.optimizer.step()
-        self.scheduler.step()
-        self.table.update_history(batch, self.glb_iter)
-        self.glb_iter += 1
+        self.table.update_history(batch, self.glb_iter, reset=reset)
         return loss
+
+    def enable_cuda_graph(self, caps, edge_cap, warmup_batches):
+        """Captures the step for fixed-shape batches of these caps (hiscache/graphed.py)."""
+        from .graphed import GraphedStep
+        self.model.train()
+        self.graphed = GraphedStep(self, caps, edge_cap, warmup_batches)
+        return self.graphed
 
     def cxg_train_epoch(self):
         self.model.train()

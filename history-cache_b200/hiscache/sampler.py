@@ -34,6 +34,8 @@ class Batch:
         b = Batch()
         for k in ("ptr", "idx", "sub_to_full", "y"):
             setattr(b, k, getattr(self, k).to(device, non_blocking=non_blocking))
+        if self.mask is not None:
+            b.mask = self.mask.to(device, non_blocking=non_blocking)
         b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
         return b
 
@@ -41,12 +43,14 @@ class Batch:
         b = Batch()
         for k in ("ptr", "idx", "sub_to_full", "y"):
             setattr(b, k, getattr(self, k).cpu().pin_memory())
+        if self.mask is not None:
+            b.mask = self.mask.cpu().pin_memory()
         b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
         return b
 
     def nbytes(self):
-        return sum(getattr(self, k).numel() * getattr(self, k).element_size()
-                   for k in ("ptr", "idx", "sub_to_full", "y"))
+        keys = ("ptr", "idx", "sub_to_full", "y") + (("mask",) if self.mask is not None else ())
+        return sum(getattr(self, k).numel() * getattr(self, k).element_size() for k in keys)
 
 
 class SyntheticGraph:
@@ -103,6 +107,57 @@ class NeighborSampler:
         self.seed = int(seed)
         self.batch_no = 0
         self.local = torch.full((graph.num_nodes,), hb.ABSENT, dtype=torch.int32, device=graph.device)
+
+    @torch.no_grad()
+    def sample_padded(self, seeds: torch.Tensor, caps, edge_cap):
+        """The same batch in a fixed shape: layer k owns rows [0, caps[k]) and the new nodes of
+        hop h start at row caps[h-1]; unused rows are padding (no neighbours, node id 0, label
+        -100, mask False).  Returns None when the batch does not fit the caps."""
+        hb, g, dev = self.hb, self.g, self.g.device
+        seeds = seeds.to(dev).contiguous()
+        L = len(self.fanouts)
+        if seeds.shape[0] > caps[0]:
+            return None
+        batch_seed = hb.mix64(self.seed * 1_000_003 + self.batch_no)
+        self.batch_no += 1
+        hb.relabel_seed(seeds, self.local)
+        sub = torch.zeros(caps[L], dtype=torch.int64, device=dev)
+        mask = torch.zeros(caps[L], dtype=torch.bool, device=dev)
+        counts = torch.zeros(caps[L - 1], dtype=torch.int64, device=dev)
+        sub[:seeds.shape[0]] = seeds
+        mask[:seeds.shape[0]] = True
+        idxs, real = [], [seeds]
+        start, base, n_edges, fits = 0, 0, 0, True
+        frontier = seeds
+        for h, f in enumerate(self.fanouts):
+            out_ptr, nbr = hb.sample_hop(g.ptr, g.idx, frontier, f, batch_seed, base)
+            new, loc = hb.relabel(nbr, self.local, caps[h])
+            real.append(new)
+            n_edges += nbr.shape[0]
+            if new.shape[0] > caps[h + 1] - caps[h] or n_edges > edge_cap:
+                fits = False
+                break
+            counts[start:start + frontier.shape[0]] = out_ptr[1:] - out_ptr[:-1]
+            idxs.append(loc)
+            sub[caps[h]:caps[h] + new.shape[0]] = new
+            mask[caps[h]:caps[h] + new.shape[0]] = True
+            base += frontier.shape[0]
+            start = caps[h]
+            frontier = new
+        hb.relabel_reset(torch.cat(real), self.local)
+        if not fits:
+            return None
+        b = Batch()
+        b.sub_to_full, b.mask = sub, mask
+        b.ptr = torch.zeros(caps[L - 1] + 1, dtype=torch.int64, device=dev)
+        torch.cumsum(counts, 0, out=b.ptr[1:])
+        b.idx = torch.zeros(edge_cap, dtype=torch.int64, device=dev)
+        b.idx[:n_edges] = torch.cat(idxs)
+        b.y = torch.full((caps[0],), -100, dtype=torch.int64, device=dev)
+        b.y[:seeds.shape[0]] = g.labels[seeds]
+        b.num_node_in_layer = torch.tensor(list(caps), dtype=torch.int64)
+        b.num_edge_in_layer = torch.tensor([edge_cap] * L, dtype=torch.int64)
+        return b
 
     @torch.no_grad()
     def sample(self, seeds: torch.Tensor) -> Batch:
@@ -218,6 +273,44 @@ class Loader:
             sel = torch.randint(0, n, (self.batch_size,), generator=self._gen, device=self.graph.device)
             seeds = torch.unique(self.train_ids[sel])
             yield self.sampler.sample(seeds)
+
+    def calibrate(self, n_batches=32, slack=1.25, align=256):
+        """Fixed-shape caps from a sample of batches: (caps [L+1] cumulative rows per layer,
+        edge_cap).  Uses throw-away generators, so the loader's own stream is not consumed."""
+        gen = torch.Generator(device=self.graph.device)
+        gen.manual_seed(12345)
+        probe = NeighborSampler.__new__(NeighborSampler)
+        probe.__dict__.update(self.sampler.__dict__)
+        probe.batch_no = 1 << 40
+        n = self.train_ids.shape[0]
+        L = len(self.sampler.fanouts)
+        new_max, e_max = [0] * (L + 1), 0
+        for _ in range(n_batches):
+            sel = torch.randint(0, n, (self.batch_size,), generator=gen, device=self.graph.device)
+            b = probe.sample(torch.unique(self.train_ids[sel]))
+            nn = [int(v) for v in b.num_node_in_layer]
+            for h in range(1, L + 1):
+                new_max[h] = max(new_max[h], nn[h] - nn[h - 1])
+            e_max = max(e_max, int(b.idx.shape[0]))
+        up = lambda v: int(-(-int(v * slack) // align) * align)
+        caps = [self.batch_size]
+        for h in range(1, L + 1):
+            caps.append(caps[-1] + up(new_max[h]))
+        return caps, up(e_max)
+
+    def iterate_padded(self, n_iters, caps, edge_cap):
+        """Fixed-shape batches (NeighborSampler.sample_padded); a batch that does not fit the caps
+        is yielded in its natural shape instead."""
+        n = self.train_ids.shape[0]
+        for _ in range(n_iters):
+            sel = torch.randint(0, n, (self.batch_size,), generator=self._gen, device=self.graph.device)
+            seeds = torch.unique(self.train_ids[sel])
+            no = self.sampler.batch_no
+            b = self.sampler.sample_padded(seeds, caps, edge_cap)
+            if b is None:
+                self.sampler.batch_no = no
+                b = self.sampler.sample(seeds)
+            yield b
 
     @property
     def train_loader(self):

@@ -376,15 +376,21 @@ def score_rows(x, kind=HC_SCORE_L2, out=None):
     return out
 
 
-def select_threshold(score, q, out=None):
-    """torch.quantile(score, q) (linear interpolation) without leaving the device."""
+def select_threshold(score, q, out=None, n_valid=None):
+    """torch.quantile(score, q) (linear interpolation) without leaving the device.  With
+    n_valid (device int64[1]) the quantile is over the n_valid smallest scores (padding rows
+    carry +inf)."""
     dev = require_cuda(score)
     score = score.contiguous()
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev), _span("hc_select_threshold", dev):
-        check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
-                                      stream_of(dev)), "hc_select_threshold")
+        if n_valid is None:
+            check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
+                                          stream_of(dev)), "hc_select_threshold")
+        else:
+            check(lib.hc_select_threshold_counted(ptr(score), score.shape[0], ptr(n_valid), float(q),
+                                                  ptr(out), stream_of(dev)), "hc_select_threshold_counted")
     _called()
     return out
 
@@ -457,7 +463,7 @@ def record_history_noalloc(buffer_new, buffer_all, used_mask, sub_to_full, sub_t
 
 def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, sub2embed, score,
                 thres, full2embed, total_num_node, embed2full, feat2full, header,
-                reset_header=False, n_admitted=None):
+                reset_header=False, n_admitted=None, valid=None):
     """Device-side HistoryCache.update_history (hiscache/history_cache.py:211-254)."""
     dev = require_cuda(produced, buffer, sub_to_full, sub2embed, score, thres, full2embed,
                        embed2full, header)
@@ -473,7 +479,7 @@ def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, 
             dtype_code(buffer), hidden, in_feat, embed_capacity, ptr(i64c(sub_to_full)),
             ptr(i64c(sub2embed)), ptr(score), ptr(thres), ptr(full2embed), total_num_node,
             ptr(embed2full), ptr(feat2full), f2f_len, ptr(header), 1 if reset_header else 0,
-            ptr(n_admitted), ptr(sc), stream_of(dev)), "hc_cache_admit")
+            ptr(valid), ptr(n_admitted), ptr(sc), stream_of(dev)), "hc_cache_admit")
     _called(4)
 
 

@@ -183,6 +183,13 @@ int hc_score_rows(const float* x, int64_t n, int32_t feat, int64_t stride,
 int64_t hc_select_scratch_bytes(int64_t n);
 int hc_select_threshold(const float* score, int64_t n, float q, float* thres,
                         void* scratch, void* stream);
+/*
+ * The same quantile over the n_valid[0] (device int64) smallest of the n
+ * scores, for batches padded to a fixed shape: the caller sets the scores of
+ * padding rows to +inf.  Nothing about the size has to be known on the host.
+ */
+int hc_select_threshold_counted(const float* score, int64_t n, const int64_t* n_valid, float q,
+                                float* thres, void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Admission and eviction                                                   */
@@ -258,7 +265,9 @@ int hc_record_history_noalloc(const float* buffer_new, int64_t new_stride, int64
  * still points into the overwritten range; then full2embed / embed2full are
  * set and header[0] advances.  Unlike the reference, rows that would run past
  * embed_capacity are not admitted.  reset_header != 0 sets header[0] = 0
- * first (the ring restart of history_cache.py:190-192).
+ * first (the ring restart of history_cache.py:190-192).  valid (bytes [n],
+ * may be NULL): rows with valid[r] == 0 are never admitted (padding rows of
+ * fixed-shape batches).
  * full2embed has 2*total_num_node + 1 entries (history_cache.py:42-46).
  */
 int hc_cache_admit(const float* produced, int64_t prod_stride, int64_t n,
@@ -268,8 +277,8 @@ int hc_cache_admit(const float* produced, int64_t prod_stride, int64_t n,
                    const float* score, const float* thres, int64_t* full2embed,
                    int64_t total_num_node, int64_t* embed2full,
                    const int64_t* feat2full, int64_t feat2full_len,
-                   int64_t* header, int32_t reset_header, int64_t* n_admitted,
-                   void* scratch, void* stream);
+                   int64_t* header, int32_t reset_header, const uint8_t* valid,
+                   int64_t* n_admitted, void* scratch, void* stream);
 
 /*
  * Staleness eviction: every slot with -1 < checkin_iter[s] <= glb_iter - limit
