@@ -365,6 +365,26 @@ __global__ void evict_stale_kernel(int64_t* checkin, int64_t* h2f, int64_t* f2h,
   }
 }
 
+// the same with the iteration number read from device memory (steps replayed from a CUDA graph
+// cannot carry it as a launch argument)
+__global__ void evict_stale_dev_kernel(int64_t* checkin, int64_t* h2f, int64_t* f2h, int64_t cap,
+                                       const int64_t* __restrict__ iter_dev, int64_t limit) {
+  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= cap) return;
+  const int64_t c = checkin[s];
+  if (c > -1 && c <= iter_dev[0] - limit) {
+    const int64_t full = h2f[s];
+    checkin[s] = -1;
+    h2f[s] = -1;
+    if (full != -1) f2h[full] = -1;
+  }
+}
+__global__ void stamp_checkin_kernel(int64_t* checkin, int64_t cap, int64_t marker,
+                                     const int64_t* __restrict__ iter_dev) {
+  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s < cap && checkin[s] == marker) checkin[s] = iter_dev[0];
+}
+
 __global__ void evict_by_score_kernel(const int64_t* __restrict__ sub_to_history,
                                       const float* __restrict__ score,
                                       const float* __restrict__ thres, int64_t n, int64_t* checkin,
@@ -513,6 +533,33 @@ extern "C" int hc_evict_stale(int64_t* checkin_iter, int64_t* history_to_full,
   HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
   evict_stale_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       checkin_iter, history_to_full, full_to_history, capacity, glb_iter - limit);
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_evict_stale_dev(int64_t* checkin_iter, int64_t* history_to_full,
+                                  int64_t* full_to_history, int64_t capacity,
+                                  const int64_t* glb_iter_dev, int64_t limit, void* stream) {
+  HC_REQUIRE(capacity >= 0, HC_ERR_SIZE);
+  if (capacity == 0) return 0;
+  HC_REQUIRE(checkin_iter && history_to_full && full_to_history && glb_iter_dev, HC_ERR_NULL);
+  const int64_t blocks = ceil_div(capacity, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  evict_stale_dev_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      checkin_iter, history_to_full, full_to_history, capacity, glb_iter_dev, limit);
+  HC_LAUNCH_OK();
+  return 0;
+}
+
+extern "C" int hc_stamp_checkin(int64_t* checkin_iter, int64_t capacity, int64_t marker,
+                                const int64_t* glb_iter_dev, void* stream) {
+  HC_REQUIRE(capacity >= 0, HC_ERR_SIZE);
+  if (capacity == 0) return 0;
+  HC_REQUIRE(checkin_iter && glb_iter_dev, HC_ERR_NULL);
+  const int64_t blocks = ceil_div(capacity, 256);
+  HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
+  stamp_checkin_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      checkin_iter, capacity, marker, glb_iter_dev);
   HC_LAUNCH_OK();
   return 0;
 }

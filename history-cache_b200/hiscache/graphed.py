@@ -44,10 +44,13 @@ class GraphedStep:
                 trainer._step_body(self.static)
         torch.cuda.current_stream(dev).wait_stream(s)
         torch.cuda.synchronize(dev)
+        import hiscache_backend as hb
         self.graph = torch.cuda.CUDAGraph()
         self._load(warmup_batches[-1])
+        before = hb.launch_count()
         with torch.cuda.graph(self.graph):
             self.loss = trainer._step_body(self.static)
+        self.library_kernels_per_step = hb.launch_count() - before
 
     def fits(self, batch) -> bool:
         return (getattr(batch, "mask", None) is not None

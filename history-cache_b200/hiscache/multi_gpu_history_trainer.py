@@ -72,7 +72,7 @@ class ShardedHistoryCache(HistoryCache):
         return self._cached_embedding
 
     @torch.no_grad()
-    def update_history(self, batch, glb_iter):
+    def update_history(self, batch, glb_iter, reset=None):
         if "history" not in self.feat_mode or self.staleness_thres == 0 or glb_iter < self.start_history:
             return
         n = int(batch.num_node_in_layer[1])
@@ -88,10 +88,20 @@ class ShardedHistoryCache(HistoryCache):
             score = torch.randn([n], device=self.device)
         self._sink = None
         prod.grad = None
-        hb.select_threshold(score, self.rate, out=self._thres)
+        valid = getattr(batch, "mask", None)
+        if valid is not None:   # fixed-shape batch: padding rows neither count nor get admitted
+            valid = valid[:n]
+            score = torch.where(valid, score, torch.full_like(score, float("inf")))
+            hb.select_threshold(score, self.rate, out=self._thres,
+                                n_valid=valid.sum(dtype=torch.int64).reshape(1))
+        else:
+            hb.select_threshold(score, self.rate, out=self._thres)
         mask = (score < self._thres) & (self.sub2embed == -1)
-        self.table.evict_stale(glb_iter)
-        self.table.admit(batch.sub_to_full[:n], prod.detach(), mask, glb_iter)
+        if valid is not None:
+            mask &= valid
+        self.table.evict_stale()
+        self.table.admit(batch.sub_to_full[:n], prod.detach(), mask)
+        self.table.tick()
         self.produced_embedding = None
 
 
@@ -127,6 +137,10 @@ class MultiGpuHistoryTrainer:
         self.num_layer = len(self.model.convs)
         self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
                                           fused=True)
+        # The single-GPU trainer can replay its step from a CUDA graph (hiscache/graphed.py).
+        # Here the step contains NCCL collectives; capturing those was tried once on two GPUs
+        # and the run stopped making progress, so the data-parallel step stays eager.
+        self.graphed = None
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
         self.glb_iter = 0

@@ -53,6 +53,9 @@ class ShardedHistoryTable:
         self.checkin = torch.full((self.capacity,), -1, dtype=torch.int64, device=dev)
         self.claim = torch.full((self.N,), -1, dtype=torch.int32, device=dev)
         self.header = torch.zeros(1, dtype=torch.int64, device=dev)
+        # the iteration number lives on the device, so that a step replayed from a CUDA graph
+        # stamps and evicts with the right value; `tick()` advances it once per step
+        self.iter_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self.n_admitted = torch.zeros(1, dtype=torch.int64, device=dev)
         self.overflow = torch.zeros(1, dtype=torch.int64, device=dev)
         self._zero_thres = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -89,10 +92,12 @@ class ShardedHistoryTable:
 
     # -- admission ------------------------------------------------------------
     @torch.no_grad()
-    def admit(self, ids, rows, mask, glb_iter):
+    def admit(self, ids, rows, mask, glb_iter=None):
         """Rows with mask set go to the owner of their id and are inserted there in
         (source rank, position) order with ring semantics; of several copies of an id in
-        one call the last wins, ids the owner already holds are skipped."""
+        one call the last wins, ids the owner already holds are skipped.  The check-in time
+        is the device-side iteration counter (`glb_iter` is accepted for symmetry with the
+        reference's signature and ignored)."""
         ops, W, S = self.ops, self.world, self.slots
         if ids.shape[0] > self.max_ids:
             raise RuntimeError(f"admission of {ids.shape[0]} ids exceeds max_ids={self.max_ids}")
@@ -106,8 +111,14 @@ class ShardedHistoryTable:
         present = ops.map_lookup(self.full_to_slot, got_ids)
         ops.record_history(got_rows, self.buffer, winners, got_ids, present, self.slot_to_full,
                            self.full_to_slot, self.header, self._zero_score, self._zero_thres,
-                           self.checkin, glb_iter, n_admitted=self.n_admitted)
+                           self.checkin, ops.CHECKIN_MARKER, n_admitted=self.n_admitted)
+        ops.stamp_checkin(self.checkin, self.iter_dev)
 
-    def evict_stale(self, glb_iter):
+    def evict_stale(self, glb_iter=None):
         if self.staleness > 0:
-            self.ops.evict_stale(self.checkin, self.slot_to_full, self.full_to_slot, glb_iter, self.staleness)
+            self.ops.evict_stale_dev(self.checkin, self.slot_to_full, self.full_to_slot, self.iter_dev,
+                                     self.staleness)
+
+    def tick(self):
+        """End of a training step: advance the device-side iteration counter."""
+        self.iter_dev.add_(1)

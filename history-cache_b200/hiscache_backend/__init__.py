@@ -33,7 +33,7 @@ __all__ = [
     "record_history", "count_history_reconstruct", "count_num", "get_graph_structure_score",
     "aggr_forward_history", "aggr_forward_history_edge_value", "p2psend", "p2psend_gentensor",
     "aggr_forward", "score_rows", "record_history_noalloc", "select_threshold", "cache_admit", "evict_stale",
-    "evict_by_score", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
+    "evict_by_score", "evict_stale_dev", "stamp_checkin", "CHECKIN_MARKER", "map_lookup", "gather_rows", "load_rows", "bucket_by_owner",
     "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "sample_hop", "relabel", "relabel_seed",
     "relabel_reset", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd", "transpose_block", "run_aggr_bwd_gather",
@@ -490,6 +490,28 @@ def evict_stale(checkin_iter, history_to_full, full_to_history, glb_iter, limit)
         check(lib.hc_evict_stale(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
                                  checkin_iter.shape[0], int(glb_iter), int(limit),
                                  stream_of(dev)), "hc_evict_stale")
+    _called()
+
+
+CHECKIN_MARKER = 1 << 60   # a glb_iter no iteration takes
+
+
+def evict_stale_dev(checkin_iter, history_to_full, full_to_history, iter_dev, limit):
+    """evict_stale with the iteration number read from a device int64[1]."""
+    dev = require_cuda(checkin_iter, history_to_full, full_to_history, iter_dev)
+    with torch.cuda.device(dev), _span("hc_evict_stale", dev):
+        check(lib.hc_evict_stale_dev(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
+                                     checkin_iter.shape[0], ptr(iter_dev), int(limit), stream_of(dev)),
+              "hc_evict_stale_dev")
+    _called()
+
+
+def stamp_checkin(checkin_iter, iter_dev, marker=CHECKIN_MARKER):
+    """checkin_iter[checkin_iter == marker] = iter_dev[0]."""
+    dev = require_cuda(checkin_iter, iter_dev)
+    with torch.cuda.device(dev), _span("hc_stamp_checkin", dev):
+        check(lib.hc_stamp_checkin(ptr(checkin_iter), checkin_iter.shape[0], int(marker), ptr(iter_dev),
+                                   stream_of(dev)), "hc_stamp_checkin")
     _called()
 
 

@@ -290,6 +290,20 @@ int hc_evict_stale(int64_t* checkin_iter, int64_t* history_to_full,
                    int64_t limit, void* stream);
 
 /*
+ * The iteration number kept in device memory (int64[1]), for steps replayed
+ * from a CUDA graph, where it cannot be a launch argument:
+ * hc_evict_stale_dev is hc_evict_stale with glb_iter read from glb_iter_dev[0];
+ * hc_stamp_checkin replaces every checkin_iter[s] == marker by glb_iter_dev[0]
+ * (call hc_record_history with glb_iter = marker, a value no iteration takes,
+ * then stamp).
+ */
+int hc_evict_stale_dev(int64_t* checkin_iter, int64_t* history_to_full,
+                       int64_t* full_to_history, int64_t capacity,
+                       const int64_t* glb_iter_dev, int64_t limit, void* stream);
+int hc_stamp_checkin(int64_t* checkin_iter, int64_t capacity, int64_t marker,
+                     const int64_t* glb_iter_dev, void* stream);
+
+/*
  * Score eviction: for r < n with score[r] >= thres[0] and
  * sub_to_history[r] != -1 the slot is cleared in all three arrays
  * (hiscache/history_table.py:234-241).

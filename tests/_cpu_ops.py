@@ -105,3 +105,14 @@ def last_occurrence(ids, claim):
             win[k] = 1
             seen.add(int(a[k]))
     return torch.from_numpy(win)
+
+
+CHECKIN_MARKER = 1 << 60
+
+
+def evict_stale_dev(checkin_iter, history_to_full, full_to_history, iter_dev, limit):
+    evict_stale(checkin_iter, history_to_full, full_to_history, int(iter_dev[0]), limit)
+
+
+def stamp_checkin(checkin_iter, iter_dev, marker=CHECKIN_MARKER):
+    checkin_iter[checkin_iter == marker] = int(iter_dev[0])

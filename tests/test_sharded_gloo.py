@@ -53,9 +53,10 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
             assert np.array_equal(hit_map != -1, want_hit), f"rank {rank} step {t}: hit sets differ"
             for r in np.nonzero(want_hit)[0]:
                 assert np.array_equal(got[hit_map[r]].numpy(), logical[int(ids[r])][0])
-            table.evict_stale(t)
+            table.evict_stale()
             table.admit(torch.from_numpy(ids).to(dev), torch.from_numpy(rows).to(dev),
-                        torch.from_numpy(mask).to(dev), t)
+                        torch.from_numpy(mask).to(dev))
+            table.tick()
             # the logical table, same step for all ranks
             for k in [k for k, v in logical.items() if v[1] <= t - staleness]:
                 del logical[k]
@@ -112,7 +113,8 @@ def test_single_rank_equals_plain_ring(oracle):
         ids, rows, mask = _inputs(t, 0, N, n, hidden)
         hit_map, got = table.lookup(torch.from_numpy(ids))
         assert np.array_equal(hit_map.numpy() != -1, f2h[ids] != -1)
-        table.admit(torch.from_numpy(ids), torch.from_numpy(rows), torch.from_numpy(mask), t)
+        table.admit(torch.from_numpy(ids), torch.from_numpy(rows), torch.from_numpy(mask))
+        table.tick()
         sel = np.nonzero(mask)[0]
         oracle.record_history(rows[sel], buf, None, ids[sel], f2h[ids[sel]].copy(), h2f, f2h, hdr,
                               np.zeros(len(sel), np.float32), 0.0, chk, t)
