@@ -115,3 +115,39 @@ def test_short_training_run(mode):
     # evaluation path: feature cache only
     tr.cxg_eval_epoch("val")
     assert 0.0 <= tr.metric <= 1.0
+
+
+def test_rgcn_training_run_config5_shapes():
+    """2-layer RGCN, 5 relations, fp16 dim-768 features in pinned host memory, hidden 1024,
+    153 classes, fan-outs 25/15 (the heterogeneous configuration's shapes on a small graph)."""
+    from hiscache import HistoryCache, HostFeatureStore, get_model, make_config
+    from hiscache.sampler import Loader, SyntheticGraph
+    dev = torch.device("cuda:0")
+    N = 60_000
+    graph = SyntheticGraph(N, 14.0, 2.0, 153, seed=9, device=dev, num_train=4000)
+    uvm = HostFeatureStore(torch.randn(N, 768).half().pin_memory(), dev)
+    cfg = make_config(feature_dim=768, num_classes=153, hidden_dim=1024, num_layers=2, num_nodes=N,
+                      model="rgcn", num_rel=5, device="cuda:0", limit=0.02, staleness_thres=5,
+                      batch_size=200, fanouts=(25, 15), rate=0.5)
+    table = HistoryCache(uvm=uvm, config=cfg, mode="history_uvm", total_num_node=N,
+                         sorted_indices=graph.sorted_indices, storage_dtype=torch.float16)
+    model = get_model(cfg, table).to(dev)
+    assert type(model).__name__ == "HistoryRGCN" and len(model.convs) == 2
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+    loader = Loader(graph, [25, 15], 200, "history_uvm", seed=1, iters_per_epoch=1 << 30)
+    it = loader.train_loader
+    model.train()
+    losses = []
+    for step in range(5):
+        b = next(it)
+        b.edge_type = torch.randint(0, 5, (b.idx.shape[0],), device=dev)
+        opt.zero_grad()
+        table.lookup_and_load(b, 2)
+        out = model(b)
+        loss = torch.nn.functional.nll_loss(out, b.y)
+        loss.backward()
+        opt.step()
+        table.update_history(b, step)
+        losses.append(float(loss.detach()))
+    assert all(np.isfinite(losses))
+    assert table.header > 0
