@@ -10,7 +10,7 @@ from .feature_store import HostFeatureStore
 from .history_cache import HistoryCache
 from .history_model import get_model
 from .history_table import HistoryTable
-from .history_trainer import HistoryTrainer
+from .history_trainer import HistoryTableTrainer, HistoryTrainer
 from .multi_gpu_history_trainer import MultiGpuHistoryTrainer
 from .sampler import get_loader
 from .util import Config, make_config
@@ -19,5 +19,5 @@ __all__ = [
     "HistoryTable", "HistoryTrainer", "HistoryCache", "count_history_reconstruct",
     "get_graph_structure_score", "record_history", "get_model", "MultiGpuHistoryTrainer",
     "all2all", "all2allnaive", "all2all_prealloc", "all2allnaive_prealloc", "prepare_transfer",
-    "post_transfer", "HostFeatureStore", "get_loader", "Config", "make_config",
+    "post_transfer", "HostFeatureStore", "HistoryTableTrainer", "get_loader", "Config", "make_config",
 ]

@@ -110,7 +110,34 @@ class HistorySAGE(torch.nn.Module):
             return t.sub2embed, t.embedding_table, True, score
         return t.sub2embed, t.cached_embedding, False, None
 
+    def _forward_layered_tables(self, batch):
+        """Per-layer history tables (HistoryTable): conv i reads table layer i for its
+        destination rows and leaves its aggregation output in table.history_out[i].  This is the
+        call the reference keeps commented out in its forward (history_model.py:129-133)."""
+        t = self.table
+        x = batch.x
+        nn = batch.num_node_in_layer
+        t.history_out = []
+        for i, conv in enumerate(self.convs[:-1]):
+            n = int(nn[self.num_layers - 1 - i])
+            if self.training and i < t.num_layers and t.history_buffer_layered[i].shape[0] > 0:
+                x, his = conv(x, batch.ptr, batch.idx, t.sub_to_history[i], t.history_buffer_layered[i],
+                              t.history_size_layered[i], n, indexed=True)
+                if not his.requires_grad:
+                    his.requires_grad_(True)
+                his.retain_grad()
+                t.history_out.append(his)
+            else:
+                x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
+            x = self.bns[i](x)
+            x = F.relu(x)
+            x = F.dropout(x, p=self.dropout, training=self.training)
+        x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))
+        return x.log_softmax(dim=-1)
+
     def forward(self, batch):
+        if hasattr(self.table, "history_buffer_layered"):
+            return self._forward_layered_tables(batch)
         x = batch.x
         nn = batch.num_node_in_layer
         for i, conv in enumerate(self.convs[:-1]):

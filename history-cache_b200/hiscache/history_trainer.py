@@ -21,6 +21,56 @@ from .sampler import get_loader
 from .util import cfg_get, log
 
 
+class HistoryTableTrainer:
+    """Training with per-layer history tables (HistoryTable) instead of the unified cache:
+    full feature load, table lookup per layer, history-aware aggregation on every hidden conv,
+    ring admission gated by the used masks, eviction by score and staleness.  The reference
+    exports HistoryTable with exactly these methods (hiscache/history_table.py:94-254) but its
+    trainer no longer drives them (history_trainer.py:18 is commented out); the order here
+    follows the methods' own contracts: lookup -> forward/backward -> record -> evict."""
+
+    def __init__(self, config, graph=None, uvm=None, loader=None, storage_dtype=torch.float32,
+                 feature_dtype=torch.float32, seed=0):
+        from .history_table import HistoryTable
+        self.config = config
+        self.device = torch.device(config.dl.device)
+        torch.cuda.set_device(self.device)
+        self.loader = loader if loader is not None else get_loader(config.dl, graph=graph, seed=seed)
+        g = self.loader.graph
+        if uvm is None:
+            uvm = HostFeatureStore.synthetic(g.num_nodes, config.dl.dataset.feature_dim,
+                                             dtype=feature_dtype, seed=seed, device=self.device)
+        self.uvm = uvm
+        self.table = HistoryTable(config, total_num_node=g.num_nodes, storage_dtype=storage_dtype)
+        self.model = get_model(config, self.table).to(self.device)
+        self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
+                                          fused=True)
+        self.loss_fn = F.nll_loss
+        self.num_layer = len(self.model.convs)
+        self.glb_iter = 0
+
+    def train_step(self, batch):
+        import hiscache_backend as hb
+        t = self.table
+        self.optimizer.zero_grad(set_to_none=True)
+        nn = [int(v) for v in batch.num_node_in_layer]
+        t.lookup(batch.sub_to_full, nn)
+        # history exists one hop from the seeds as far as the pruning kernel is concerned
+        # (grad_check.cu:122-124): that is table layer num_layers_all - 2
+        hop1 = t.sub_to_history[t.num_layers_all - 2] if t.num_layers_all >= 2 else None
+        used = hb.count_history_reconstruct(batch.ptr, batch.idx, hop1, batch.sub_to_full.shape[0],
+                                            batch.y.shape[0], self.num_layer)
+        batch.x = hb.load_rows(self.uvm.buffer, None, batch.sub_to_full, None, used[0])
+        out = self.model(batch)
+        loss = self.loss_fn(out, batch.y)
+        loss.backward()
+        self.optimizer.step()
+        t.record_history(batch.sub_to_full, batch, self.glb_iter, used)
+        t.evict_history(batch, self.glb_iter)
+        self.glb_iter += 1
+        return loss
+
+
 class HistoryTrainer:
 
     def __init__(self, config, graph=None, uvm=None, loader=None, storage_dtype=torch.float32,

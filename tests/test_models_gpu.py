@@ -151,3 +151,35 @@ def test_rgcn_training_run_config5_shapes():
         losses.append(float(loss.detach()))
     assert all(np.isfinite(losses))
     assert table.header > 0
+
+
+def test_per_layer_table_training_run():
+    """3-layer SAGE on per-layer history tables with a staleness limit (the 2.4 M-node
+    configuration's mechanism on a small graph): tables fill, hits appear, stale entries go."""
+    from hiscache import HistoryTableTrainer, HostFeatureStore, make_config
+    from hiscache.sampler import SyntheticGraph
+    dev = torch.device("cuda:0")
+    N = 80_000
+    graph = SyntheticGraph(N, 26.0, 2.0, 47, seed=4, device=dev, num_train=3000)
+    uvm = HostFeatureStore(torch.randn(N, 100, device=dev), dev)
+    cfg = make_config(feature_dim=100, num_classes=47, hidden_dim=256, num_layers=3, num_nodes=N,
+                      device="cuda:0", staleness_thres=3, batch_size=300, rate=0.5,
+                      buffer_size=[40_000, 20_000], method="grad")
+    tr = HistoryTableTrainer(cfg, graph=graph, uvm=uvm)
+    tr.model.train()
+    it = tr.loader.train_loader
+    losses, hits = [], 0
+    for step in range(10):
+        losses.append(float(tr.train_step(next(it)).detach()))
+        hits += sum(int((m != -1).sum()) for m in tr.table.sub_to_history)
+        for layer in range(tr.table.num_layers):
+            chk = tr.table.checkin_iter[layer]
+            live = chk[chk > -1]
+            # nothing older than the staleness limit survives an eviction
+            assert live.numel() == 0 or int(live.min()) > step - 3
+            f2h, h2f = tr.table.full_to_history_layered[layer], tr.table.history_to_full_layered[layer]
+            mapped = torch.nonzero(f2h != -1).squeeze(1)
+            assert torch.equal(h2f[f2h[mapped]], mapped)
+    assert all(np.isfinite(losses))
+    assert hits > 0
+    assert all(int((c > -1).sum()) > 0 for c in tr.table.checkin_iter)
