@@ -379,6 +379,12 @@ def run_ours(args):
     }
     if roof:
         out["roofline"] = roof
+    if world > 1:
+        ovf = torch.tensor([trainer.table.table.overflow_count], dtype=torch.int64, device=device)
+        dist.all_reduce(ovf)
+        out["exchange"] = {"slots_per_pair": trainer.table.table.slots, "max_ids": trainer.table.table.max_ids,
+                           "ids_dropped_by_overflow": int(ovf.item()),
+                           "shard_capacity_rows": trainer.table.table.capacity}
 
     if rank == 0 and world == 1 and not args.no_large_block:
         out["roofline_large_block"] = large_block_roofline(device, peak, bool(peaks))
