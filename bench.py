@@ -60,6 +60,9 @@ def parse():
                     help="one GPU only: replay the whole step as one CUDA graph over fixed-shape "
                          "(padded) batches.  Off by default: the step is GPU-bound and the padding "
                          "costs more than the launches save (458 vs 494 iters/s)")
+    ap.add_argument("--exchange", default=os.environ.get("HC_EXCHANGE", "auto"), choices=["auto", "peer", "nccl"],
+                    help="multi-GPU history exchange: peer memory (CUDA IPC + NVLink loads) or padded "
+                         "all-to-alls; auto = peer memory when every rank can map every other")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -162,7 +165,7 @@ def make_config(args, device, world):
               num_nodes=args.nodes, model="SAGE", dropout=0.5, num_device=world, device=str(device),
               feat_mode="history_uvm", method="grad", rate=args.rate, staleness_thres=args.staleness,
               limit=args.cache_gb, batch_size=args.batch, fanouts=fanouts,
-              distributed_store=world > 1)
+              distributed_store=world > 1, exchange=args.exchange)
 
 
 def conv0_bytes(batch, feat, elem):
@@ -382,7 +385,8 @@ def run_ours(args):
     if world > 1:
         ovf = torch.tensor([trainer.table.table.overflow_count], dtype=torch.int64, device=device)
         dist.all_reduce(ovf)
-        out["exchange"] = {"slots_per_pair": trainer.table.table.slots, "max_ids": trainer.table.table.max_ids,
+        out["exchange"] = {"mode": trainer.table.exchange,
+                           "slots_per_pair": trainer.table.table.slots, "max_ids": trainer.table.table.max_ids,
                            "ids_dropped_by_overflow": int(ovf.item()),
                            "shard_capacity_rows": trainer.table.table.capacity}
 

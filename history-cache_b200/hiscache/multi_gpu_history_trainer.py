@@ -19,7 +19,7 @@ from .feature_store import HostFeatureStore
 from .history_cache import HistoryCache
 from .history_model import get_model
 from .sampler import get_loader
-from .sharded import ShardedHistoryTable
+from .sharded import PeerHistoryTable, ShardedHistoryTable
 from .util import cfg_get, log
 
 
@@ -34,9 +34,22 @@ class ShardedHistoryCache(HistoryCache):
             1024, int(cfg_get(config, "history.shard_capacity", 1 << 20)))
         fan = cfg_get(config, "dl.sampler.fanouts", [15])
         max_ids = int(cfg_get(config, "dl.sampler.batch_size", 1000)) * (1 + int(fan[0]))
-        self.table = ShardedHistoryTable(self.total_num_node, self.hidden_channels, cap,
-                                         dtype=self.storage_dtype, device=self.device, group=group,
-                                         ops=ops, staleness=self.staleness_thres, max_ids=max_ids)
+        kw_t = dict(dtype=self.storage_dtype, device=self.device, group=group, ops=ops,
+                    staleness=self.staleness_thres, max_ids=max_ids)
+        # "peer": lookups and admissions read the other GPUs' memory directly (csrc/peer.cu);
+        # "nccl": padded all-to-alls; "auto": peer memory when every rank can map every other
+        how = str(cfg_get(config, "history.exchange", "auto")).lower()
+        self.table = None
+        if how in ("peer", "auto") and ops is None:
+            try:
+                self.table = PeerHistoryTable(self.total_num_node, self.hidden_channels, cap, **kw_t)
+            except RuntimeError as e:
+                if how == "peer":
+                    raise
+                log.warning("history exchange falls back to all-to-all: %s", e)
+        if self.table is None:
+            self.table = ShardedHistoryTable(self.total_num_node, self.hidden_channels, cap, **kw_t)
+        self.exchange = "peer" if isinstance(self.table, PeerHistoryTable) else "nccl"
         self._rows = None
 
     @property
@@ -72,9 +85,11 @@ class ShardedHistoryCache(HistoryCache):
         return self._cached_embedding
 
     @torch.no_grad()
-    def update_history(self, batch, glb_iter, reset=None):
+    def prepare_update(self, batch, glb_iter):
+        """First half of update_history: score, threshold, candidate mask, and the candidates
+        handed to the table (published).  Returns False when there is nothing to admit."""
         if "history" not in self.feat_mode or self.staleness_thres == 0 or glb_iter < self.start_history:
-            return
+            return False
         n = int(batch.num_node_in_layer[1])
         prod = self.produced_embedding
         if prod is None:
@@ -99,10 +114,23 @@ class ShardedHistoryCache(HistoryCache):
         mask = (score < self._thres) & (self.sub2embed == -1)
         if valid is not None:
             mask &= valid
-        self.table.evict_stale()
-        self.table.admit(batch.sub_to_full[:n], prod.detach(), mask)
-        self.table.tick()
+        self.table.publish(batch.sub_to_full[:n], prod.detach(), mask)
         self.produced_embedding = None
+        return True
+
+    @torch.no_grad()
+    def finish_update(self):
+        """Second half: the owners drop stale entries and take in what every rank published.
+        All ranks must have passed a collective since prepare_update (see PeerHistoryTable)."""
+        self.table.evict_stale()
+        self.table.admit_published()
+        self.table.tick()
+        self.table.fence()
+
+    def update_history(self, batch, glb_iter, reset=None):
+        if self.prepare_update(batch, glb_iter):
+            self.table.fence()
+            self.finish_update()
 
 
 class MultiGpuHistoryTrainer:
@@ -131,6 +159,14 @@ class MultiGpuHistoryTrainer:
                                          sorted_indices=self.loader.graph.sorted_indices,
                                          storage_dtype=storage_dtype)
         self.tables = [self.table]
+        if self.table.exchange == "peer":
+            # With the peers' memory mapped into the process a cudaMalloc costs ~0.7 ms instead
+            # of a few microseconds (measured on B200), and because batch sizes vary the caching
+            # allocator would keep calling it every few steps.  One large block, allocated and
+            # handed back to the allocator's pool here, is split for all later requests.
+            gb = float(cfg_get(config, "train.reserve_gb", 6.0))
+            if gb > 0:
+                torch.empty(int(gb * (1 << 30)), dtype=torch.uint8, device=self.device)
         torch.manual_seed(seed)      # same initial weights on every rank
         self.model = get_model(config, self.table).to(self.device)
         self.models = [self.model]
@@ -176,11 +212,17 @@ class MultiGpuHistoryTrainer:
         self.glb_iter += 1
 
     def train_step(self, batch):
+        """The gradient all-reduce sits between the two halves of the history update: it is
+        the collective that tells every owner that all ranks have published their candidates
+        and finished this step's lookups."""
         self.load(batch)
         out = self.run_forward(batch)
         loss = self.run_backward(batch, out)
+        pending = self.table.prepare_update(batch, self.glb_iter)
         self.update_grad()
-        self.update_history(batch)
+        if pending:
+            self.table.finish_update()
+        self.glb_iter += 1
         return loss
 
     def cxg_train_epoch(self):

@@ -44,7 +44,7 @@ def make_config(*, feature_dim, num_classes, hidden_dim, num_layers, num_nodes, 
                 method="grad", rate=0.5, staleness_thres=10, start_history=0, limit=1.0,
                 distributed_store=False, lr=1e-3, num_epochs=1, eval_begin=1 << 30,
                 dataset_name="synthetic", dataset_path="", num_rel=1, buffer_size=0,
-                batch_size=1000, fanouts=(15, 10, 5), **extra):
+                batch_size=1000, fanouts=(15, 10, 5), exchange="auto", **extra):
     """Builds the nested config the classes of this package read (the same keys as the
     reference: hiscache/history_cache.py:13-35,58, hiscache/history_table.py:21-30,63,
     hiscache/history_model.py:447-452, hiscache/history_trainer.py:20-40)."""
@@ -60,7 +60,7 @@ def make_config(*, feature_dim, num_classes, hidden_dim, num_layers, num_nodes, 
         history=dict(method=method, rate=rate, staleness_thres=staleness_thres,
                      start_history=start_history, limit=limit,
                      distributed_store=distributed_store, buffer_size=buffer_size,
-                     store_last_layer=False, graph_struct_norm=0),
+                     store_last_layer=False, graph_struct_norm=0, exchange=exchange),
     )
     for k, v in extra.items():
         cfg[k] = v

@@ -37,6 +37,7 @@ __all__ = [
     "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "sample_hop", "relabel", "relabel_seed",
     "relabel_reset", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd", "transpose_block", "run_aggr_bwd_gather",
+    "PeerRegion", "peer_open", "peer_close", "peer_ptrs", "peer_lookup", "peer_publish", "peer_pull",
 ]
 
 _launches = 0
@@ -734,6 +735,127 @@ def owner_lookup(map_t, ids, table, rows_out=None):
               "hc_owner_lookup")
     _called()
     return flags, rows_out
+
+
+# ---------------------------------------------------------------------------
+# history exchange over peer memory
+# ---------------------------------------------------------------------------
+HC_MAX_PEERS = 32
+
+
+class PeerRegion:
+    """One device allocation made by the library (hc_peer_alloc) that other processes of the
+    box can map.  `view(offset, shape, dtype)` gives torch tensors over parts of it."""
+
+    def __init__(self, nbytes, device):
+        self.device = torch.device(device)
+        self.nbytes = int(nbytes)
+        out = C.c_void_p()
+        with torch.cuda.device(self.device):
+            check(lib.hc_peer_alloc(self.nbytes, C.byref(out)), "hc_peer_alloc")
+        self.ptr = int(out.value)
+        self.__cuda_array_interface__ = {"shape": (self.nbytes,), "typestr": "|u1",
+                                         "data": (self.ptr, False), "version": 2}
+        with torch.cuda.device(self.device):
+            self.bytes = torch.as_tensor(self, device=self.device)
+        if self.bytes.data_ptr() != self.ptr:
+            raise RuntimeError("PeerRegion: torch copied the region instead of viewing it")
+
+    def view(self, offset, shape, dtype):
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        if offset % 16 or offset + nb > self.nbytes:
+            raise ValueError("PeerRegion.view: bad offset or size")
+        return self.bytes[offset:offset + nb].view(dtype).view(*shape)
+
+    def export(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            check(lib.hc_peer_export(self.ptr, buf), "hc_peer_export")
+        return buf.raw
+
+    def free(self):
+        if self.ptr:
+            self.bytes = None
+            with torch.cuda.device(self.device):
+                check(lib.hc_peer_free(self.ptr), "hc_peer_free")
+            self.ptr = 0
+
+
+def peer_open(handle: bytes, device) -> int:
+    """Maps another process's exported region into this one; returns its device address."""
+    if len(handle) != 64:
+        raise ValueError("peer_open: a handle is 64 bytes")
+    out = C.c_void_p()
+    with torch.cuda.device(device):
+        check(lib.hc_peer_open(C.create_string_buffer(handle, 64), C.byref(out)), "hc_peer_open")
+    return int(out.value)
+
+
+def peer_close(address: int, device):
+    with torch.cuda.device(device):
+        check(lib.hc_peer_close(address), "hc_peer_close")
+
+
+def peer_ptrs(addresses):
+    """Host pointer table (one device address per rank) in the form the peer calls take."""
+    if not 1 <= len(addresses) <= HC_MAX_PEERS:
+        raise ValueError(f"between 1 and {HC_MAX_PEERS} ranks")
+    return (C.c_void_p * len(addresses))(*[int(a) for a in addresses])
+
+
+def peer_lookup(maps, tables, world, map_len, table_rows, feat, dtype, ids, rows_out=None):
+    """One-kernel lookup in the node-partitioned history: (hit_map [n], rows [n, feat]).
+    maps / tables: peer_ptrs() of every rank's id->slot map and row table."""
+    dev = require_cuda(ids)
+    ids = i64c(ids, "ids")
+    n = ids.shape[0]
+    if rows_out is None:
+        rows_out = torch.empty((n, feat), dtype=dtype, device=dev)
+    hit = torch.empty(n, dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev), _span("hc_peer_lookup", dev):
+        check(lib.hc_peer_lookup(maps, tables, world, map_len, dtype_code(rows_out), table_rows, feat,
+                                 feat, ptr(ids), n, ptr(rows_out), rows_out.stride(0) if n > 1 else feat,
+                                 ptr(hit), stream_of(dev)), "hc_peer_lookup")
+    _called()
+    return hit, rows_out
+
+
+def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n):
+    """Writes this rank's admission candidates into its published area."""
+    dev = require_cuda(ids, rows, mask, pub_ids, pub_rows, pub_n)
+    ids = i64c(ids, "ids")
+    n = ids.shape[0]
+    if rows.dtype != torch.float32:
+        raise TypeError("peer_publish: rows must be float32")
+    rows = rows2d(rows)
+    if mask is not None:
+        mask = mask.contiguous()
+        if mask.dtype == torch.bool:
+            mask = mask.view(torch.uint8)
+    F = pub_rows.shape[1]
+    if n and rows.shape[1] != F:
+        raise ValueError("peer_publish: row width differs from the published area")
+    with torch.cuda.device(dev), _span("hc_peer_publish", dev):
+        check(lib.hc_peer_publish(ptr(ids), ptr(mask), n, ptr(rows), rows.stride(0) if n > 1 else F, F,
+                                  ptr(pub_ids), ptr(pub_rows), ptr(pub_n), pub_ids.shape[0],
+                                  stream_of(dev)), "hc_peer_publish")
+    _called()
+
+
+def peer_pull(pub_ids, pub_rows, pub_n, world, me, max_ids, feat, got_ids, got_rows, overflow=None):
+    """Collects, in (rank, row) order, the published candidates this rank owns into
+    got_ids [cap] (tail -1) and got_rows [cap, feat] fp32."""
+    dev = require_cuda(got_ids, got_rows, overflow)
+    cap = got_ids.shape[0]
+    sc = scratch(dev, int(lib.hc_peer_pull_scratch_bytes(world, max_ids)), "peer_pull")
+    with torch.cuda.device(dev), _span("hc_peer_pull", dev):
+        check(lib.hc_peer_pull(pub_ids, pub_rows, pub_n, world, me, max_ids, feat, ptr(got_ids),
+                               ptr(got_rows), cap, ptr(overflow), ptr(sc), stream_of(dev)), "hc_peer_pull")
+    _called(3)
+    return got_ids, got_rows
 
 
 # ---------------------------------------------------------------------------

@@ -86,6 +86,15 @@ _SIGS = {
     "hc_last_occurrence": (C.c_int, [vp, i64, vp, i64, vp, vp]),
     "hc_unpermute_rows": (C.c_int, [vp, i32, i64, i32, vp, vp, i64, vp, i64, vp, vp]),
     "hc_owner_lookup": (C.c_int, [vp, i64, vp, i64, vp, i32, i64, i64, i32, vp, i64, vp, vp]),
+    "hc_peer_alloc": (C.c_int, [i64, C.POINTER(vp)]),
+    "hc_peer_free": (C.c_int, [vp]),
+    "hc_peer_export": (C.c_int, [vp, vp]),
+    "hc_peer_open": (C.c_int, [vp, C.POINTER(vp)]),
+    "hc_peer_close": (C.c_int, [vp]),
+    "hc_peer_lookup": (C.c_int, [vp, vp, i32, i64, i32, i64, i64, i32, vp, i64, vp, i64, vp, vp]),
+    "hc_peer_publish": (C.c_int, [vp, vp, i64, vp, i64, i32, vp, vp, vp, i64, vp]),
+    "hc_peer_pull_scratch_bytes": (i64, [i32, i64]),
+    "hc_peer_pull": (C.c_int, [vp, vp, vp, i32, i32, i64, i32, vp, vp, i64, vp, vp, vp]),
 }
 
 for _name, (_res, _args) in _SIGS.items():

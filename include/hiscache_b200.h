@@ -465,6 +465,61 @@ int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids,
                     void* stream);
 
 /* ------------------------------------------------------------------------ */
+/* History exchange over peer memory (one process per GPU, NVLink loads)    */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Replaces the p2psend / all2all path of src/cpp/src/comm.cu:5-29 and
+ * hiscache/comm.py:8-151 for the node-partitioned history (owner(id) =
+ * hc_mix64(id) mod world).  Every rank keeps its shard (id -> slot map, rows)
+ * and a "published candidates" area (ids, fp32 rows, count) in ONE allocation
+ * made by hc_peer_alloc, exports it with hc_peer_export, and maps the other
+ * ranks' allocations with hc_peer_open.  The pointer tables below are HOST
+ * arrays of `world` device pointers, entry r = rank r's copy (own memory for
+ * r == me).  Only plain loads cross the link; nothing is written to a peer.
+ * No kernel waits for another GPU: the caller orders the ranks with the
+ * collectives its step already has (a lookup may not overlap an admission on
+ * the owner; a pull may not start before every rank published).
+ *
+ *   hc_peer_alloc / hc_peer_free : cudaMalloc'd, zero-filled region (the one
+ *       place this library allocates: an exported region must be an allocation
+ *       of its own).  hc_peer_export writes HC_PEER_HANDLE_BYTES bytes that
+ *       another process of the same box passes to hc_peer_open (mapped with
+ *       lazily enabled peer access); hc_peer_close unmaps.
+ *   hc_peer_lookup : for i < n: slot = peer_maps[owner(ids[i])][ids[i]]; on a
+ *       hit (0 <= slot < table_rows) rows_out[i,:] = peer_tables[owner][slot,:]
+ *       and hit_map[i] = i, else hit_map[i] = -1 and the row is left untouched.
+ *       Rows must be multiples of 16 bytes (else -HC_ERR_UNSUPPORTED).
+ *   hc_peer_publish: pub_n[0] = n; for i < n: pub_ids[i] = mask[i] ? ids[i] : -1
+ *       (mask NULL = all) and pub_rows[i,:] = rows[i,:] for published rows.
+ *       n > max_ids is -HC_ERR_LIMIT.
+ *   hc_peer_pull   : scans every rank's published ids in (rank, row) order, keeps
+ *       those this rank owns, and writes them to got_ids[0..cap) / got_rows
+ *       (fp32 [cap, feat], contiguous) in that order; the tail of got_ids is -1;
+ *       candidates beyond cap are dropped and counted in *overflow (may be
+ *       NULL).  scratch >= hc_peer_pull_scratch_bytes(world, max_ids).
+ */
+#define HC_MAX_PEERS 32
+#define HC_PEER_HANDLE_BYTES 64
+int hc_peer_alloc(int64_t bytes, void** ptr);
+int hc_peer_free(void* ptr);
+int hc_peer_export(const void* ptr, void* handle);
+int hc_peer_open(const void* handle, void** ptr);
+int hc_peer_close(void* ptr);
+int hc_peer_lookup(const void* const* peer_maps, const void* const* peer_tables, int32_t world,
+                   int64_t map_len, int32_t dtype, int64_t table_rows, int64_t table_stride,
+                   int32_t feat, const int64_t* ids, int64_t n, void* rows_out, int64_t out_stride,
+                   int64_t* hit_map, void* stream);
+int hc_peer_publish(const int64_t* ids, const uint8_t* mask, int64_t n, const float* rows,
+                    int64_t row_stride, int32_t feat, int64_t* pub_ids, float* pub_rows,
+                    int64_t* pub_n, int64_t max_ids, void* stream);
+int64_t hc_peer_pull_scratch_bytes(int32_t world, int64_t max_ids);
+int hc_peer_pull(const void* const* peer_pub_ids, const void* const* peer_pub_rows,
+                 const void* const* peer_pub_n, int32_t world, int32_t me, int64_t max_ids,
+                 int32_t feat, int64_t* got_ids, float* got_rows, int64_t cap, int64_t* overflow,
+                 void* scratch, void* stream);
+
+/* ------------------------------------------------------------------------ */
 /* Neighbour sampling (stand-in for the external loader)                    */
 /* ------------------------------------------------------------------------ */
 

@@ -26,7 +26,7 @@ def _inputs(step, rank, N, n, hidden):
     return ids, rows, mask
 
 
-def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"):
+def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo", kind="a2a"):
     for p in (os.path.join(ROOT, "history-cache_b200"), os.path.join(ROOT, "oracle"), HERE):
         sys.path.insert(0, p)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -40,9 +40,9 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
         import _cpu_ops
         dev, ops = torch.device("cpu"), _cpu_ops
     try:
-        from hiscache.sharded import ShardedHistoryTable
-        table = ShardedHistoryTable(N, hidden, capacity=4096, device=dev, ops=ops,
-                                    staleness=staleness, max_ids=n)
+        from hiscache.sharded import PeerHistoryTable, ShardedHistoryTable
+        cls = PeerHistoryTable if kind == "peer" else ShardedHistoryTable
+        table = cls(N, hidden, capacity=4096, device=dev, ops=ops, staleness=staleness, max_ids=n)
         assert table.world == world and table.rank == rank
         logical = {}   # id -> (row, checkin)
         for t in range(steps):
@@ -72,6 +72,7 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
             have = set(np.nonzero(table.full_to_slot.cpu().numpy() != -1)[0].tolist())
             assert have == mine, f"rank {rank} step {t}: owned set differs"
         assert table.overflow_count == 0
+        table.close()
         q.put((rank, "ok", len(logical)))
     except Exception as e:  # noqa: BLE001
         import traceback

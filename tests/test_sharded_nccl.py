@@ -11,14 +11,16 @@ from test_sharded_gloo import _worker
 pytestmark = pytest.mark.gpu
 
 
-def test_sharded_table_two_gpus():
+@pytest.mark.parametrize("kind", ["a2a", "peer"])
+def test_sharded_table_two_gpus(kind):
+    """kind = a2a: padded all-to-alls; peer: the owners' memory is read directly (CUDA IPC)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 150
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q, "nccl"))
+    port = 29500 + os.getpid() % 150 + (200 if kind == "peer" else 0)
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q, "nccl", kind))
              for r in range(world)]
     for p in procs:
         p.start()
