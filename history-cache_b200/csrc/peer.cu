@@ -66,14 +66,19 @@ __global__ void __launch_bounds__(256)
 template <int G>
 __global__ void __launch_bounds__(256)
     peer_publish_kernel(const int64_t* __restrict__ ids, const uint8_t* __restrict__ mask,
-                        const int64_t n, const float* __restrict__ rows, const int64_t row_stride,
-                        const int feat, const int vec_ok, int64_t* __restrict__ pub_ids,
-                        float* __restrict__ pub_rows, int64_t* __restrict__ pub_n) {
+                        const float* __restrict__ score, const float* __restrict__ thres,
+                        const int64_t* __restrict__ present, const int64_t n,
+                        const float* __restrict__ rows, const int64_t row_stride, const int feat,
+                        const int vec_ok, int64_t* __restrict__ pub_ids, float* __restrict__ pub_rows,
+                        int64_t* __restrict__ pub_n) {
   if (blockIdx.x == 0 && threadIdx.x == 0) pub_n[0] = n;
   const int gl = threadIdx.x % G;
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
   if (i >= n) return;
-  const int64_t id = (mask == nullptr || mask[i] != 0) ? ids[i] : -1;
+  bool take = mask == nullptr || mask[i] != 0;
+  if (take && score != nullptr) take = score[i] < thres[0];   // the admission test
+  if (take && present != nullptr) take = present[i] == -1;    // rows served from history are not re-admitted
+  const int64_t id = take ? ids[i] : -1;
   if (gl == 0) pub_ids[i] = id;
   if (id < 0) return;
   const float* src = rows + i * row_stride;
@@ -306,13 +311,15 @@ extern "C" int hc_peer_lookup(const void* const* peer_maps, const void* const* p
   return 0;
 }
 
-extern "C" int hc_peer_publish(const int64_t* ids, const uint8_t* mask, int64_t n, const float* rows,
-                               int64_t row_stride, int32_t feat, int64_t* pub_ids, float* pub_rows,
-                               int64_t* pub_n, int64_t max_ids, void* stream) {
+extern "C" int hc_peer_publish(const int64_t* ids, const uint8_t* mask, const float* score,
+                               const float* thres, const int64_t* present, int64_t n,
+                               const float* rows, int64_t row_stride, int32_t feat, int64_t* pub_ids,
+                               float* pub_rows, int64_t* pub_n, int64_t max_ids, void* stream) {
   HC_REQUIRE(n >= 0 && feat > 0 && max_ids >= 0, HC_ERR_SIZE);
   HC_REQUIRE(n <= max_ids, HC_ERR_LIMIT);
   HC_REQUIRE(pub_ids && pub_rows && pub_n, HC_ERR_NULL);
   HC_REQUIRE(n == 0 || (ids && rows), HC_ERR_NULL);
+  HC_REQUIRE(score == nullptr || thres != nullptr, HC_ERR_NULL);
   if (row_stride == 0) row_stride = feat;
   HC_REQUIRE(row_stride >= feat, HC_ERR_SIZE);
   const int vec_ok = (feat % 4 == 0) && (row_stride % 4 == 0) && aligned16(rows) && aligned16(pub_rows);
@@ -321,7 +328,8 @@ extern "C" int hc_peer_publish(const int64_t* ids, const uint8_t* mask, int64_t 
   HC_REQUIRE(blocks <= 0x7fffffffLL, HC_ERR_SIZE);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   HC_PEER_DISPATCH_G(G, peer_publish_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(
-                            ids, mask, n, rows, row_stride, feat, vec_ok, pub_ids, pub_rows, pub_n));
+                            ids, mask, score, thres, present, n, rows, row_stride, feat, vec_ok, pub_ids,
+                            pub_rows, pub_n));
   HC_LAUNCH_OK();
   return 0;
 }
@@ -363,5 +371,89 @@ extern "C" int hc_peer_pull(const void* const* peer_pub_ids, const void* const* 
   pull_place_kernel<<<grid, kPullBlock, 0, st>>>(pid, prow, pn, world, me, max_ids, feat, vec_ok, counts,
                                                 got_ids, got_rows, cap);
   HC_LAUNCH_OK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// The whole owner-side admission of a step as one call: eviction of stale entries, pull of
+// the published candidates, last-copy-wins, skip of ids already held, ring admission, check-in
+// stamp and (optionally) the advance of the device-side iteration counter.  The same entry
+// points a host would call one by one, launched back to back on one stream.
+// ---------------------------------------------------------------------------
+namespace hc {
+static __device__ float g_zero_thres = 0.f;   // threshold 0 = "admit every candidate" for the ring admission
+static void* g_zero_thres_addr[64];
+
+static int zero_thres_ptr(const float** out) {
+  int dev = -1;
+  HC_CUDA(cudaGetDevice(&dev));
+  HC_REQUIRE(dev >= 0 && dev < 64, HC_ERR_SIZE);
+  void* p = __atomic_load_n(&g_zero_thres_addr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    HC_CUDA(cudaGetSymbolAddress(&p, g_zero_thres));
+    HC_REQUIRE(p != nullptr, HC_ERR_NULL);
+    __atomic_store_n(&g_zero_thres_addr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = reinterpret_cast<const float*>(p);
+  return 0;
+}
+
+__global__ void advance_iter_kernel(int64_t* iter_dev) { iter_dev[0] += 1; }
+
+constexpr int64_t kCheckinMarker = 1ll << 60;  // a check-in time no iteration takes
+inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+}  // namespace hc
+
+extern "C" int64_t hc_peer_admit_scratch_bytes(int32_t world, int64_t max_ids, int64_t cap) {
+  if (cap < 0) cap = 0;
+  return align256(hc_peer_pull_scratch_bytes(world, max_ids)) + align256(hc_admit_scratch_bytes(cap)) +
+         align256(cap) + align256(cap * 8);
+}
+
+extern "C" int hc_peer_admit(const hc_shard* sh, const void* const* peer_pub_ids,
+                             const void* const* peer_pub_rows, const void* const* peer_pub_n,
+                             int32_t world, int32_t me, int64_t max_ids, int64_t* got_ids,
+                             float* got_rows, int64_t cap, int64_t* overflow, int32_t evict,
+                             int32_t advance_iter, void* scratch, void* stream) {
+  HC_REQUIRE(sh != nullptr && scratch != nullptr, HC_ERR_NULL);
+  HC_REQUIRE(sh->struct_size == sizeof(hc_shard), HC_ERR_STRUCT);
+  HC_REQUIRE(sh->full_to_slot && sh->slot_to_full && sh->checkin && sh->table && sh->header &&
+                 sh->iter_dev && sh->claim,
+             HC_ERR_NULL);
+  HC_REQUIRE(cap > 0 && sh->capacity > 0 && sh->feat > 0, HC_ERR_SIZE);
+  const float* zero = nullptr;
+  int rc = zero_thres_ptr(&zero);
+  if (rc) return rc;
+  char* sc = reinterpret_cast<char*>(scratch);
+  void* pull_sc = sc;
+  sc += align256(hc_peer_pull_scratch_bytes(world, max_ids));
+  void* admit_sc = sc;
+  sc += align256(hc_admit_scratch_bytes(cap));
+  uint8_t* winners = reinterpret_cast<uint8_t*>(sc);
+  sc += align256(cap);
+  int64_t* present = reinterpret_cast<int64_t*>(sc);
+  if (evict && sh->staleness > 0) {
+    rc = hc_evict_stale_dev(sh->checkin, sh->slot_to_full, sh->full_to_slot, sh->capacity, sh->iter_dev,
+                            sh->staleness, stream);
+    if (rc) return rc;
+  }
+  rc = hc_peer_pull(peer_pub_ids, peer_pub_rows, peer_pub_n, world, me, max_ids, sh->feat, got_ids,
+                    got_rows, cap, overflow, pull_sc, stream);
+  if (rc) return rc;
+  rc = hc_last_occurrence(got_ids, cap, sh->claim, sh->map_len, winners, stream);
+  if (rc) return rc;
+  rc = hc_map_lookup(sh->full_to_slot, sh->map_len, got_ids, cap, 0, 0, present, stream);
+  if (rc) return rc;
+  // score is never read when the threshold is 0 (every candidate that won is admitted)
+  rc = hc_record_history(got_rows, sh->feat, cap, sh->table, sh->dtype, sh->capacity, sh->feat, winners,
+                         got_ids, present, sh->slot_to_full, sh->full_to_slot, sh->header, got_rows, zero,
+                         sh->checkin, kCheckinMarker, sh->n_admitted, admit_sc, stream);
+  if (rc) return rc;
+  rc = hc_stamp_checkin(sh->checkin, sh->capacity, kCheckinMarker, sh->iter_dev, stream);
+  if (rc) return rc;
+  if (advance_iter) {
+    advance_iter_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sh->iter_dev);
+    HC_LAUNCH_OK();
+  }
   return 0;
 }

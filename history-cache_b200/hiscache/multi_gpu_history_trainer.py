@@ -111,10 +111,9 @@ class ShardedHistoryCache(HistoryCache):
                                 n_valid=valid.sum(dtype=torch.int64).reshape(1))
         else:
             hb.select_threshold(score, self.rate, out=self._thres)
-        mask = (score < self._thres) & (self.sub2embed == -1)
-        if valid is not None:
-            mask &= valid
-        self.table.publish(batch.sub_to_full[:n], prod.detach(), mask)
+        # candidates: score below the threshold, not served from history, not padding
+        self.table.publish(batch.sub_to_full[:n], prod.detach(), valid, score=score, thres=self._thres,
+                           present=self.sub2embed)
         self.produced_embedding = None
         return True
 
@@ -123,8 +122,7 @@ class ShardedHistoryCache(HistoryCache):
         """Second half: the owners drop stale entries and take in what every rank published.
         All ranks must have passed a collective since prepare_update (see PeerHistoryTable)."""
         self.table.evict_stale()
-        self.table.admit_published()
-        self.table.tick()
+        self.table.admit_published(tick=True)
         self.table.fence()
 
     def update_history(self, batch, glb_iter, reset=None):
@@ -180,17 +178,17 @@ class MultiGpuHistoryTrainer:
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
         self.glb_iter = 0
-        # one flat gradient bucket: every parameter's .grad is a view into it
-        params = [p for p in self.model.parameters() if p.requires_grad]
-        self.flat_grad = torch.zeros(sum(p.numel() for p in params), device=self.device)
-        off = 0
-        for p in params:
-            p.grad = self.flat_grad[off:off + p.numel()].view_as(p)
-            off += p.numel()
+        # gradients travel in one flat bucket: autograd leaves fresh per-parameter gradients
+        # (no accumulation kernels), one concatenation packs them, one all-reduce averages them
+        # and the parameters' .grad become views of the result
+        self.params = [p for p in self.model.parameters() if p.requires_grad]
+        self._numels = [p.numel() for p in self.params]
+        self.flat_grad = None
 
     # the five phases of the reference's step (multi_gpu_history_trainer.py:60-133)
     def load(self, batch):
-        self.flat_grad.zero_()
+        for p in self.params:
+            p.grad = None
         self.table.lookup_and_load(batch, self.num_layer)
 
     def run_forward(self, batch):
@@ -202,8 +200,12 @@ class MultiGpuHistoryTrainer:
         return loss
 
     def update_grad(self):
-        dist.all_reduce(self.flat_grad, group=self.group)
-        self.flat_grad.div_(self.world)
+        flat = torch.cat([p.grad.reshape(-1) if p.grad is not None else p.new_zeros(p.numel())
+                          for p in self.params])
+        dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
+        for p, g in zip(self.params, flat.split(self._numels)):
+            p.grad = g.view_as(p)
+        self.flat_grad = flat
         self.optimizer.step()
         self.scheduler.step()
 

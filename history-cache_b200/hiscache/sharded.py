@@ -117,13 +117,23 @@ class ShardedHistoryTable:
 
     # the two-phase form of an admission (same calls as PeerHistoryTable, so that a training
     # step can put its gradient all-reduce between the two)
-    def publish(self, ids, rows, mask):
+    def publish(self, ids, rows, mask, score=None, thres=None, present=None):
+        """Candidates of this step: rows with mask set (None = all), score < thres and
+        present == -1 (each test only when given)."""
+        if score is not None:
+            m = score < thres
+            mask = m if mask is None else (mask & m)
+        if present is not None:
+            m = present == -1
+            mask = m if mask is None else (mask & m)
         self._pending = (ids, rows, mask)
 
-    def admit_published(self):
+    def admit_published(self, tick=False):
         ids, rows, mask = self._pending
         self._pending = None
         self.admit(ids, rows, mask)
+        if tick:
+            self.tick()
 
     def fence(self):
         """Nothing to do: the all-to-alls of lookup and admit already order the ranks."""
@@ -219,12 +229,13 @@ class PeerHistoryTable:
         self.iter_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self.n_admitted = torch.zeros(1, dtype=torch.int64, device=dev)
         self.overflow = torch.zeros(1, dtype=torch.int64, device=dev)
-        self._zero_thres = torch.zeros(1, dtype=torch.float32, device=dev)
-        self._zero_score = torch.zeros(self.cand_cap, dtype=torch.float32, device=dev)
         self._got_ids = torch.empty(self.cand_cap, dtype=torch.int64, device=dev)
         self._got_rows = torch.empty((self.cand_cap, self.hidden), dtype=torch.float32, device=dev)
         self._tok = torch.zeros(1, dtype=torch.int32, device=dev)
         self._evict_pending = False
+        self._shard = self.ops.make_shard(self.full_to_slot, self.slot_to_full, self.checkin, self.buffer,
+                                          self.header, self.iter_dev, self.claim, self.staleness,
+                                          self.n_admitted)
         self._opened = []
         self._ptrs = None
         if connect:
@@ -302,28 +313,25 @@ class PeerHistoryTable:
 
     # -- admission ------------------------------------------------------------
     @torch.no_grad()
-    def publish(self, ids, rows, mask):
+    def publish(self, ids, rows, mask, score=None, thres=None, present=None):
+        """Candidates of this step: rows with mask set (None = all), score < thres and
+        present == -1 (each test only when given); the tests run inside the publishing kernel."""
         if ids.shape[0] > self.max_ids:
             raise RuntimeError(f"admission of {ids.shape[0]} ids exceeds max_ids={self.max_ids}")
         if rows.dtype != torch.float32:
             rows = rows.float()
-        self.ops.peer_publish(ids, rows, mask, self.pub_ids, self.pub_rows, self.pub_n)
+        self.ops.peer_publish(ids, rows, mask, self.pub_ids, self.pub_rows, self.pub_n,
+                              score=score, thres=thres, present=present)
 
     @torch.no_grad()
-    def admit_published(self):
-        ops, p = self.ops, self._ptrs
-        if self._evict_pending:
-            ops.evict_stale_dev(self.checkin, self.slot_to_full, self.full_to_slot, self.iter_dev,
-                                self.staleness)
-            self._evict_pending = False
-        got_ids, got_rows = ops.peer_pull(p["ids"], p["rows"], p["n"], self.world, self.rank, self.max_ids,
-                                          self.hidden, self._got_ids, self._got_rows, self.overflow)
-        winners = ops.last_occurrence(got_ids, self.claim)
-        present = ops.map_lookup(self.full_to_slot, got_ids)
-        ops.record_history(got_rows, self.buffer, winners, got_ids, present, self.slot_to_full,
-                           self.full_to_slot, self.header, self._zero_score, self._zero_thres,
-                           self.checkin, ops.CHECKIN_MARKER, n_admitted=self.n_admitted)
-        ops.stamp_checkin(self.checkin, self.iter_dev)
+    def admit_published(self, tick=False):
+        """Owner-side admission of what every rank published (one library call).  tick=True
+        also advances the iteration counter, saving the separate tick()."""
+        p = self._ptrs
+        self.ops.peer_admit(self._shard, p["ids"], p["rows"], p["n"], self.world, self.rank, self.max_ids,
+                            self._got_ids, self._got_rows, self.overflow, evict=self._evict_pending,
+                            advance_iter=tick)
+        self._evict_pending = False
 
     def admit(self, ids, rows, mask, glb_iter=None):
         self.publish(ids, rows, mask)

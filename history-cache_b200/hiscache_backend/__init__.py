@@ -37,7 +37,7 @@ __all__ = [
     "unpermute_rows", "owner_lookup", "bucket_pad", "unpad_hits", "last_occurrence", "sample_hop", "relabel", "relabel_seed",
     "relabel_reset", "mix64", "launch_count", "ScoreSink", "KernelTimer",
     "set_kernel_timer", "prepare_aggr", "run_aggr_fwd", "run_aggr_bwd", "transpose_block", "run_aggr_bwd_gather",
-    "PeerRegion", "peer_open", "peer_close", "peer_ptrs", "peer_lookup", "peer_publish", "peer_pull",
+    "PeerRegion", "peer_open", "peer_close", "peer_ptrs", "peer_lookup", "peer_publish", "peer_pull", "peer_admit", "make_shard",
 ]
 
 _launches = 0
@@ -823,9 +823,19 @@ def peer_lookup(maps, tables, world, map_len, table_rows, feat, dtype, ids, rows
     return hit, rows_out
 
 
-def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n):
-    """Writes this rank's admission candidates into its published area."""
-    dev = require_cuda(ids, rows, mask, pub_ids, pub_rows, pub_n)
+def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n, score=None, thres=None, present=None):
+    """Writes this rank's admission candidates into its published area: rows with mask set
+    (None = all), score < thres (when given) and present == -1 (when given)."""
+    dev = require_cuda(ids, rows, mask, pub_ids, pub_rows, pub_n, score, thres, present)
+    if score is not None:
+        if thres is None or score.dtype != torch.float32 or thres.dtype != torch.float32:
+            raise TypeError("peer_publish: score and thres must be float32 tensors")
+        score = score.contiguous()
+        if score.shape[0] != ids.shape[0]:
+            raise ValueError("peer_publish: one score per id")
+    present = i64c(present, "present")
+    if present is not None and present.shape[0] != ids.shape[0]:
+        raise ValueError("peer_publish: one present entry per id")
     ids = i64c(ids, "ids")
     n = ids.shape[0]
     if rows.dtype != torch.float32:
@@ -839,7 +849,8 @@ def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n):
     if n and rows.shape[1] != F:
         raise ValueError("peer_publish: row width differs from the published area")
     with torch.cuda.device(dev), _span("hc_peer_publish", dev):
-        check(lib.hc_peer_publish(ptr(ids), ptr(mask), n, ptr(rows), rows.stride(0) if n > 1 else F, F,
+        check(lib.hc_peer_publish(ptr(ids), ptr(mask), ptr(score), ptr(thres), ptr(present), n, ptr(rows),
+                                  rows.stride(0) if n > 1 else F, F,
                                   ptr(pub_ids), ptr(pub_rows), ptr(pub_n), pub_ids.shape[0],
                                   stream_of(dev)), "hc_peer_publish")
     _called()
@@ -856,6 +867,42 @@ def peer_pull(pub_ids, pub_rows, pub_n, world, me, max_ids, feat, got_ids, got_r
                                ptr(got_rows), cap, ptr(overflow), ptr(sc), stream_of(dev)), "hc_peer_pull")
     _called(3)
     return got_ids, got_rows
+
+
+def make_shard(full_to_slot, slot_to_full, checkin, table, header, iter_dev, claim, staleness,
+               n_admitted=None):
+    """struct hc_shard over one rank's tables (keep the tensors alive while it is used)."""
+    require_cuda(full_to_slot, slot_to_full, checkin, table, header, iter_dev, claim, n_admitted)
+    if claim.dtype != torch.int32:
+        raise TypeError("claim must be int32")
+    for t, name in ((full_to_slot, "full_to_slot"), (slot_to_full, "slot_to_full"), (checkin, "checkin"),
+                    (header, "header"), (iter_dev, "iter_dev")):
+        if t.dtype != torch.int64 or not t.is_contiguous():
+            raise TypeError(f"{name} must be contiguous int64")
+    if not table.is_contiguous():
+        raise ValueError("table must be contiguous")
+    sh = _capi.Shard()
+    sh.struct_size = C.sizeof(_capi.Shard)
+    sh.full_to_slot, sh.map_len = ptr(full_to_slot), full_to_slot.shape[0]
+    sh.slot_to_full, sh.checkin, sh.capacity = ptr(slot_to_full), ptr(checkin), table.shape[0]
+    sh.table, sh.dtype, sh.feat = ptr(table), dtype_code(table), table.shape[1]
+    sh.header, sh.iter_dev, sh.claim = ptr(header), ptr(iter_dev), ptr(claim)
+    sh.staleness, sh.n_admitted = int(staleness), ptr(n_admitted)
+    return sh
+
+
+def peer_admit(shard, pub_ids, pub_rows, pub_n, world, me, max_ids, got_ids, got_rows, overflow=None,
+               evict=True, advance_iter=False):
+    """Owner-side admission of one step in one call (evict, pull, last copy wins, skip ids
+    already held, ring admission, stamp, optional iteration advance)."""
+    dev = require_cuda(got_ids, got_rows, overflow)
+    cap = got_ids.shape[0]
+    sc = scratch(dev, int(lib.hc_peer_admit_scratch_bytes(world, max_ids, cap)), "peer_admit")
+    with torch.cuda.device(dev), _span("hc_peer_admit", dev):
+        check(lib.hc_peer_admit(C.byref(shard), pub_ids, pub_rows, pub_n, world, me, max_ids, ptr(got_ids),
+                                ptr(got_rows), cap, ptr(overflow), 1 if evict else 0,
+                                1 if advance_iter else 0, ptr(sc), stream_of(dev)), "hc_peer_admit")
+    _called(14)
 
 
 # ---------------------------------------------------------------------------

@@ -41,6 +41,16 @@ class AggrArgs(C.Structure):
     ]
 
 
+class Shard(C.Structure):
+    """struct hc_shard"""
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("full_to_slot", vp), ("map_len", i64), ("slot_to_full", vp), ("checkin", vp),
+        ("capacity", i64), ("table", vp), ("dtype", i32), ("feat", i32), ("header", vp),
+        ("iter_dev", vp), ("claim", vp), ("staleness", i64), ("n_admitted", vp),
+    ]
+
+
 _SIGS = {
     "hc_abi_version": (C.c_int, []),
     "hc_error_string": (C.c_char_p, [C.c_int]),
@@ -92,9 +102,11 @@ _SIGS = {
     "hc_peer_open": (C.c_int, [vp, C.POINTER(vp)]),
     "hc_peer_close": (C.c_int, [vp]),
     "hc_peer_lookup": (C.c_int, [vp, vp, i32, i64, i32, i64, i64, i32, vp, i64, vp, i64, vp, vp]),
-    "hc_peer_publish": (C.c_int, [vp, vp, i64, vp, i64, i32, vp, vp, vp, i64, vp]),
+    "hc_peer_publish": (C.c_int, [vp, vp, vp, vp, vp, i64, vp, i64, i32, vp, vp, vp, i64, vp]),
     "hc_peer_pull_scratch_bytes": (i64, [i32, i64]),
     "hc_peer_pull": (C.c_int, [vp, vp, vp, i32, i32, i64, i32, vp, vp, i64, vp, vp, vp]),
+    "hc_peer_admit_scratch_bytes": (i64, [i32, i64, i64]),
+    "hc_peer_admit": (C.c_int, [C.POINTER(Shard), vp, vp, vp, i32, i32, i64, vp, vp, i64, vp, i32, i32, vp, vp]),
 }
 
 for _name, (_res, _args) in _SIGS.items():

@@ -490,9 +490,13 @@ int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids,
  *       hit (0 <= slot < table_rows) rows_out[i,:] = peer_tables[owner][slot,:]
  *       and hit_map[i] = i, else hit_map[i] = -1 and the row is left untouched.
  *       Rows must be multiples of 16 bytes (else -HC_ERR_UNSUPPORTED).
- *   hc_peer_publish: pub_n[0] = n; for i < n: pub_ids[i] = mask[i] ? ids[i] : -1
- *       (mask NULL = all) and pub_rows[i,:] = rows[i,:] for published rows.
- *       n > max_ids is -HC_ERR_LIMIT.
+ *   hc_peer_publish: pub_n[0] = n; for i < n: row i is published when mask[i] != 0
+ *       (mask NULL = all) and score[i] < thres[0] (score NULL = no test; the
+ *       admission test of grad_check.cu:31-33 made where the candidates are
+ *       written) and present[i] == -1 (present NULL = no test; rows that were
+ *       served from history are not admitted again).  pub_ids[i] = ids[i] or -1,
+ *       pub_rows[i,:] = rows[i,:] for published rows.  n > max_ids is
+ *       -HC_ERR_LIMIT.
  *   hc_peer_pull   : scans every rank's published ids in (rank, row) order, keeps
  *       those this rank owns, and writes them to got_ids[0..cap) / got_rows
  *       (fp32 [cap, feat], contiguous) in that order; the tail of got_ids is -1;
@@ -510,7 +514,8 @@ int hc_peer_lookup(const void* const* peer_maps, const void* const* peer_tables,
                    int64_t map_len, int32_t dtype, int64_t table_rows, int64_t table_stride,
                    int32_t feat, const int64_t* ids, int64_t n, void* rows_out, int64_t out_stride,
                    int64_t* hit_map, void* stream);
-int hc_peer_publish(const int64_t* ids, const uint8_t* mask, int64_t n, const float* rows,
+int hc_peer_publish(const int64_t* ids, const uint8_t* mask, const float* score,
+                    const float* thres, const int64_t* present, int64_t n, const float* rows,
                     int64_t row_stride, int32_t feat, int64_t* pub_ids, float* pub_rows,
                     int64_t* pub_n, int64_t max_ids, void* stream);
 int64_t hc_peer_pull_scratch_bytes(int32_t world, int64_t max_ids);
@@ -518,6 +523,47 @@ int hc_peer_pull(const void* const* peer_pub_ids, const void* const* peer_pub_ro
                  const void* const* peer_pub_n, int32_t world, int32_t me, int64_t max_ids,
                  int32_t feat, int64_t* got_ids, float* got_rows, int64_t cap, int64_t* overflow,
                  void* scratch, void* stream);
+
+/*
+ * One rank's shard of the node-partitioned history, as hc_peer_admit needs it
+ * (the members of hiscache/history_table.py:33-61 for one table, plus the
+ * device-side iteration counter).  struct_size = sizeof(hc_shard).
+ */
+typedef struct hc_shard {
+  uint32_t struct_size;
+  int64_t* full_to_slot;   /* [map_len] node id -> slot or -1                  */
+  int64_t map_len;
+  int64_t* slot_to_full;   /* [capacity]                                       */
+  int64_t* checkin;        /* [capacity] iteration of admission, -1 = free     */
+  int64_t capacity;
+  void* table;             /* [capacity, feat] rows, dtype                     */
+  int32_t dtype;
+  int32_t feat;
+  int64_t* header;         /* [1] ring header                                  */
+  int64_t* iter_dev;       /* [1] current iteration                            */
+  int32_t* claim;          /* [map_len] int32, all -1 between calls            */
+  int64_t staleness;       /* entries older than this leave; <= 0: never       */
+  int64_t* n_admitted;     /* [1] rows admitted by the call, may be NULL       */
+} hc_shard;
+
+/*
+ * The owner-side admission of one step in one call, on one stream:
+ *   evict (when evict != 0 and staleness > 0; hc_evict_stale_dev), hc_peer_pull,
+ *   last copy of an id wins (hc_last_occurrence), ids the shard already holds
+ *   are skipped, ring admission with writeback (hc_record_history), check-in
+ *   stamp (hc_stamp_checkin), and iter_dev[0] += 1 when advance_iter != 0.
+ * got_ids [cap] / got_rows [cap, feat] fp32 are the candidate list (left
+ * filled for inspection).  scratch >= hc_peer_admit_scratch_bytes(world,
+ * max_ids, cap).  The ordering rules of the peer exchange apply: every rank has
+ * published and finished its lookups before this call, and no rank looks up
+ * again before every rank has returned from it (stream order + a collective).
+ */
+int64_t hc_peer_admit_scratch_bytes(int32_t world, int64_t max_ids, int64_t cap);
+int hc_peer_admit(const hc_shard* shard, const void* const* peer_pub_ids,
+                  const void* const* peer_pub_rows, const void* const* peer_pub_n, int32_t world,
+                  int32_t me, int64_t max_ids, int64_t* got_ids, float* got_rows, int64_t cap,
+                  int64_t* overflow, int32_t evict, int32_t advance_iter, void* scratch,
+                  void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Neighbour sampling (stand-in for the external loader)                    */

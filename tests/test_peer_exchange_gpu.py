@@ -172,3 +172,28 @@ def test_limits_and_errors():
         t.close()
     with pytest.raises(ValueError):
         PeerHistoryTable(100, 6, 16, dtype=torch.float16, device="cuda:0", rank=0, world=1)  # 12-byte rows
+
+
+def test_publish_applies_the_admission_test():
+    """publish(mask, score, thres, present) == publish(mask & (score < thres) & (present == -1))."""
+    from hiscache.sharded import PeerHistoryTable
+    N, n, hidden = 4000, 500, 16
+    rng = np.random.default_rng(5)
+    ids, rows, mask = _inputs(0, 0, N, n, hidden)
+    score = rng.random(n).astype(np.float32)
+    score[::7] = 0.5                                   # ties with the threshold are not admitted
+    present = np.where(rng.random(n) < 0.3, rng.integers(0, 99, n), -1).astype(np.int64)
+    t = PeerHistoryTable(N, hidden, 64, device="cuda:0", max_ids=n, rank=0, world=1)
+    try:
+        c = lambda a: torch.from_numpy(a).cuda()
+        t.publish(c(ids), c(rows), c(mask), score=c(score), thres=torch.tensor([0.5], device="cuda:0"),
+                  present=c(present))
+        take = mask & (score < 0.5) & (present == -1)
+        assert 0 < take.sum() < n
+        assert np.array_equal(t.pub_ids.cpu().numpy(), np.where(take, ids, -1))
+        assert int(t.pub_n[0]) == n
+        assert np.array_equal(t.pub_rows.cpu().numpy()[take], rows[take])
+        t.publish(c(ids), c(rows), None, present=c(present))
+        assert np.array_equal(t.pub_ids.cpu().numpy(), np.where(present == -1, ids, -1))
+    finally:
+        t.close()
