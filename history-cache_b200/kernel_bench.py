@@ -95,10 +95,26 @@ def bench_bwd_gather(n_dst, deg, n_src, feat, reps, dev="cuda:0"):
     return ms, byts, ms_t
 
 
-def bench_load(n, n_table, feat, dtype, reps, host, cache_frac=0.0, dev="cuda:0"):
+def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0"):
     """batch.x assembly.  bytes = rows read (F*s each) + rows written (F*s) + 8*n ids (+ 8*n map)."""
     es = 2 if dtype == torch.float16 else 4
-    if host:
+    if host and thp:
+        # anonymous mapping backed by 2 MB transparent huge pages, then registered with CUDA
+        import mmap
+        import numpy as np
+        nbytes = n_table * feat * es
+        mm = mmap.mmap(-1, nbytes + (2 << 20), flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+        mm.madvise(mmap.MADV_HUGEPAGE)
+        raw = np.frombuffer(mm, dtype=np.uint8)
+        off = (-raw.ctypes.data) % (2 << 20)
+        raw = raw[off:off + nbytes]
+        raw[::4096] = 1      # touch every page
+        table = torch.from_numpy(raw.view(np.float16 if es == 2 else np.float32).reshape(n_table, feat))
+        rc = torch.cuda.cudart().cudaHostRegister(table.data_ptr(), nbytes, 0)
+        if int(rc) != 0:
+            raise RuntimeError(f"cudaHostRegister failed with {rc}")
+        bench_load.keep = mm
+    elif host:
         table = torch.empty((n_table, feat), dtype=dtype, pin_memory=True)  # contents do not matter
     else:
         table = torch.randn((n_table, feat), device=dev).to(dtype)
@@ -119,6 +135,7 @@ def main():
     ap.add_argument("--dtype", default="f16", choices=["f16", "f32"])
     ap.add_argument("--hit-rate", type=float, default=0.0)
     ap.add_argument("--host", action="store_true", help="load: table in pinned host memory")
+    ap.add_argument("--thp", action="store_true", help="load --host: back the table with 2 MB huge pages")
     ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args()
     dt = torch.float16 if args.dtype == "f16" else torch.float32
@@ -131,7 +148,7 @@ def main():
         ms, byts, ms_t = bench_bwd_gather(args.dst, args.deg, args.src, args.feat, args.reps)
         extra = {"transpose_ms": round(ms_t, 4)}
     else:
-        ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host)
+        ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host, args.thp)
     print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
                       "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate,
                       "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1), **extra}))
