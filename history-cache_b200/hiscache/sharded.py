@@ -1,10 +1,16 @@
 """Node-partitioned embedding history for the GPUs of one box.
 
-One logical table keyed by global node id, split by owner(id) = mix64(id) mod world.  A
-rank asks the owners for the rows of its hop-1 nodes (all-to-all of ids, then of rows) and
-sends the rows it admits to their owners the same way; remote rows always land in the asking
-rank's own memory before a kernel reads them.  All messages have fixed shapes (padded
-buckets), so the exchange adds no device->host wait to a training step.
+One logical table keyed by global node id, split by owner(id) = mix64(id) mod world, in two
+interchangeable forms:
+
+  PeerHistoryTable     the ranks map each other's shard (CUDA IPC) and read it with plain loads
+                       over NVLink: a lookup is one kernel, an admission is a local publish
+                       followed by the owner pulling what it owns (csrc/peer.cu);
+  ShardedHistoryTable  padded all-to-alls: ids to the owners, flags and rows back; admitted
+                       (id, row) pairs to the owners the same way.  All messages have fixed
+                       shapes, so the exchange adds no device->host wait to a training step.
+
+In both, remote rows land in the asking rank's own memory before the aggregation reads them.
 
 The reference has no working counterpart: its distributed store splits the feature axis with
 an empty slice (hiscache/history_cache.py:72-78) and the only caller discards the result of
