@@ -264,7 +264,8 @@ class PeerHistoryTable:
         if not self._dist or self.world == 1:
             self.connect_raw([self.region.ptr])
             return
-        torch.cuda.synchronize(self.device)      # the fills above are done before anybody reads
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)  # the fills above are done before anybody reads
         handles = [None] * self.world
         dist.all_gather_object(handles, self.region.export(), group=self.group)
         base, err = [], None
@@ -289,7 +290,8 @@ class PeerHistoryTable:
     def close(self, collective=True):
         """Unmaps the peers' regions and frees this rank's (all ranks together)."""
         if collective and self._dist and self.world > 1:
-            torch.cuda.synchronize(self.device)
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
             dist.barrier(group=self.group)
         for a in self._opened:
             self.ops.peer_close(a, self.device)

@@ -116,3 +116,141 @@ def evict_stale_dev(checkin_iter, history_to_full, full_to_history, iter_dev, li
 
 def stamp_checkin(checkin_iter, iter_dev, marker=CHECKIN_MARKER):
     checkin_iter[checkin_iter == marker] = int(iter_dev[0])
+
+
+# ---------------------------------------------------------------------------
+# peer-memory exchange: the "device allocation other ranks can map" is a file in /dev/shm
+# that the other CPU ranks mmap; addresses are process-local virtual addresses.
+# ---------------------------------------------------------------------------
+import ctypes
+import mmap
+import os
+import types
+
+_NPDT = {torch.float32: np.float32, torch.float16: np.float16, torch.int64: np.int64,
+         torch.int32: np.int32, torch.uint8: np.uint8}
+_maps = {}      # address -> (mmap object, path or None)
+_count = [0]
+
+
+def _addr(mm):
+    return ctypes.addressof(ctypes.c_char.from_buffer(mm))
+
+
+def _at(addr, count, dt):
+    nb = int(count) * np.dtype(dt).itemsize
+    return np.frombuffer((ctypes.c_char * nb).from_address(int(addr)), dtype=dt, count=int(count))
+
+
+class PeerRegion:
+    def __init__(self, nbytes, device):
+        _count[0] += 1
+        self.path = f"/dev/shm/hc_cpu_region_{os.getpid()}_{_count[0]}"
+        self.nbytes = int(nbytes)
+        with open(self.path, "wb") as f:
+            f.truncate(self.nbytes)
+        fd = os.open(self.path, os.O_RDWR)
+        try:
+            self.mm = mmap.mmap(fd, self.nbytes, mmap.MAP_SHARED, mmap.PROT_READ | mmap.PROT_WRITE)
+        finally:
+            os.close(fd)
+        self.ptr = _addr(self.mm)
+
+    def view(self, offset, shape, dtype):
+        n = int(np.prod(shape))
+        return torch.from_numpy(_at(self.ptr + offset, n, _NPDT[dtype]).reshape(tuple(int(d) for d in shape)))
+
+    def export(self):
+        return self.path.encode().ljust(64, b"\0")
+
+    def free(self):
+        if self.path and os.path.exists(self.path):
+            os.unlink(self.path)      # the pages stay while somebody maps them
+        self.path = None
+
+
+def peer_open(handle, device):
+    path = handle.rstrip(b"\0").decode()
+    fd = os.open(path, os.O_RDWR)
+    try:
+        mm = mmap.mmap(fd, 0, mmap.MAP_SHARED, mmap.PROT_READ | mmap.PROT_WRITE)
+    finally:
+        os.close(fd)
+    a = _addr(mm)
+    _maps[a] = mm
+    return a
+
+
+def peer_close(address, device):
+    _maps.pop(address, None)
+
+
+def peer_ptrs(addresses):
+    return [int(a) for a in addresses]
+
+
+def peer_lookup(maps, tables, world, map_len, table_rows, feat, dtype, ids, rows_out=None):
+    a = _np(ids)
+    n = a.shape[0]
+    dt = _NPDT[dtype]
+    rows = np.zeros((n, feat), dtype=dt)
+    hit = np.full(n, -1, dtype=np.int64)
+    ok = (a >= 0) & (a < map_len)
+    own = np.zeros(n, dtype=np.int64)
+    own[ok] = O.owner(a[ok], world)
+    for i in np.nonzero(ok)[0]:
+        slot = _at(maps[own[i]], map_len, np.int64)[a[i]]
+        if 0 <= slot < table_rows:
+            rows[i] = _at(tables[own[i]], table_rows * feat, dt).reshape(table_rows, feat)[slot]
+            hit[i] = i
+    return torch.from_numpy(hit), torch.from_numpy(rows)
+
+
+def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n, score=None, thres=None, present=None):
+    n = ids.shape[0]
+    take = torch.ones(n, dtype=torch.bool) if mask is None else mask.bool().clone()
+    if score is not None:
+        take &= score < thres
+    if present is not None:
+        take &= present == -1
+    pub_n[0] = n
+    pub_ids[:n] = torch.where(take, ids, torch.full_like(ids, -1))
+    pub_rows[:n][take] = rows[take].float()
+
+
+def make_shard(full_to_slot, slot_to_full, checkin, table, header, iter_dev, claim, staleness,
+               n_admitted=None):
+    return types.SimpleNamespace(full_to_slot=full_to_slot, slot_to_full=slot_to_full, checkin=checkin,
+                                 table=table, header=header, iter_dev=iter_dev, claim=claim,
+                                 staleness=int(staleness), n_admitted=n_admitted)
+
+
+def peer_admit(shard, pub_ids, pub_rows, pub_n, world, me, max_ids, got_ids, got_rows, overflow=None,
+               evict=True, advance_iter=False):
+    feat, cap = got_rows.shape[1], got_ids.shape[0]
+    if evict and shard.staleness > 0:
+        evict_stale_dev(shard.checkin, shard.slot_to_full, shard.full_to_slot, shard.iter_dev, shard.staleness)
+    cand_ids, cand_rows = [], []
+    for p in range(world):
+        n_p = int(np.clip(_at(pub_n[p], 1, np.int64)[0], 0, max_ids))
+        ids_p = _at(pub_ids[p], n_p, np.int64)
+        rows_p = _at(pub_rows[p], max_ids * feat, np.float32).reshape(max_ids, feat)[:n_p]
+        own = ids_p >= 0
+        own[own] = O.owner(ids_p[own], world) == me
+        cand_ids.append(ids_p[own].copy())
+        cand_rows.append(rows_p[own].copy())
+    cand_ids, cand_rows = np.concatenate(cand_ids), np.concatenate(cand_rows)
+    k = min(len(cand_ids), cap)
+    if overflow is not None and len(cand_ids) > cap:
+        overflow[0] += len(cand_ids) - cap
+    got_ids[:] = -1
+    got_ids[:k] = torch.from_numpy(cand_ids[:k])
+    got_rows[:k] = torch.from_numpy(cand_rows[:k])
+    winners = last_occurrence(got_ids, shard.claim)
+    present = map_lookup(shard.full_to_slot, got_ids)
+    record_history(got_rows, shard.table, winners, got_ids, present, shard.slot_to_full,
+                   shard.full_to_slot, shard.header, torch.zeros(cap), torch.zeros(1), shard.checkin,
+                   CHECKIN_MARKER, n_admitted=shard.n_admitted)
+    stamp_checkin(shard.checkin, shard.iter_dev)
+    if advance_iter:
+        shard.iter_dev += 1

@@ -81,12 +81,15 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2])
-def test_sharded_table_two_cpu_ranks(world, oracle):
+@pytest.mark.parametrize("world,kind", [(2, "a2a"), (2, "peer"), (3, "peer")])
+def test_sharded_table_two_cpu_ranks(world, kind, oracle):
+    """kind = a2a: the padded all-to-all exchange; peer: the exchange through memory the ranks
+    map from each other (here a file in /dev/shm per rank stands in for the device allocation)."""
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29700 + os.getpid() % 200
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q)) for r in range(world)]
+    port = 29700 + os.getpid() % 200 + (230 if kind == "peer" else 0) + world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q, "gloo", kind))
+             for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=240) for _ in procs]
@@ -94,7 +97,7 @@ def test_sharded_table_two_cpu_ranks(world, oracle):
         p.join(timeout=60)
     for rank, status, info in res:
         assert status == "ok", f"rank {rank}:\n{info}"
-    assert res[0][2] == res[1][2] > 0
+    assert all(r[2] == res[0][2] for r in res) and res[0][2] > 0
 
 
 def test_single_rank_equals_plain_ring(oracle):
