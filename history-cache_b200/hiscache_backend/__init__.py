@@ -27,7 +27,7 @@ import torch
 
 from . import _capi
 from ._capi import (HC_F16, HC_F32, HC_SCORE_L1, HC_SCORE_L2, AggrArgs, check, dtype_code, i64c,
-                    lib, ptr, require_cuda, rows2d, scratch, stream_of)
+                    lib, on_device, ptr, require_cuda, rows2d, scratch, stream_of)
 
 __all__ = [
     "record_history", "count_history_reconstruct", "count_num", "get_graph_structure_score",
@@ -175,7 +175,7 @@ class _AggrFunction(torch.autograd.Function):
         shape = (num_node, inp.shape[1], inp.shape[2]) if multi else (num_node, inp.shape[1])
         out = torch.empty(shape, dtype=torch.float32, device=dev)
         a = _aggr_args(inp, ptr_t, idx_t, num_node, edge_value, hmap, hbuf, h_indexed, src_map, src_alt)
-        with torch.cuda.device(dev), _span(_tag("hc_aggr_fwd", inp), dev):
+        with on_device(dev), _span(_tag("hc_aggr_fwd", inp), dev):
             check(lib.hc_aggr_fwd(C.byref(a), ptr(out), stream_of(dev)), "hc_aggr_fwd")
         _called()
         ctx.save_for_backward(inp, ptr_t, idx_t, edge_value, hmap, hbuf, src_map, src_alt)
@@ -206,7 +206,7 @@ class _AggrFunction(torch.autograd.Function):
                 and GATHER_MIN_FEAT <= inp.shape[1] <= 1024
                 and idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES):
             t_ptr, t_dst, t_w = transpose_block(PreparedAggr(a, None, dev, ""), idx_t.numel())
-            with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd_gather", inp), dev):
+            with on_device(dev), _span(_tag("hc_aggr_bwd_gather", inp), dev):
                 check(lib.hc_aggr_bwd_gather(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(grad_out),
                                              ptr(g_in), stream_of(dev)), "hc_aggr_bwd_gather")
             _called()
@@ -222,7 +222,7 @@ class _AggrFunction(torch.autograd.Function):
         if not (need_in or need_ev or need_h or score is not None):
             return (None,) * 12
         if not gathered or need_h or score is not None:
-            with torch.cuda.device(dev), _span(_tag("hc_aggr_bwd", inp), dev):
+            with on_device(dev), _span(_tag("hc_aggr_bwd", inp), dev):
                 check(lib.hc_aggr_bwd(C.byref(a), ptr(grad_out), None if gathered else ptr(g_in), 1,
                                       ptr(g_h), ptr(g_ev), ptr(score), ctx.score_kind, stream_of(dev)),
                       "hc_aggr_bwd")
@@ -316,7 +316,7 @@ def transpose_block(p: PreparedAggr, max_edges):
     t_dst = torch.empty(max(int(max_edges), 1), dtype=torch.int64, device=dev)
     t_w = torch.empty(max(int(max_edges), 1), dtype=torch.float32, device=dev)
     sc = scratch(dev, lib.hc_transpose_scratch_bytes(n_src), "transpose")
-    with torch.cuda.device(dev), _span("hc_transpose_block", dev):
+    with on_device(dev), _span("hc_transpose_block", dev):
         check(lib.hc_transpose_block(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(sc),
                                      stream_of(dev)), "hc_transpose_block")
     _called(7)
@@ -370,7 +370,7 @@ def score_rows(x, kind=HC_SCORE_L2, out=None):
     n, F = x.shape
     if out is None:
         out = torch.empty(n, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev), _span("hc_score_rows", dev):
+    with on_device(dev), _span("hc_score_rows", dev):
         check(lib.hc_score_rows(ptr(x), n, F, x.stride(0) if n > 1 else F, kind, ptr(out),
                                 stream_of(dev)), "hc_score_rows")
     _called()
@@ -385,7 +385,7 @@ def select_threshold(score, q, out=None, n_valid=None):
     score = score.contiguous()
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev), _span("hc_select_threshold", dev):
+    with on_device(dev), _span("hc_select_threshold", dev):
         if n_valid is None:
             check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
                                           stream_of(dev)), "hc_select_threshold")
@@ -425,7 +425,7 @@ def record_history(buffer_new, buffer_all, used_mask, sub_to_full, sub_to_histor
         raise RuntimeError("record_history: per-row arguments shorter than buffer_new")
     thres = thres.reshape(-1).float()
     sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
-    with torch.cuda.device(dev), _span("hc_record_history", dev):
+    with on_device(dev), _span("hc_record_history", dev):
         check(lib.hc_record_history(
             ptr(buffer_new), buffer_new.stride(0) if n > 1 else hs, n, ptr(buffer_all),
             dtype_code(buffer_all), buffer_all.shape[0], hs, ptr(used_mask),
@@ -474,7 +474,7 @@ def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, 
     n = produced.shape[0]
     sc = scratch(dev, lib.hc_admit_scratch_bytes(n), "admit")
     f2f_len = 0 if feat2full is None else feat2full.shape[0]
-    with torch.cuda.device(dev), _span("hc_cache_admit", dev):
+    with on_device(dev), _span("hc_cache_admit", dev):
         check(lib.hc_cache_admit(
             ptr(produced), produced.stride(0) if n > 1 else hidden, n, ptr(buffer),
             dtype_code(buffer), hidden, in_feat, embed_capacity, ptr(i64c(sub_to_full)),
@@ -487,7 +487,7 @@ def cache_admit(produced, buffer, hidden, in_feat, embed_capacity, sub_to_full, 
 def evict_stale(checkin_iter, history_to_full, full_to_history, glb_iter, limit):
     """hiscache/history_table.py:189-200."""
     dev = require_cuda(checkin_iter, history_to_full, full_to_history)
-    with torch.cuda.device(dev), _span("hc_evict_stale", dev):
+    with on_device(dev), _span("hc_evict_stale", dev):
         check(lib.hc_evict_stale(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
                                  checkin_iter.shape[0], int(glb_iter), int(limit),
                                  stream_of(dev)), "hc_evict_stale")
@@ -500,7 +500,7 @@ CHECKIN_MARKER = 1 << 60   # a glb_iter no iteration takes
 def evict_stale_dev(checkin_iter, history_to_full, full_to_history, iter_dev, limit):
     """evict_stale with the iteration number read from a device int64[1]."""
     dev = require_cuda(checkin_iter, history_to_full, full_to_history, iter_dev)
-    with torch.cuda.device(dev), _span("hc_evict_stale", dev):
+    with on_device(dev), _span("hc_evict_stale", dev):
         check(lib.hc_evict_stale_dev(ptr(checkin_iter), ptr(history_to_full), ptr(full_to_history),
                                      checkin_iter.shape[0], ptr(iter_dev), int(limit), stream_of(dev)),
               "hc_evict_stale_dev")
@@ -510,7 +510,7 @@ def evict_stale_dev(checkin_iter, history_to_full, full_to_history, iter_dev, li
 def stamp_checkin(checkin_iter, iter_dev, marker=CHECKIN_MARKER):
     """checkin_iter[checkin_iter == marker] = iter_dev[0]."""
     dev = require_cuda(checkin_iter, iter_dev)
-    with torch.cuda.device(dev), _span("hc_stamp_checkin", dev):
+    with on_device(dev), _span("hc_stamp_checkin", dev):
         check(lib.hc_stamp_checkin(ptr(checkin_iter), checkin_iter.shape[0], int(marker), ptr(iter_dev),
                                    stream_of(dev)), "hc_stamp_checkin")
     _called()
@@ -520,7 +520,7 @@ def evict_by_score(sub_to_history, score, thres, checkin_iter, history_to_full, 
     """hiscache/history_table.py:234-241."""
     dev = require_cuda(sub_to_history, score, thres, checkin_iter)
     n = min(sub_to_history.shape[0], score.shape[0])
-    with torch.cuda.device(dev), _span("hc_evict_by_score", dev):
+    with on_device(dev), _span("hc_evict_by_score", dev):
         check(lib.hc_evict_by_score(ptr(i64c(sub_to_history)), ptr(score.contiguous()),
                                     ptr(thres.reshape(-1)), n, ptr(checkin_iter),
                                     ptr(history_to_full), ptr(full_to_history), stream_of(dev)),
@@ -538,7 +538,7 @@ def count_history_reconstruct(ptr_t, idx_t, history_maps, num_node, num_seed, nu
     ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
     hm = None if _empty(history_maps) else i64c(history_maps, "history_maps")
     buf = torch.empty((num_layer + 1, num_node), dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev), _span("hc_used_masks", dev):
+    with on_device(dev), _span("hc_used_masks", dev):
         check(lib.hc_used_masks(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, ptr(hm),
                                 0 if hm is None else hm.shape[0], num_node, num_seed, num_layer,
                                 ptr(buf), stream_of(dev)), "hc_used_masks")
@@ -553,7 +553,7 @@ def get_graph_structure_score(ptr_t, idx_t, num_node, num_seed, num_layer):
     ptr_t, idx_t = i64c(ptr_t, "ptr"), i64c(idx_t, "idx")
     out = torch.empty(num_node, dtype=torch.int64, device=dev)
     sc = torch.empty(num_node, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_structure_score", dev):
+    with on_device(dev), _span("hc_structure_score", dev):
         check(lib.hc_structure_score(ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1, num_node,
                                      num_seed, num_layer, ptr(out), ptr(sc), stream_of(dev)),
               "hc_structure_score")
@@ -566,7 +566,7 @@ def count_num(arr, mmax):
     dev = require_cuda(arr)
     arr = i64c(arr, "arr")
     out = torch.empty(int(mmax) + 1, dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev), _span("hc_count_num", dev):
+    with on_device(dev), _span("hc_count_num", dev):
         check(lib.hc_count_num(ptr(arr), arr.shape[0], int(mmax), ptr(out), stream_of(dev)),
               "hc_count_num")
     _called()
@@ -583,7 +583,7 @@ def map_lookup(map_t, ids, offset=0, force_miss_below=0, out=None):
     n = ids.shape[0]
     if out is None:
         out = torch.empty(n, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_map_lookup", dev):
+    with on_device(dev), _span("hc_map_lookup", dev):
         check(lib.hc_map_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, int(offset),
                                 int(force_miss_below), ptr(out), stream_of(dev)), "hc_map_lookup")
     _called()
@@ -597,7 +597,7 @@ def gather_rows(table, rows, zero_missing=False, out_dtype=None):
     rows = i64c(rows, "rows")
     n, F = rows.shape[0], table.shape[1]
     out = torch.empty((n, F), dtype=out_dtype or table.dtype, device=dev)
-    with torch.cuda.device(dev), _span("hc_gather_rows", dev):
+    with on_device(dev), _span("hc_gather_rows", dev):
         check(lib.hc_gather_rows(ptr(table), dtype_code(table), table.shape[0],
                                  table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows), n,
                                  1 if zero_missing else 0, ptr(out), dtype_code(out), F,
@@ -628,7 +628,7 @@ def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=Non
         feat_cache = rows2d(feat_cache)
         cd, cr = dtype_code(feat_cache), feat_cache.shape[0]
         cs = feat_cache.stride(0) if cr > 1 else F
-    with torch.cuda.device(dev), _span("hc_load_rows", dev):
+    with on_device(dev), _span("hc_load_rows", dev):
         check(lib.hc_load_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
                                host_table.stride(0) if host_table.shape[0] > 1 else F,
                                ptr(feat_cache), cd, cr, cs, F, ptr(sub_to_full), ptr(sub2feat),
@@ -656,7 +656,7 @@ def bucket_by_owner(ids, world, keep=None):
     sc = scratch(dev, lib.hc_bucket_scratch_bytes(n, world), "bucket")
     if keep is not None:
         keep = keep.contiguous()
-    with torch.cuda.device(dev), _span("hc_bucket_by_owner", dev):
+    with on_device(dev), _span("hc_bucket_by_owner", dev):
         check(lib.hc_bucket_by_owner(ptr(ids), ptr(keep), n, world, ptr(counts), ptr(perm),
                                      ptr(bucketed), ptr(sc), stream_of(dev)), "hc_bucket_by_owner")
     _called(3)
@@ -668,7 +668,7 @@ def bucket_pad(bucketed, counts, world, slots, overflow=None, out=None):
     dev = require_cuda(bucketed, counts)
     if out is None:
         out = torch.empty((world, slots), dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_bucket_pad", dev):
+    with on_device(dev), _span("hc_bucket_pad", dev):
         check(lib.hc_bucket_pad(ptr(bucketed), ptr(counts), bucketed.shape[0], world, slots, ptr(out),
                                 ptr(overflow), stream_of(dev)), "hc_bucket_pad")
     _called()
@@ -681,7 +681,7 @@ def unpad_hits(perm, counts, world, slots, flags_back=None, want_slots=False):
     n = perm.shape[0]
     hit = torch.empty(n, dtype=torch.int64, device=dev) if flags_back is not None else None
     slot_of = torch.full((n,), -1, dtype=torch.int64, device=dev) if want_slots else None
-    with torch.cuda.device(dev), _span("hc_unpad_hits", dev):
+    with on_device(dev), _span("hc_unpad_hits", dev):
         check(lib.hc_unpad_hits(ptr(perm), ptr(counts), n, world, slots, ptr(flags_back), ptr(hit),
                                 ptr(slot_of), stream_of(dev)), "hc_unpad_hits")
     _called()
@@ -695,7 +695,7 @@ def last_occurrence(ids, claim):
     if claim.dtype != torch.int32:
         raise TypeError("claim must be int32")
     win = torch.empty(ids.shape[0], dtype=torch.uint8, device=dev)
-    with torch.cuda.device(dev), _span("hc_last_occurrence", dev):
+    with on_device(dev), _span("hc_last_occurrence", dev):
         check(lib.hc_last_occurrence(ptr(ids), ids.shape[0], ptr(claim), claim.shape[0], ptr(win),
                                      stream_of(dev)), "hc_last_occurrence")
     _called(3)
@@ -709,7 +709,7 @@ def unpermute_rows(src, perm, flags, dst, hit_out=None):
     F = 0 if src is None else src.shape[1]
     if flags is not None:
         flags = flags.contiguous()
-    with torch.cuda.device(dev), _span("hc_unpermute_rows", dev):
+    with on_device(dev), _span("hc_unpermute_rows", dev):
         check(lib.hc_unpermute_rows(ptr(src), HC_F32 if src is None else dtype_code(src),
                                     0 if src is None else (src.stride(0) if n > 1 else F), F,
                                     ptr(i64c(perm)), ptr(flags), n, ptr(dst),
@@ -727,7 +727,7 @@ def owner_lookup(map_t, ids, table, rows_out=None):
     F = table.shape[1]
     if rows_out is None:
         rows_out = torch.empty((n, F), dtype=table.dtype, device=dev)
-    with torch.cuda.device(dev), _span("hc_owner_lookup", dev):
+    with on_device(dev), _span("hc_owner_lookup", dev):
         check(lib.hc_owner_lookup(ptr(map_t), map_t.shape[0], ptr(ids), n, ptr(table),
                                   dtype_code(table), table.shape[0],
                                   table.stride(0) if table.shape[0] > 1 else F, F, ptr(rows_out),
@@ -815,7 +815,7 @@ def peer_lookup(maps, tables, world, map_len, table_rows, feat, dtype, ids, rows
     if rows_out is None:
         rows_out = torch.empty((n, feat), dtype=dtype, device=dev)
     hit = torch.empty(n, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_peer_lookup", dev):
+    with on_device(dev), _span("hc_peer_lookup", dev):
         check(lib.hc_peer_lookup(maps, tables, world, map_len, dtype_code(rows_out), table_rows, feat,
                                  feat, ptr(ids), n, ptr(rows_out), rows_out.stride(0) if n > 1 else feat,
                                  ptr(hit), stream_of(dev)), "hc_peer_lookup")
@@ -848,7 +848,7 @@ def peer_publish(ids, rows, mask, pub_ids, pub_rows, pub_n, score=None, thres=No
     F = pub_rows.shape[1]
     if n and rows.shape[1] != F:
         raise ValueError("peer_publish: row width differs from the published area")
-    with torch.cuda.device(dev), _span("hc_peer_publish", dev):
+    with on_device(dev), _span("hc_peer_publish", dev):
         check(lib.hc_peer_publish(ptr(ids), ptr(mask), ptr(score), ptr(thres), ptr(present), n, ptr(rows),
                                   rows.stride(0) if n > 1 else F, F,
                                   ptr(pub_ids), ptr(pub_rows), ptr(pub_n), pub_ids.shape[0],
@@ -862,7 +862,7 @@ def peer_pull(pub_ids, pub_rows, pub_n, world, me, max_ids, feat, got_ids, got_r
     dev = require_cuda(got_ids, got_rows, overflow)
     cap = got_ids.shape[0]
     sc = scratch(dev, int(lib.hc_peer_pull_scratch_bytes(world, max_ids)), "peer_pull")
-    with torch.cuda.device(dev), _span("hc_peer_pull", dev):
+    with on_device(dev), _span("hc_peer_pull", dev):
         check(lib.hc_peer_pull(pub_ids, pub_rows, pub_n, world, me, max_ids, feat, ptr(got_ids),
                                ptr(got_rows), cap, ptr(overflow), ptr(sc), stream_of(dev)), "hc_peer_pull")
     _called(3)
@@ -898,7 +898,7 @@ def peer_admit(shard, pub_ids, pub_rows, pub_n, world, me, max_ids, got_ids, got
     dev = require_cuda(got_ids, got_rows, overflow)
     cap = got_ids.shape[0]
     sc = scratch(dev, int(lib.hc_peer_admit_scratch_bytes(world, max_ids, cap)), "peer_admit")
-    with torch.cuda.device(dev), _span("hc_peer_admit", dev):
+    with on_device(dev), _span("hc_peer_admit", dev):
         check(lib.hc_peer_admit(C.byref(shard), pub_ids, pub_rows, pub_n, world, me, max_ids, ptr(got_ids),
                                 ptr(got_rows), cap, ptr(overflow), 1 if evict else 0,
                                 1 if advance_iter else 0, ptr(sc), stream_of(dev)), "hc_peer_admit")
@@ -918,13 +918,13 @@ def sample_hop(gptr, gidx, frontier, fanout, seed, base):
     frontier = i64c(frontier, "frontier")
     nf = frontier.shape[0]
     out_ptr = torch.zeros(nf + 1, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_sample_counts", dev):
+    with on_device(dev), _span("hc_sample_counts", dev):
         check(lib.hc_sample_counts(ptr(gptr), ptr(frontier), nf, int(fanout), ptr(out_ptr[1:]),
                                    stream_of(dev)), "hc_sample_counts")
     torch.cumsum(out_ptr[1:], 0, out=out_ptr[1:])
     total = int(out_ptr[-1]) if nf > 0 else 0
     nbr = torch.empty(total, dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev), _span("hc_sample_picks", dev):
+    with on_device(dev), _span("hc_sample_picks", dev):
         check(lib.hc_sample_picks(ptr(gptr), ptr(gidx), ptr(frontier), nf, int(fanout), ptr(out_ptr),
                                   C.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), int(base), ptr(nbr),
                                   stream_of(dev)), "hc_sample_picks")
@@ -957,7 +957,7 @@ def relabel(nbr, local_map, n_total):
     n_new = torch.zeros(1, dtype=torch.int64, device=dev)
     out_idx = torch.empty(m, dtype=torch.int64, device=dev)
     sc = scratch(dev, lib.hc_relabel_scratch_bytes(m), "relabel")
-    with torch.cuda.device(dev), _span("hc_relabel", dev):
+    with on_device(dev), _span("hc_relabel", dev):
         check(lib.hc_relabel(ptr(nbr), m, ptr(local_map), int(n_total), ptr(new_nodes), ptr(n_new),
                              ptr(out_idx), ptr(sc), stream_of(dev)), "hc_relabel")
     _called(6)

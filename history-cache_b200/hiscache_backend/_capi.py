@@ -155,7 +155,32 @@ def ptr(t):
 
 
 def stream_of(dev: torch.device):
-    return torch.cuda.current_stream(dev).cuda_stream
+    """Raw handle of torch's current stream on `dev` (the integer the C ABI takes)."""
+    idx = dev.index
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device() if idx is None else idx)
+
+
+class _Here:
+    """No-op context: the wanted device is already current."""
+    __slots__ = ()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_HERE = _Here()
+
+
+def on_device(dev: torch.device):
+    """Context that makes `dev` current for a library call; free when it already is (the
+    usual case with one process per GPU)."""
+    idx = dev.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _HERE
+    return torch.cuda.device(dev)
 
 
 def i64c(t, name="index"):
