@@ -240,6 +240,9 @@ extern "C" int hc_peer_alloc(int64_t bytes, void** ptr) {
   void* p = nullptr;
   HC_CUDA(cudaMalloc(&p, (size_t)bytes));
   cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+  // the fill runs on the legacy default stream; wait for it here, once, so that a caller
+  // working on a non-blocking stream never sees a region that is still being cleared
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     cudaFree(p);
     return (int)e;

@@ -283,7 +283,7 @@ class PeerHistoryTable:
         ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=self.device)
         dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
         if int(ok.item()) == 0:
-            self.close(collective=False)
+            self.close()      # every rank is here: unmap first, barrier, then free
             raise RuntimeError(f"PeerHistoryTable: peer memory is not available on this box ({err})")
         self.connect_raw(base)
 

@@ -126,3 +126,53 @@ def test_single_rank_equals_plain_ring(oracle):
         assert np.array_equal(table.slot_to_full.numpy(), h2f)
         assert np.array_equal(table.buffer.numpy(), buf)
         assert int(table.header[0]) == int(hdr[0])
+
+
+def _fail_worker(rank, world, port, q):
+    """Rank 1 cannot map rank 0's region (a fake of the failing call): every rank must see the
+    error, release what it mapped and stay usable for the all-to-all form."""
+    for p in (os.path.join(ROOT, "history-cache_b200"), os.path.join(ROOT, "oracle"), HERE):
+        sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import types
+        import _cpu_ops
+        from hiscache.sharded import PeerHistoryTable, ShardedHistoryTable
+        ops = types.SimpleNamespace(**{k: getattr(_cpu_ops, k) for k in dir(_cpu_ops) if not k.startswith("__")})
+        if rank == 1:
+            def broken(handle, device):
+                raise RuntimeError("peer access is not supported between these two devices")
+            ops.peer_open = broken
+        try:
+            PeerHistoryTable(500, 8, 64, device="cpu", ops=ops, max_ids=50)
+            q.put((rank, "fail", "no error raised"))
+            return
+        except RuntimeError as e:
+            assert "peer memory is not available" in str(e)
+        # the process group is still usable: the all-to-all form works right after
+        t = ShardedHistoryTable(500, 8, 64, device="cpu", ops=_cpu_ops, max_ids=50)
+        ids = torch.arange(rank * 50, rank * 50 + 50)
+        t.admit(ids, torch.ones(50, 8), torch.ones(50, dtype=torch.bool))
+        hit, _ = t.lookup(torch.arange(0, 100)[rank::2][:50])
+        assert bool((hit != -1).all())
+        q.put((rank, "ok", 0))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, "fail", traceback.format_exc()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_mapping_failure_is_seen_by_every_rank(oracle):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29100 + os.getpid() % 200
+    procs = [ctx.Process(target=_fail_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, status, info in res:
+        assert status == "ok", f"rank {rank}:\n{info}"
