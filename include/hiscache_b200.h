@@ -48,7 +48,7 @@ extern "C" {
 #define HC_ERR_ALIGN 4     /* pointer not aligned to its element type         */
 #define HC_ERR_UNSUPPORTED 5 /* combination of options not implemented        */
 #define HC_ERR_STRUCT 6    /* args->struct_size does not match this build     */
-#define HC_ERR_LIMIT 7     /* more rows than a fixed-scratch entry point takes */
+#define HC_ERR_LIMIT 7     /* more rows than a fixed-capacity entry point takes */
 
 /* score kinds */
 #define HC_SCORE_L2 0 /* sqrt(sum x^2): HistoryCache.update_history, history_cache.py:205 */

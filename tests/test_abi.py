@@ -60,3 +60,58 @@ def test_backend_refuses_cpu_tensors():
         hb.aggr_forward(x, p, i, 1)
     with pytest.raises(RuntimeError, match="CUDA"):
         hb.count_history_reconstruct(p, i, torch.tensor([]), 1, 1, 1)
+
+
+def _declared_arity():
+    """name -> number of parameters, parsed from the header's prototypes."""
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(hc_[a-z0-9_]+)\s*\(([^;{}]*?)\)\s*;", text, flags=re.S):
+        params = m.group(2).strip()
+        out[m.group(1)] = 0 if params in ("", "void") else params.count(",") + 1
+    return out
+
+
+def test_binding_arity_matches_the_header():
+    import hiscache_backend._capi as capi
+    arity = _declared_arity()
+    for name, (_res, args) in capi._SIGS.items():
+        assert arity[name] == len(args), f"{name}: header has {arity[name]} parameters, binding {len(args)}"
+
+
+def test_header_is_plain_c_and_struct_sizes_agree(tmp_path):
+    """The header compiles as C (it is what a cgo / JNI / ctypes host includes) and the structs
+    have the size the ctypes mirror assumes."""
+    import subprocess
+    import hiscache_backend._capi as capi
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include "hiscache_b200.h"\n'
+                   'int main(void){printf("%zu %zu\\n", sizeof(hc_aggr_args), sizeof(hc_shard));return 0;}\n')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)],
+                   check=True)
+    a, s = map(int, subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split())
+    assert a == ctypes.sizeof(capi.AggrArgs)
+    assert s == ctypes.sizeof(capi.Shard)
+
+
+def test_peer_entry_points_check_arguments_without_gpu():
+    import hiscache_backend._capi as capi
+    lib = capi.lib
+    two = (ctypes.c_void_p * 2)(16, 32)
+    # world out of range, NULL tables, bad struct, too many rows: all refused before any CUDA call
+    assert lib.hc_peer_lookup(two, two, 0, 10, 0, 4, 8, 8, None, 1, None, 8, None, None) == -2
+    assert lib.hc_peer_lookup(two, two, 33, 10, 0, 4, 8, 8, None, 1, None, 8, None, None) == -2
+    assert lib.hc_peer_lookup(two, two, 2, 10, 9, 4, 8, 8, None, 1, None, 8, None, None) == -3
+    assert lib.hc_peer_lookup(two, two, 2, 10, 0, 4, 8, 8, None, 0, None, 8, None, None) == 0   # n == 0
+    assert lib.hc_peer_lookup(None, two, 2, 10, 0, 4, 8, 8, None, 1, None, 8, None, None) == -1
+    assert lib.hc_peer_publish(None, None, None, None, None, 11, None, 8, 8, two, two, two, 10, None) == -7
+    assert lib.hc_peer_publish(None, None, None, None, None, 1, None, 8, 8, None, None, None, 10, None) == -1
+    sh = capi.Shard()
+    assert lib.hc_peer_admit(ctypes.byref(sh), two, two, two, 2, 0, 10, None, None, 4, None, 1, 1, two, None) == -6
+    assert lib.hc_peer_alloc(0, ctypes.byref(ctypes.c_void_p())) == -2
+    assert lib.hc_peer_export(None, None) == -1 and lib.hc_peer_open(None, None) == -1
+    assert lib.hc_peer_free(None) == 0 and lib.hc_peer_close(None) == 0
+    assert lib.hc_peer_pull_scratch_bytes(8, 16000) == (8 * 63 + 1) * 8
+    assert lib.hc_error_string(-7).startswith(b"hiscache_b200")
