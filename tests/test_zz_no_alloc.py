@@ -63,4 +63,4 @@ def test_noalloc_rejects_oversize(backend):
     rc = _capi.lib.hc_record_history_noalloc(None, 0, n, None, 0, 16, 4, None, None, None, None, None,
                                              None, None, None, None, 0, None, None)
     assert rc == -7
-    assert b"fixed-scratch" in _capi.lib.hc_error_string(rc)
+    assert b"hc_noalloc_max_rows" in _capi.lib.hc_error_string(rc)
