@@ -13,6 +13,7 @@ from .history_table import HistoryTable
 from .history_trainer import HistoryTableTrainer, HistoryTrainer
 from .multi_gpu_history_trainer import MultiGpuHistoryTrainer
 from .sampler import get_loader
+from .sharded import PeerHistoryTable, ShardedHistoryTable
 from .util import Config, make_config
 
 __all__ = [
@@ -20,4 +21,5 @@ __all__ = [
     "get_graph_structure_score", "record_history", "get_model", "MultiGpuHistoryTrainer",
     "all2all", "all2allnaive", "all2all_prealloc", "all2allnaive_prealloc", "prepare_transfer",
     "post_transfer", "HostFeatureStore", "HistoryTableTrainer", "get_loader", "Config", "make_config",
+    "PeerHistoryTable", "ShardedHistoryTable",
 ]
