@@ -417,7 +417,7 @@ def measure_h2d_peak(device):
 
 
 def large_block_roofline(device, peak, measured):
-    """The same aggregation kernels on blocks larger than L2 (history-cache_b200/kernel_bench.py):
+    """The same aggregation kernels on blocks larger than L2 (kernel_bench.py):
     forward fp16 dim 128, 2 M destination rows x 10 neighbours from 16 M source rows; backward
     fp32 dim 256, 1 M rows x 10 neighbours into 4 M source rows."""
     import kernel_bench as kb

@@ -263,7 +263,11 @@ class Loader:
         self.batch_size = int(batch_size)
         ids = graph.train_ids
         self.train_ids = ids[rank::world] if world > 1 else ids
-        self.iters_per_epoch = iters_per_epoch or max(1, math.ceil(self.train_ids.shape[0] / self.batch_size))
+        # derived from the GLOBAL training set, so that every rank runs the same number of
+        # iterations (and therefore issues the same number of collectives) whatever the
+        # remainder of len(train_ids) / world is
+        self.iters_per_epoch = iters_per_epoch or max(
+            1, math.ceil(math.ceil(ids.shape[0] / max(world, 1)) / self.batch_size))
         self._gen = torch.Generator(device=graph.device)
         self._gen.manual_seed(int(seed) * 7919 + rank)
 

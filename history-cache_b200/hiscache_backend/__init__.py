@@ -453,6 +453,24 @@ def record_history_noalloc(buffer_new, buffer_all, used_mask, sub_to_full, sub_t
             raise RuntimeError("record_history_noalloc: arguments must be contiguous")
     if buffer_new.dtype != torch.float32 or score.dtype != torch.float32 or thres.dtype != torch.float32:
         raise TypeError("record_history_noalloc: rows, score and thres must be float32")
+    # the same argument checks as record_history (comparisons only, nothing is allocated):
+    # a narrower table or 32-bit maps would otherwise be read out of bounds on the device
+    if buffer_all.dim() != 2 or buffer_all.shape[1] != hs:
+        raise RuntimeError("record_history_noalloc: row widths differ")
+    for name, t in (("sub_to_full", sub_to_full), ("sub_to_history", sub_to_history),
+                    ("history_to_full", history_to_full), ("full_to_history", full_to_history),
+                    ("header", header), ("checkin_iter", checkin_iter)):
+        if t.dtype != torch.int64:
+            raise TypeError(f"record_history_noalloc: {name} must be int64")
+    if used_mask is not None:
+        if used_mask.dtype not in (torch.bool, torch.uint8) or not used_mask.is_contiguous():
+            raise TypeError("record_history_noalloc: used_mask must be contiguous bool")
+        if used_mask.shape[0] < n:
+            raise RuntimeError("record_history_noalloc: used_mask shorter than buffer_new")
+    if sub_to_full.shape[0] < n or sub_to_history.shape[0] < n or score.shape[0] < n:
+        raise RuntimeError("record_history_noalloc: per-row arguments shorter than buffer_new")
+    if history_to_full.shape[0] < buffer_all.shape[0] or checkin_iter.shape[0] < buffer_all.shape[0]:
+        raise RuntimeError("record_history_noalloc: slot arrays shorter than the table")
     with torch.cuda.device(dev):
         check(lib.hc_record_history_noalloc(
             ptr(buffer_new), hs, n, ptr(buffer_all), dtype_code(buffer_all), buffer_all.shape[0], hs,

@@ -1,6 +1,6 @@
 """Micro-benchmark of the libhiscache_b200 kernels on synthetic blocks.
 
-    python history-cache_b200/kernel_bench.py --op fwd --dst 2000000 --deg 10 --src 16000000 \
+    python kernel_bench.py --op fwd --dst 2000000 --deg 10 --src 16000000 \
         --feat 128 --dtype f16 --reps 10
 
 Prints one JSON line per run: achieved GB/s computed from the ALGORITHMIC bytes of the
@@ -15,7 +15,7 @@ import json
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "history-cache_b200"))
 
 import torch  # noqa: E402
 

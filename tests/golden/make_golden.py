@@ -266,7 +266,8 @@ def gen_invalidate(ref, seed, out):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("HISCACHE_REFERENCE"), required="HISCACHE_REFERENCE" not in os.environ,
+                    help="root of the upstream history-cache checkout")
     args = ap.parse_args()
     O.build()
     HistoryCache, HistoryTable = load_reference(args.ref)

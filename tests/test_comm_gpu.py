@@ -5,7 +5,6 @@ import os
 
 import pytest
 import torch
-import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
@@ -37,26 +36,22 @@ def _rank(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    try:
+    def body():
         from hiscache import all2all
         send = [torch.full((2 + rank + d, 3), float(10 * rank + d), device="cuda") for d in range(world)]
         got = all2all(send)
-        ok = all(got[s].shape == (2 + s + rank, 3) and bool((got[s] == 10 * s + rank).all()) for s in range(world))
-        q.put((rank, ok))
-    finally:
-        dist.destroy_process_group()
+        assert all(got[s].shape == (2 + s + rank, 3) and bool((got[s] == 10 * s + rank).all())
+                   for s in range(world))
+        return True
+
+    sys.path.insert(0, here)
+    from _mp import report_and_exit
+    report_and_exit(q, rank, body)
+    dist.destroy_process_group()
 
 
 def test_all2all_one_process_per_gpu():
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = 29300 + os.getpid() % 100
-    ps = [ctx.Process(target=_rank, args=(r, 2, port, q)) for r in range(2)]
-    for p in ps:
-        p.start()
-    res = [q.get(timeout=240) for _ in ps]
-    for p in ps:
-        p.join(timeout=60)
-    assert all(ok for _, ok in res)
+    from _mp import run_ranks
+    assert all(run_ranks(_rank, 2, (29300 + os.getpid() % 100,), timeout=240))

@@ -8,7 +8,6 @@ import sys
 import numpy as np
 import pytest
 import torch
-import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
 
@@ -25,7 +24,8 @@ def _train_worker(rank, world, port, exchange, q):
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    try:
+
+    def body():
         from hiscache import HostFeatureStore, MultiGpuHistoryTrainer, make_config
         from hiscache.sampler import SyntheticGraph
         N, feat = 60_000, 64
@@ -59,28 +59,18 @@ def _train_worker(rank, world, port, exchange, q):
         res = dict(losses=losses, hits=hits, same=same, owned=owned, params=flat.cpu().numpy(),
                    overflow=tr.table.table.overflow_count, header=tr.table.header)
         tr.table.table.close()
-        q.put((rank, "ok", res))
-    except Exception:  # noqa: BLE001
-        import traceback
-        q.put((rank, "fail", traceback.format_exc()))
-    finally:
-        dist.destroy_process_group()
+        return res
+
+    sys.path.insert(0, HERE)
+    from _mp import report_and_exit
+    report_and_exit(q, rank, body)
+    dist.destroy_process_group()
 
 
 def _run(world, exchange, port):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    procs = [ctx.Process(target=_train_worker, args=(r, world, port, exchange, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-    out = {}
-    for rank, status, info in res:
-        assert status == "ok", f"rank {rank} ({exchange}):\n{info}"
-        out[rank] = info
-    return [out[r] for r in range(world)]
+    sys.path.insert(0, HERE)
+    from _mp import run_ranks
+    return run_ranks(_train_worker, world, (port, exchange), timeout=300)
 
 
 def _check(runs):

@@ -26,7 +26,7 @@ def _inputs(step, rank, N, n, hidden):
     return ids, rows, mask
 
 
-def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo", kind="a2a"):
+def _worker(rank, world, port, N, n, hidden, steps, staleness, backend, kind, q):
     for p in (os.path.join(ROOT, "history-cache_b200"), os.path.join(ROOT, "oracle"), HERE):
         sys.path.insert(0, p)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -39,7 +39,7 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
         dist.init_process_group("gloo", rank=rank, world_size=world)
         import _cpu_ops
         dev, ops = torch.device("cpu"), _cpu_ops
-    try:
+    def body():
         from hiscache.sharded import PeerHistoryTable, ShardedHistoryTable
         cls = PeerHistoryTable if kind == "peer" else ShardedHistoryTable
         table = cls(N, hidden, capacity=4096, device=dev, ops=ops, staleness=staleness, max_ids=n)
@@ -73,31 +73,21 @@ def _worker(rank, world, port, N, n, hidden, steps, staleness, q, backend="gloo"
             assert have == mine, f"rank {rank} step {t}: owned set differs"
         assert table.overflow_count == 0
         table.close()
-        q.put((rank, "ok", len(logical)))
-    except Exception as e:  # noqa: BLE001
-        import traceback
-        q.put((rank, "fail", traceback.format_exc()))
-    finally:
-        dist.destroy_process_group()
+        return len(logical)
+
+    from _mp import report_and_exit
+    report_and_exit(q, rank, body)
+    dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world,kind", [(2, "a2a"), (2, "peer"), (3, "peer")])
 def test_sharded_table_two_cpu_ranks(world, kind, oracle):
     """kind = a2a: the padded all-to-all exchange; peer: the exchange through memory the ranks
     map from each other (here a file in /dev/shm per rank stands in for the device allocation)."""
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
+    from _mp import run_ranks
     port = 29700 + os.getpid() % 200 + (230 if kind == "peer" else 0) + world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q, "gloo", kind))
-             for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=240) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-    for rank, status, info in res:
-        assert status == "ok", f"rank {rank}:\n{info}"
-    assert all(r[2] == res[0][2] for r in res) and res[0][2] > 0
+    res = run_ranks(_worker, world, (port, 3000, 400, 8, 7, 3, "gloo", kind), timeout=240)
+    assert all(r == res[0] for r in res) and res[0] > 0
 
 
 def test_single_rank_equals_plain_ring(oracle):
@@ -135,7 +125,7 @@ def _fail_worker(rank, world, port, q):
         sys.path.insert(0, p)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    try:
+    def body():
         import types
         import _cpu_ops
         from hiscache.sharded import PeerHistoryTable, ShardedHistoryTable
@@ -146,8 +136,7 @@ def _fail_worker(rank, world, port, q):
             ops.peer_open = broken
         try:
             PeerHistoryTable(500, 8, 64, device="cpu", ops=ops, max_ids=50)
-            q.put((rank, "fail", "no error raised"))
-            return
+            raise AssertionError("no error raised")
         except RuntimeError as e:
             assert "peer memory is not available" in str(e)
         # the process group is still usable: the all-to-all form works right after
@@ -156,23 +145,25 @@ def _fail_worker(rank, world, port, q):
         t.admit(ids, torch.ones(50, 8), torch.ones(50, dtype=torch.bool))
         hit, _ = t.lookup(torch.arange(0, 100)[rank::2][:50])
         assert bool((hit != -1).all())
-        q.put((rank, "ok", 0))
-    except Exception:  # noqa: BLE001
-        import traceback
-        q.put((rank, "fail", traceback.format_exc()))
-    finally:
-        dist.destroy_process_group()
+        return 0
+
+    from _mp import report_and_exit
+    report_and_exit(q, rank, body)
+    dist.destroy_process_group()
 
 
 def test_peer_mapping_failure_is_seen_by_every_rank(oracle):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = 29100 + os.getpid() % 200
-    procs = [ctx.Process(target=_fail_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=240) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-    for rank, status, info in res:
-        assert status == "ok", f"rank {rank}:\n{info}"
+    from _mp import run_ranks
+    run_ranks(_fail_worker, 2, (29100 + os.getpid() % 200,), timeout=240)
+
+
+def test_every_rank_runs_the_same_number_of_iterations():
+    """The ranks of a data-parallel run issue one set of collectives per iteration, so an epoch
+    must have the same length on every rank even when the training set does not divide evenly."""
+    from hiscache.sampler import Loader, SyntheticGraph
+    graph = SyntheticGraph(5000, 6.0, 2.0, 7, seed=3, device="cpu", num_train=2001)
+    for world in (2, 3, 8):
+        loaders = [Loader(graph, [3, 2], 1000, "history_uvm", seed=0, rank=r, world=world) for r in range(world)]
+        counts = {l.iters_per_epoch for l in loaders}
+        assert len(counts) == 1, f"world {world}: {counts}"
+        assert sum(1 for _ in loaders[-1].train_loader) == loaders[0].iters_per_epoch

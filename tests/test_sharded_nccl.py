@@ -4,7 +4,6 @@ import os
 
 import pytest
 import torch
-import torch.multiprocessing as mp
 
 from test_sharded_gloo import _worker
 
@@ -16,16 +15,6 @@ def test_sharded_table_two_gpus(kind):
     """kind = a2a: padded all-to-alls; peer: the owners' memory is read directly (CUDA IPC)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    world = 2
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
+    from _mp import run_ranks
     port = 29500 + os.getpid() % 150 + (200 if kind == "peer" else 0)
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 3000, 400, 8, 7, 3, q, "nccl", kind))
-             for r in range(world)]
-    for p in procs:
-        p.start()
-    res = [q.get(timeout=300) for _ in procs]
-    for p in procs:
-        p.join(timeout=60)
-    for rank, status, info in res:
-        assert status == "ok", f"rank {rank}:\n{info}"
+    run_ranks(_worker, 2, (port, 3000, 400, 8, 7, 3, "nccl", kind), timeout=300)

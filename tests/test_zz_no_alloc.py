@@ -64,3 +64,32 @@ def test_noalloc_rejects_oversize(backend):
                                              None, None, None, None, 0, None, None)
     assert rc == -7
     assert b"hc_noalloc_max_rows" in _capi.lib.hc_error_string(rc)
+
+
+def test_noalloc_wrapper_rejects_bad_arguments_before_launching(backend):
+    """A table of another width or 32-bit maps must raise in the wrapper; nothing is launched."""
+    dev = "cuda"
+    n, hs, cap, N = 64, 16, 128, 1000
+    mk = lambda: dict(
+        buffer_new=torch.zeros(n, hs, device=dev), buffer_all=torch.zeros(cap, hs, device=dev),
+        used_mask=torch.ones(n, dtype=torch.bool, device=dev),
+        sub_to_full=torch.arange(n, device=dev), sub_to_history=torch.full((n,), -1, device=dev),
+        history_to_full=torch.full((cap,), -1, device=dev), full_to_history=torch.full((N,), -1, device=dev),
+        header=torch.zeros(1, dtype=torch.int64, device=dev), score=torch.zeros(n, device=dev),
+        thres=torch.zeros(1, device=dev), checkin_iter=torch.full((cap,), -1, device=dev), glb_iter=0)
+    before = backend.launch_count()
+    bad = mk()
+    bad["buffer_all"] = torch.zeros(cap, hs // 2, device=dev)
+    with pytest.raises(RuntimeError, match="row widths"):
+        backend.record_history_noalloc(**bad)
+    bad = mk()
+    bad["sub_to_full"] = bad["sub_to_full"].int()
+    with pytest.raises(TypeError, match="sub_to_full"):
+        backend.record_history_noalloc(**bad)
+    bad = mk()
+    bad["score"] = bad["score"][: n - 1]
+    with pytest.raises(RuntimeError, match="shorter"):
+        backend.record_history_noalloc(**bad)
+    assert backend.launch_count() == before
+    backend.record_history_noalloc(**mk())      # the well-formed call goes through
+    torch.cuda.synchronize()
