@@ -35,6 +35,10 @@ sys.path.insert(0, os.path.join(ROOT, "history-cache_b200"))
 import torch  # noqa: E402
 
 
+GRAPH_BY_DEFAULT = False    # what --graph auto means
+EST_STEP_S = 2.0e-3         # a step takes about this long (sizes the number of repeated regions)
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -56,10 +60,15 @@ def parse():
     ap.add_argument("--cpu-steps", type=int, default=3)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-large-block", action="store_true")
-    ap.add_argument("--graph", default="off", choices=["on", "off"],
-                    help="one GPU only: replay the whole step as one CUDA graph over fixed-shape "
-                         "(padded) batches.  Off by default: the step is GPU-bound and the padding "
-                         "costs more than the launches save (458 vs 494 iters/s)")
+    ap.add_argument("--graph", default=os.environ.get("HC_BENCH_GRAPH", "auto"), choices=["auto", "on", "off"],
+                    help="replay the step from CUDA graphs over fixed-shape (padded) batches: one graph on "
+                         "one GPU, two captured segments around the eager gradient all-reduce on several")
+    ap.add_argument("--graph-slack", type=float, default=1.0,
+                    help="fixed shape = this factor x the largest layer sizes of --graph-calibrate probe batches")
+    ap.add_argument("--graph-calibrate", type=int, default=64)
+    ap.add_argument("--min-timed-s", type=float, default=2.0,
+                    help="the K-step region is repeated until about this much has been timed")
+    ap.add_argument("--max-repeats", type=int, default=50)
     ap.add_argument("--exchange", default=os.environ.get("HC_EXCHANGE", "auto"), choices=["auto", "peer", "nccl"],
                     help="multi-GPU history exchange: peer memory (CUDA IPC + NVLink loads) or padded "
                          "all-to-alls; auto = peer memory when every rank can map every other")
@@ -80,7 +89,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -176,9 +185,88 @@ def conv0_bytes(batch, feat, elem):
     return e * feat * elem + n_d * feat * 4 + 8 * (n_d + 1 + e)
 
 
+def _region(trainer, batches, world, device, barrier, feed=None):
+    """Times one region of len(batches) steps: barrier + synchronize on both sides, CUDA events on
+    the training stream.  Returns (device ms, host issue ms, losses or None)."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    if feed is None:
+        for b in batches:
+            trainer.train_step(b)
+        losses = None
+    else:
+        losses = feed(batches)
+    e1.record()
+    t_issue = (time.perf_counter() - t0) * 1e3
+    barrier()
+    return e0.elapsed_time(e1), t_issue, losses
+
+
+def exchange_check(trainer, device, rank, world, seed):
+    """Outside every timed region, world > 1 only.  (1) the replicas hold bit-identical
+    parameters; (2) no id was dropped by a full exchange bucket; (3) two fresh tables, one per
+    form of the exchange (peer memory / padded all-to-alls), fed the same admissions by every
+    rank, answer K fresh lookups with the same hit set and the same rows, bit for bit."""
+    import torch.distributed as dist
+    from hiscache.sharded import PeerHistoryTable, ShardedHistoryTable
+    flat = torch.cat([p.detach().reshape(-1) for p in trainer.model.parameters()])
+    # checksum of the raw bits (order-sensitive weights), compared across ranks
+    bits = flat.view(torch.int32).to(torch.int64)
+    w = torch.arange(1, bits.numel() + 1, device=device, dtype=torch.int64) % 1000003
+    chk = torch.stack([(bits * w).sum(), bits.sum()])
+    both = [torch.empty_like(chk) for _ in range(world)]
+    dist.all_gather(both, chk)
+    replicas_identical = all(torch.equal(both[0], x) for x in both)
+    ovf = torch.tensor([trainer.table.table.overflow_count], dtype=torch.int64, device=device)
+    dist.all_reduce(ovf)
+    res = {"replicas_identical": bool(replicas_identical), "ids_dropped_by_overflow": int(ovf.item())}
+    ok = replicas_identical and int(ovf.item()) == 0
+    if trainer.table.exchange == "peer":
+        N, hidden, cap, n = 2_000_000, 256, 1 << 16, 4096
+        kw = dict(dtype=torch.float16, device=device, staleness=3, max_ids=n)
+        peer = PeerHistoryTable(N, hidden, cap, **kw)
+        a2a = ShardedHistoryTable(N, hidden, cap, slots=n, **kw)
+        g = torch.Generator(device=device)
+        g.manual_seed(seed * 7919 + 13 * rank + 5)
+        rounds, lookups, same_hits, same_rows, n_hits = 6, 4, True, True, 0
+        pool = torch.randint(0, 40_000, (rounds + lookups, n), generator=g, device=device)  # colliding ids
+        for t in range(rounds):
+            ids = torch.unique(pool[t])
+            rows = torch.randn((ids.shape[0], hidden), generator=g, device=device)
+            mask = torch.rand(ids.shape[0], generator=g, device=device) < 0.6
+            for tab in (peer, a2a):
+                tab.evict_stale()
+                tab.admit(ids, rows, mask)
+                tab.tick()
+        for t in range(lookups):
+            ids = torch.unique(pool[rounds + t])
+            hp, rp = peer.lookup(ids)
+            ha, ra = a2a.lookup(ids)
+            hit_p, hit_a = hp != -1, ha != -1
+            same_hits &= bool(torch.equal(hit_p, hit_a))
+            both_hit = hit_p & hit_a
+            n_hits += int(both_hit.sum())
+            same_rows &= bool(torch.equal(rp[hp[both_hit]], ra[ha[both_hit]]))
+        flag = torch.tensor([int(same_hits), int(same_rows), n_hits, peer.overflow_count + a2a.overflow_count],
+                            dtype=torch.int64, device=device)
+        mn = flag.clone()
+        dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        dist.all_reduce(flag, op=dist.ReduceOp.SUM)
+        peer.close()
+        res.update({"peer_vs_all2all": {"hit_sets_equal": bool(mn[0].item()), "rows_bit_equal": bool(mn[1].item()),
+                                        "hits_compared": int(flag[2].item()), "overflow": int(flag[3].item()),
+                                        "rounds": rounds, "lookups": lookups, "ids_per_rank": n}})
+        ok = ok and bool(mn[0].item()) and bool(mn[1].item()) and int(flag[2].item()) > 0 and int(flag[3].item()) == 0
+    res["ok"] = bool(ok)
+    return res
+
+
 def run_ours(args):
     import torch.distributed as dist
     import hiscache_backend as hb
+    from hiscache.pipeline import HostBatchPipeline
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
@@ -199,29 +287,6 @@ def run_ours(args):
                                  storage_dtype=torch.float16, seed=args.seed)
     trainer.model.train()
 
-    # pre-sampled batches: the loader's job in the reference (asynchronous sampler threads).
-    # With the CUDA-graph step they are sampled into one fixed shape (padded layers).
-    total = args.warmup + args.steps
-    use_graph = args.graph == "on" and world == 1
-    caps = ecap = None
-    if use_graph:
-        caps, ecap = loader.calibrate(32)
-        it = loader.iterate_padded(1 << 30, caps, ecap)
-    else:
-        it = loader.train_loader
-    for _ in range(3):          # first calls load the library's device code
-        next(it)
-    torch.cuda.synchronize()
-    t0 = time.time()
-    batches = [next(it) for _ in range(total)]
-    torch.cuda.synchronize()
-    t_sample = (time.time() - t0) / total
-    host_batches = [b.pin() for b in batches]
-    n_fixed = sum(1 for b in batches if b.mask is not None)
-    if use_graph:
-        warm = [b for b in batches if b.mask is not None][:3]
-        trainer.enable_cuda_graph(caps, ecap, warm)
-
     def barrier():
         if world > 1:
             dist.barrier()
@@ -234,111 +299,189 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    # ---- warm-up (also brings the history table to steady state: >= 2 x staleness)
-    for b in batches[:args.warmup]:
+    # ---- pre-sampled batches: the loader's job in the reference (asynchronous sampler threads).
+    # K steps take a few tens of milliseconds, too little to read a 5 % effect from, so the K-step
+    # region is repeated (fresh batches each time) until about --min-timed-s have been timed;
+    # `value` is the median region.
+    K = args.steps
+    use_graph = args.graph == "on" or (args.graph == "auto" and GRAPH_BY_DEFAULT)
+    caps = ecap = None
+    if use_graph:
+        caps, ecap = loader.calibrate(args.graph_calibrate, slack=args.graph_slack, align=128)
+        it = loader.iterate_padded(1 << 30, caps, ecap)
+    else:
+        it = loader.train_loader
+    for _ in range(3):          # first calls load the library's device code
+        next(it)
+    torch.cuda.synchronize()
+    t0 = time.time()
+    probe = [next(it) for _ in range(8)]
+    torch.cuda.synchronize()
+    t_sample = (time.time() - t0) / len(probe)
+    repeats = int(min(args.max_repeats, max(1, round(args.min_timed_s / max(K * EST_STEP_S, 1e-4)))))
+    total = args.warmup + K * repeats
+    batches = probe + [next(it) for _ in range(total - len(probe))] if total > len(probe) else probe[:total]
+    torch.cuda.synchronize()
+    host_batches = [b.pin() for b in batches]
+    n_fixed = sum(1 for b in batches if b.mask is not None)
+
+    # ---- warm-up (also brings the history table to steady state: >= 2 x staleness).  With the
+    # captured step the first warm-up steps run eagerly (the capture needs an active history).
+    n_eager_warm = min(args.warmup, max(2, args.staleness // 2)) if use_graph else args.warmup
+    for b in batches[:n_eager_warm]:
         trainer.train_step(b)
+    if use_graph:
+        warm = [b for b in batches if b.mask is not None][:2]
+        if len(warm) < 2:      # every rank must run the same number of warm-up steps (collectives)
+            raise RuntimeError("no batch fits the fixed shape; raise --graph-slack")
+        trainer.enable_cuda_graph(caps, ecap, warm)
+        for b in batches[n_eager_warm:args.warmup]:
+            trainer.train_step(b)
     barrier()
+    timed = [batches[args.warmup + r * K: args.warmup + (r + 1) * K] for r in range(repeats)]
+    timed_host = [host_batches[args.warmup + r * K: args.warmup + (r + 1) * K] for r in range(repeats)]
 
     # ---- timed: value (batches resident in HBM)
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     trainer.table.load_stats.zero_()
-    dominant = f"hc_aggr_fwd[f16,F={args.feat}]"
-    prof = hb.KernelTimer(only=dominant)   # only the dominant kernel is bracketed by events here
-    hb.set_kernel_timer(prof)
     l0 = hb.launch_count()
-    barrier()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for b in batches[args.warmup:]:
-        trainer.train_step(b)
-    ev1.record()
-    barrier()
-    ms = max_over_ranks(ev0.elapsed_time(ev1))
-    launches = hb.launch_count() - l0
+    reg_ms, reg_issue = [], []
+    for r in range(repeats):
+        ms_r, issue_r, _ = _region(trainer, timed[r], world, device, barrier)
+        reg_ms.append(max_over_ranks(ms_r))
+        reg_issue.append(max_over_ranks(issue_r))
+    ms = statistics.median(reg_ms)
+    launches = (hb.launch_count() - l0) / repeats
     if use_graph:   # replayed kernels are not seen by the Python-side counter
         launches += trainer.graphed.library_kernels_per_step * sum(
-            1 for b in batches[args.warmup:] if trainer.graphed.fits(b))
-    hb.set_kernel_timer(None)
-    kt = prof.summary()
+            1 for b in timed[0] if trainer.graphed.fits(b))
     stats = trainer.table.load_stats.tolist()
 
-    # ---- timed: e2e (batch structures from pinned host memory, loss read back every step)
-    h2d = sum(b.nbytes() for b in host_batches[args.warmup:]) / args.steps
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    loss_sum = 0.0
-    for hbatch in host_batches[args.warmup:]:
-        # a fixed-shape batch goes from pinned host memory straight into the graph's input buffers
-        b = hbatch if (use_graph and trainer.graphed.fits(hbatch)) else hbatch.to(device, non_blocking=True)
-        loss = trainer.train_step(b)
-        loss_sum += float(loss.item())   # device -> host read of the step's result
-    e1.record()
-    barrier()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1))
+    # ---- timed: e2e.  Every step copies its batch structures from page-locked host memory and
+    # reads its loss back to the host; both are pipelined (hiscache/pipeline.py): the copy of batch
+    # k+1 runs on a second stream during step k, the loss of step k is read one step later.
+    h2d = sum(b.nbytes() for hbs in timed_host for b in hbs) / (K * repeats)
+    pipe = HostBatchPipeline(trainer, host_batches)
+    e2e_ms, losses_all = [], []
+    for r in range(repeats):
+        ms_r, _, losses = _region(trainer, timed_host[r], world, device, barrier, feed=pipe.run)
+        e2e_ms.append(max_over_ranks(ms_r))
+        losses_all += losses
+    ms_e2e = statistics.median(e2e_ms)
+    # the same with the copy and the read-back inline (blocking), for comparison
+    def blocking(hbs):
+        out = []
+        for hbatch in hbs:
+            out.append(float(trainer.train_step(hbatch.to(device, non_blocking=True)).item()))
+        return out
+    blk_ms = []
+    for r in range(min(repeats, 5)):
+        ms_r, _, _ = _region(trainer, timed_host[r], world, device, barrier, feed=blocking)
+        blk_ms.append(max_over_ranks(ms_r))
     clocks = sampler.stop()
 
     # ---- the same step with the batch sampled inside it (hc_sample_* / hc_relabel kernels)
-    n_samp = min(args.steps, 30)
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(n_samp):
-        trainer.train_step(next(it))
-    s1.record()
-    barrier()
-    ms_samp = max_over_ranks(s0.elapsed_time(s1))
+    n_samp = min(K, 30)
+    ms_samp, _, _ = _region(trainer, [None] * n_samp, world, device, barrier,
+                            feed=lambda xs: [trainer.train_step(next(it)) for _ in xs])
+    ms_samp = max_over_ranks(ms_samp)
 
     # ---- untimed pass with every library call bracketed by events: per-kernel table
     full = hb.KernelTimer()
     hb.set_kernel_timer(full)
-    n_prof = min(args.steps, 20)
-    graphed, trainer.graphed = trainer.graphed, None      # eager, so that each call can be bracketed
-    for b in batches[args.warmup:args.warmup + n_prof]:
+    n_prof = min(K, 20)
+    if trainer.graphed is not None:
+        trainer.graphed.enabled = False      # eager, so that each call can be bracketed
+    ar0 = [torch.cuda.Event(enable_timing=True) for _ in range(n_prof)]
+    ar1 = [torch.cuda.Event(enable_timing=True) for _ in range(n_prof)]
+    if world > 1 and n_prof:
+        orig_reduce = trainer._reduce_flat
+        step_no = [0]
+
+        def timed_reduce():
+            ar0[step_no[0]].record()
+            orig_reduce()
+            ar1[step_no[0]].record()
+            step_no[0] += 1
+        trainer._reduce_flat = timed_reduce
+    for b in timed[0][:n_prof]:
         trainer.train_step(b)
-    trainer.graphed = graphed
+    torch.cuda.synchronize()
+    if world > 1 and n_prof:
+        trainer._reduce_flat = orig_reduce
+    if trainer.graphed is not None:
+        trainer.graphed.enabled = True
     hb.set_kernel_timer(None)
-    kt_all = full.summary()
-    if use_graph:
-        kt = kt_all   # inside a replayed graph single kernels cannot be bracketed by events
+    kt_all = full.summary() if n_prof else {}
+    allreduce_ms = (sum(a.elapsed_time(b) for a, b in zip(ar0, ar1)) / n_prof) if (world > 1 and n_prof) else None
     host_link_peak = measure_h2d_peak(device)
 
     # host-link bytes per step: rows read from host memory by the load kernel
-    host_rows_per_step = stats[0] / args.steps
+    steps_value = K * repeats
+    host_rows_per_step = stats[0] / steps_value
     feat_bytes = args.feat * 2
 
-    # ---- roofline of the dominant kernel, live from the timed region
-    fwd = kt.get(dominant, None)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
     except OSError:
         pass
     peak = float(peaks.get("hbm_gbs", 6650.0))
-    roof = None
-    if fwd:
-        bytes_per_launch = sum(conv0_bytes(b, args.feat, 2) for b in batches[args.warmup:]) / args.steps
-        if use_graph:
-            bytes_per_launch = sum(conv0_bytes(b, args.feat, 2)
-                                   for b in batches[args.warmup:args.warmup + n_prof]) / n_prof
-        ach = bytes_per_launch / (fwd["ms_total"] / fwd["launches"] * 1e-3) / 1e9
-        roof = {"bound": "hbm", "kernel": "aggr_fwd_vec_kernel<half,16,1> (first conv, no history)",
-                "achieved": round(ach, 1), "peak": peak,
-                "peak_source": "measured" if peaks else "fallback", "unit": "GB/s",
-                "frac": round(ach / peak, 4),
-                # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture of a
-                # 500 K-row block (profiles/aggr_fwd_f16_F128_*): 0.94 x algorithmic, scaled here
-                # by the rows gathered; inside a step the block is L2-resident, so this is an upper bound
-                "traffic": int(0.94 * bytes_per_launch),
-                "bytes_per_launch": int(bytes_per_launch),
-                "us_per_launch": round(fwd["ms_total"] / fwd["launches"] * 1e3, 2),
-                "note": "per-step blocks are far smaller than L2 (126 MB): latency bound, see roofline_large_block"}
+    src = "measured" if peaks else "fallback"
 
+    # ---- roofline: the library's kernels with the largest share of a step, each against the
+    # roof that bounds it.  Times are CUDA events around each call in the untimed pass above.
+    def per_launch(name):
+        v = kt_all.get(name)
+        return (v["ms_total"] / v["launches"], v["launches"] / n_prof) if v else (None, 0)
+
+    prof_b = timed[0][:n_prof]
+    roof = None
+    top = []
+    if n_prof:
+        ms_load, _ = per_launch("hc_load_rows")
+        if ms_load:
+            byts = host_rows_per_step * feat_bytes
+            top.append({"kernel": "load_rows_bulk_kernel (batch.x assembly; host rows over the host link)",
+                        "bound": "host-link", "ms_per_launch": round(ms_load, 4),
+                        "bytes_per_launch": int(byts), "achieved": round(byts / ms_load / 1e6, 2),
+                        "peak": host_link_peak, "unit": "GB/s",
+                        "frac": round(byts / ms_load / 1e6 / host_link_peak, 4) if host_link_peak else None,
+                        "peak_source": "pinned cudaMemcpy H2D of 256 MB on this box, best of 5",
+                        "note": "algorithmic bytes = host rows x row bytes; the same launch also copies the "
+                                "feature-cache rows inside HBM"})
+        dom = f"hc_aggr_fwd[f16,F={args.feat}]"
+        ms_f, _ = per_launch(dom)
+        if ms_f:
+            byts = sum(conv0_bytes(b, args.feat, 2) for b in prof_b) / n_prof
+            roof = {"bound": "hbm", "kernel": "aggr_fwd_vec_kernel<half> (first conv, no history)",
+                    "achieved": round(byts / ms_f / 1e6, 1), "peak": peak, "peak_source": src, "unit": "GB/s",
+                    "frac": round(byts / ms_f / 1e6 / peak, 4),
+                    # dram__bytes_read + dram__bytes_write of this kernel from the ncu capture of a
+                    # 500 K-row block (profiles/aggr_fwd_f16_F128_*): 0.94 x algorithmic, scaled here
+                    # by the rows gathered; inside a step the block is L2-resident: an upper bound
+                    "traffic": int(0.94 * byts), "bytes_per_launch": int(byts),
+                    "us_per_launch": round(ms_f * 1e3, 2),
+                    "note": "per-step blocks are far smaller than L2 (126 MB): latency bound, see "
+                            "roofline_large_block; the kernels with the largest share of a step are in roofline_top"}
+            top.append(dict(roof, ms_per_launch=round(ms_f, 4)))
+        dom_h = f"hc_aggr_fwd[f32,F={args.hidden}]"
+        ms_h, per_step = per_launch(dom_h)
+        if ms_h:
+            # the two hidden-layer aggregations: conv1 (with history) and conv2
+            byts = sum(hidden_fwd_bytes(b, args.hidden) for b in prof_b) / n_prof / max(per_step, 1)
+            top.append({"kernel": "aggr_fwd_vec_kernel<float> (hidden convs, history read in the gather)",
+                        "bound": "hbm", "ms_per_launch": round(ms_h, 4), "bytes_per_launch": int(byts),
+                        "achieved": round(byts / ms_h / 1e6, 1), "peak": peak, "unit": "GB/s",
+                        "frac": round(byts / ms_h / 1e6 / peak, 4), "peak_source": src,
+                        "note": "upper bound on the bytes: hit rows are counted as gathered"})
+
+    val = world * K / (ms * 1e-3)
     out = {
-        "metric": "train iters/sec (3-layer SAGE, 111M nodes)", "value": round(world * args.steps / (ms * 1e-3), 2),
-        "unit": "iters/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "weak",
+        "metric": "train iters/sec (3-layer SAGE, 111M nodes)", "value": round(val, 2),
+        "unit": "iters/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
+        "ms_per_step": round(ms / K, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 accumulate, f16 feature and history storage",
         "data": "synthetic",
         "config": {"workload": "configs[2]: 3-layer SAGE, synthetic power-law graph" if world == 1 else
@@ -353,20 +496,38 @@ def run_ours(args):
                    "batches": "pre-sampled pool (the loader's job); sampling alone takes "
                               f"{t_sample * 1e3:.2f} ms/batch with the library's sampling kernels",
                    "cuda_graph": ({"caps": caps, "edge_cap": ecap, "fixed_shape_batches": f"{n_fixed}/{total}",
-                                   "note": "whole step replayed as one CUDA graph over padded batches; the "
-                                           "per-kernel times and the roofline come from an eager pass over "
-                                           "the same batches after the timed region"}
+                                   "slack": args.graph_slack,
+                                   "note": ("whole step replayed as one CUDA graph over padded batches" if world == 1
+                                            else "step replayed as two captured segments around the eager "
+                                                 "gradient all-reduce") +
+                                           "; a batch that does not fit the caps takes the eager step"}
                                   if use_graph else None),
                    "prep": prep},
-        "e2e": {"value": round(world * args.steps / (ms_e2e * 1e-3), 2), "unit": "iters/s",
+        "repeats": {"regions": repeats, "steps_per_region": K,
+                    "value_iters_s": {"median": round(val, 2),
+                                      "min": round(world * K / (max(reg_ms) * 1e-3), 2),
+                                      "max": round(world * K / (min(reg_ms) * 1e-3), 2)},
+                    "e2e_iters_s": {"median": round(world * K / (ms_e2e * 1e-3), 2),
+                                    "min": round(world * K / (max(e2e_ms) * 1e-3), 2),
+                                    "max": round(world * K / (min(e2e_ms) * 1e-3), 2)},
+                    "timed_s": round(sum(reg_ms) * 1e-3, 3),
+                    "note": "each region is exactly `steps` steps between barrier + synchronize; "
+                            "value / e2e are the median region, max over ranks per region"},
+        "e2e": {"value": round(world * K / (ms_e2e * 1e-3), 2), "unit": "iters/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4,
                 "host_link_feature_bytes_per_step": int(host_rows_per_step * feat_bytes),
-                "mean_loss": round(loss_sum / args.steps, 4)},
+                "mean_loss": round(sum(losses_all) / max(len(losses_all), 1), 4),
+                "pipelined": "batch k+1 is copied host->device on a second stream during step k; the loss of "
+                             "step k is read on the host during step k+1 (hiscache/pipeline.py)",
+                "blocking_value": round(world * K / (statistics.median(blk_ms) * 1e-3), 2)},
         "with_sampling": {"value": round(world * n_samp / (ms_samp * 1e-3), 2), "unit": "iters/s",
                           "note": "each step also samples its batch on the GPU (sizes read back per hop)"},
         "gpu_launches": int(launches),
+        "gpu_launches_note": "library kernels per K-step region (PyTorch's own kernels not counted)",
+        "host_issue_ms_per_step": round(statistics.median(reg_issue) / K, 4),
+        "allreduce_ms_per_step": round(allreduce_ms, 4) if allreduce_ms is not None else None,
         "clocks": clocks,
-        "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt_all.items())},
+        "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt_all.items())} if n_prof else None,
         "host_link": {"rows_per_step": round(host_rows_per_step, 1),
                       "bytes_per_step": int(host_rows_per_step * feat_bytes),
                       "achieved_GBps": round(host_rows_per_step * feat_bytes /
@@ -378,27 +539,44 @@ def run_ours(args):
         "batch_shape": {"nodes_in_layer": [int(v) for v in batches[-1].num_node_in_layer],
                         "edges_in_layer": [int(v) for v in batches[-1].num_edge_in_layer]},
         "hit": {"host_rows_per_step": round(host_rows_per_step, 1),
-                "feature_cache_rows_per_step": round(stats[1] / args.steps, 1)},
+                "feature_cache_rows_per_step": round(stats[1] / steps_value, 1)},
     }
     if roof:
         out["roofline"] = roof
+    if top:
+        out["roofline_top"] = top
+    rc = 0
     if world > 1:
-        ovf = torch.tensor([trainer.table.table.overflow_count], dtype=torch.int64, device=device)
-        dist.all_reduce(ovf)
         out["exchange"] = {"mode": trainer.table.exchange,
                            "slots_per_pair": trainer.table.table.slots, "max_ids": trainer.table.table.max_ids,
-                           "ids_dropped_by_overflow": int(ovf.item()),
                            "shard_capacity_rows": trainer.table.table.capacity}
+        chk = exchange_check(trainer, device, rank, world, args.seed)
+        out["exchange"]["ids_dropped_by_overflow"] = chk["ids_dropped_by_overflow"]
+        out["exchange_check"] = chk
+        if not chk["ok"]:
+            rc = 3
 
     if rank == 0 and world == 1 and not args.no_large_block:
         out["roofline_large_block"] = large_block_roofline(device, peak, bool(peaks))
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_baseline(args, graph, uvm, batches[args.warmup:], args.cpu_steps,
-                                           threads=None, kind_note="same batches")
+        nat = loader.train_loader       # natural-shape batches of the same workload
+        out["cpu_baseline"] = cpu_baseline(args, graph, uvm, [next(nat) for _ in range(args.cpu_steps + 1)],
+                                           args.cpu_steps, threads=None, kind_note="same loader, same shapes")
     if world > 1:
+        trainer.table.table.close()
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(out), flush=True)
+    return rc
+
+
+def hidden_fwd_bytes(batch, hidden):
+    """Algorithmic bytes of the two hidden-layer aggregations of one step (fp32 rows)."""
+    nn, ne = [int(v) for v in batch.num_node_in_layer], [int(v) for v in batch.num_edge_in_layer]
+    tot = 0
+    for n_d, e in ((nn[1], ne[1]), (nn[0], ne[0])):
+        tot += e * hidden * 4 + n_d * hidden * 4 + 8 * (n_d + 1 + e)
+    return tot + 8 * nn[1]
 
 
 def measure_h2d_peak(device):
@@ -444,7 +622,7 @@ def large_block_roofline(device, peak, measured):
     return res
 
 
-def cpu_baseline(args, graph, uvm, batches, n_steps, threads, kind_note):
+def cpu_baseline(args, graph, uvm, batches, n_steps, threads, kind_note, warmup=1):
     """Times the CPU restatement of the iteration on the host cores (bounded sample)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import hc_oracle
@@ -459,17 +637,18 @@ def cpu_baseline(args, graph, uvm, batches, n_steps, threads, kind_note):
     tr = CpuTrainer(host, graph.num_nodes, args.feat, args.hidden, args.classes, len(fanouts),
                     buffer_elems=lcm_elems, sorted_indices=graph.sorted_indices.cpu().numpy(),
                     rate=args.rate, staleness=args.staleness, seed=args.seed)
-    sample = batches[:n_steps + 1]
+    sample = batches[:n_steps + warmup]
     cpu_b = [(b.ptr.cpu().numpy(), b.idx.cpu().numpy(), b.sub_to_full.cpu().numpy(), b.y.cpu().numpy(),
               [int(v) for v in b.num_node_in_layer]) for b in sample]
-    tr.step(*cpu_b[0])  # warm-up
+    for cb in cpu_b[:warmup]:
+        tr.step(*cb)
     t0 = time.time()
-    for cb in cpu_b[1:]:
+    for cb in cpu_b[warmup:]:
         tr.step(*cb)
     dt = time.time() - t0
-    n = len(cpu_b) - 1
+    n = len(cpu_b) - warmup
     return {"value": round(n / dt, 4), "unit": "iters/s", "cores": cores, "kind": "port",
-            "sample": f"{n} iterations of the same workload ({kind_note}), after 1 warm-up; "
+            "sample": f"{n} iterations of the same workload ({kind_note}), after {warmup} warm-up; "
                       "history table starts empty"}
 
 
@@ -483,11 +662,13 @@ def run_reference(args):
     torch.cuda.set_device(device)
     graph, uvm, loader, prep = setup_workload(args, 0, 1, device)
     it = loader.train_loader
-    k = max(1, min(args.steps, 8))
-    w = max(1, min(args.warmup, 1))
+    # --steps / --warmup are honoured up to a cap that keeps the arm within a couple of minutes
+    k = max(1, min(args.steps, 40))
+    w = max(1, min(args.warmup, 10))
     batches = [next(it) for _ in range(k + w)]
     t_all0 = time.time()
-    cb = cpu_baseline(args, graph, uvm, batches, k, threads=os.cpu_count(), kind_note="pre-sampled on the GPU")
+    cb = cpu_baseline(args, graph, uvm, batches, k, threads=os.cpu_count(), kind_note="pre-sampled on the GPU",
+                      warmup=w)
     wall = time.time() - t_all0
     val = cb["value"]
     out = {"impl": "reference", "metric": "train iters/sec (3-layer SAGE, 111M nodes)", "value": val,
@@ -498,7 +679,9 @@ def run_reference(args):
                       "edges": graph.num_edges, "feat": args.feat, "hidden": args.hidden,
                       "classes": args.classes, "batch_per_gpu": args.batch, "fanouts": args.fanouts,
                       "note": "the reference has no CPU implementation of this path; this is the "
-                              "CPU restatement (oracle/) on all host threads", "prep": prep,
+                              "CPU restatement (oracle/) on all host threads" +
+                              ("; at n_gpus > 1 it is still ONE CPU process on rank 0 (the other ranks exit)"
+                               if world > 1 else ""), "prep": prep,
                       "wall_s": round(wall, 1)},
            "cpu_baseline": cb,
            "e2e": {"value": val, "unit": "iters/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -510,7 +693,7 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     else:
-        run_ours(args)
+        sys.exit(run_ours(args))
 
 
 if __name__ == "__main__":

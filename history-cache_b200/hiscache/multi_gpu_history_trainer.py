@@ -118,12 +118,14 @@ class ShardedHistoryCache(HistoryCache):
         return True
 
     @torch.no_grad()
-    def finish_update(self):
+    def finish_update(self, fence=True):
         """Second half: the owners drop stale entries and take in what every rank published.
-        All ranks must have passed a collective since prepare_update (see PeerHistoryTable)."""
+        All ranks must have passed a collective since prepare_update (see PeerHistoryTable).
+        fence=False leaves the closing fence to the caller (a captured step issues it eagerly)."""
         self.table.evict_stale()
         self.table.admit_published(tick=True)
-        self.table.fence()
+        if fence:
+            self.table.fence()
 
     def update_history(self, batch, glb_iter, reset=None):
         if self.prepare_update(batch, glb_iter):
@@ -170,10 +172,9 @@ class MultiGpuHistoryTrainer:
         self.models = [self.model]
         self.num_layer = len(self.model.convs)
         self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
-                                          fused=True)
-        # The single-GPU trainer can replay its step from a CUDA graph (hiscache/graphed.py).
-        # Here the step contains NCCL collectives; capturing those was tried once on two GPUs
-        # and the run stopped making progress, so the data-parallel step stays eager.
+                                          fused=True, capturable=True)
+        # enable_cuda_graph() replays the step as two captured segments with the collectives
+        # issued eagerly between them (hiscache/graphed.py); no collective is ever captured.
         self.graphed = None
         self.scheduler = torch.optim.lr_scheduler.LambdaLR(self.optimizer, lambda _: 1.0)
         self.loss_fn = F.nll_loss
@@ -187,8 +188,11 @@ class MultiGpuHistoryTrainer:
 
     # the five phases of the reference's step (multi_gpu_history_trainer.py:60-133)
     def load(self, batch):
-        for p in self.params:
-            p.grad = None
+        if self.graphed is not None:
+            self.flat_grad.zero_()      # the parameters' .grad are views of it for good
+        else:
+            for p in self.params:
+                p.grad = None
         self.table.lookup_and_load(batch, self.num_layer)
 
     def run_forward(self, batch):
@@ -199,15 +203,29 @@ class MultiGpuHistoryTrainer:
         loss.backward()
         return loss
 
+    def _reduce_flat(self):
+        dist.all_reduce(self.flat_grad, op=dist.ReduceOp.AVG, group=self.group)
+
     def update_grad(self):
-        flat = torch.cat([p.grad.reshape(-1) if p.grad is not None else p.new_zeros(p.numel())
-                          for p in self.params])
-        dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
-        for p, g in zip(self.params, flat.split(self._numels)):
-            p.grad = g.view_as(p)
-        self.flat_grad = flat
+        if self.graphed is None:
+            self.flat_grad = torch.cat([p.grad.reshape(-1) if p.grad is not None else p.new_zeros(p.numel())
+                                        for p in self.params])
+            self._reduce_flat()
+            for p, g in zip(self.params, self.flat_grad.split(self._numels)):
+                p.grad = g.view_as(p)
+        else:
+            self._reduce_flat()
         self.optimizer.step()
         self.scheduler.step()
+
+    def enable_cuda_graph(self, caps, edge_cap, warmup_batches):
+        """Replays the step for fixed-shape batches of these caps as two captured segments around
+        the gradient all-reduce (hiscache/graphed.py).  Collective: every rank must call it, with
+        the same number of warm-up batches."""
+        from .graphed import GraphedDataParallelStep
+        self.model.train()
+        self.graphed = GraphedDataParallelStep(self, caps, edge_cap, warmup_batches)
+        return self.graphed
 
     def update_history(self, batch):
         self.table.update_history(batch, self.glb_iter)
@@ -217,6 +235,11 @@ class MultiGpuHistoryTrainer:
         """The gradient all-reduce sits between the two halves of the history update: it is
         the collective that tells every owner that all ranks have published their candidates
         and finished this step's lookups."""
+        g = self.graphed
+        if g is not None and g.fits(batch):
+            loss = g.run(batch)
+            self.glb_iter += 1
+            return loss
         self.load(batch)
         out = self.run_forward(batch)
         loss = self.run_backward(batch, out)

@@ -1,7 +1,8 @@
 """CPU restatement of one HisCache training iteration.  TEST INFRASTRUCTURE.
 
 Used only as the checker / timed CPU baseline (bench.py's `cpu_baseline` leg and
-`--impl reference`, and the end-to-end parity test).  The reference has no CPU implementation
+`--impl reference`, and tests/test_whole_iteration_gpu.py, which steps the GPU trainer and this
+one over the same batches).  The reference has no CPU implementation
 of this path: its operators are CUDA only.  This module runs the same iteration
 (hiscache/history_trainer.py:183-191) on host cores: lookup and row assembly in numpy
 (hc_oracle.cache_lookup / load_rows), aggregation forward/backward in the C restatement with
@@ -89,6 +90,7 @@ class CpuTrainer:
         self.full2embed[self.feat2full] = np.arange(len(ci))
         self.buffer.reshape(-1, in_c)[feat_slots - len(ci):] = host_table[ci].astype(np.float32)
         self.glb_iter = 0
+        self.last = {}     # what the last step looked up / admitted, for the parity test
 
     def step(self, ptr, idx, sub_to_full, y, nn):
         ptr, idx, s2f = (np.ascontiguousarray(a, dtype=np.int64) for a in (ptr, idx, sub_to_full))
@@ -106,9 +108,11 @@ class CpuTrainer:
         loss.backward()
         self.opt.step()
         # update_history (history_cache.py:190-254)
+        self.last = {"sub2embed": sub2embed, "sub2feat": sub2feat, "used0": used0, "x": x}
         if his is not None and his.grad is not None and self.staleness > 0:
             score = O.score_rows(his.grad.numpy(), "l2")
             thres = O.quantile(score, self.rate)
+            self.last.update(score=score, thres=thres, his=his.detach().numpy())
             O.cache_admit(his.detach().numpy(), self.buffer, self.hidden, self.in_c, s2f[:n1],
                           sub2embed, score, thres, self.full2embed, self.N, self.embed2full,
                           self.feat2full, self.header,

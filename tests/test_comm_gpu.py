@@ -3,6 +3,8 @@ conventions: the reference's single-process 2-D list (peer copies) and the one-p
 flat list (NCCL).  Needs two GPUs."""
 import os
 
+import numpy as np
+
 import pytest
 import torch
 
@@ -55,3 +57,94 @@ def test_all2all_one_process_per_gpu():
         pytest.skip("needs two GPUs")
     from _mp import run_ranks
     assert all(run_ranks(_rank, 2, (29300 + os.getpid() % 100,), timeout=240))
+
+
+# ---------------------------------------------------------------------------------------------
+# p2psend / p2psend_gentensor (src/cpp/src/comm.cu:3-20) and prepare_transfer / post_transfer
+# (hiscache/comm.py:132-151) against a numpy statement of what the reference computes.  With one
+# GPU every "device" of the single-process convention is cuda:0; with two the pieces really cross.
+# ---------------------------------------------------------------------------------------------
+def _devices(n):
+    have = torch.cuda.device_count()
+    return [torch.device("cuda", i % have) for i in range(n)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int64])
+def test_p2psend_copies_the_leading_elements(backend, dtype):
+    src_dev, dst_dev = _devices(2)
+    src = (torch.arange(60, device=src_dev).reshape(12, 5) * 3).to(dtype)
+    dst = torch.full((12, 5), -7, device=dst_dev).to(dtype)
+    cur = torch.cuda.current_device()
+    backend.p2psend(src, dst, 23, dst_dev.index)
+    torch.cuda.synchronize(dst_dev)
+    assert torch.cuda.current_device() == cur, "the current device must not change"
+    want = np.full(60, -7.0)
+    want[:23] = np.arange(60)[:23] * 3
+    assert np.array_equal(dst.cpu().numpy().reshape(-1).astype(np.float64), want)
+    # all elements, non-contiguous source
+    src_t = src.t()
+    dst2 = torch.empty(5, 12, device=dst_dev, dtype=dtype)
+    backend.p2psend(src_t, dst2, src_t.numel(), dst_dev.index)
+    torch.cuda.synchronize(dst_dev)
+    assert torch.equal(dst2.cpu(), src_t.contiguous().cpu())
+
+
+def test_p2psend_gentensor_allocates_on_the_target(backend):
+    src_dev, dst_dev = _devices(2)
+    src = torch.randn(7, 9, device=src_dev)
+    out = backend.p2psend_gentensor(src, src.numel(), dst_dev.index)
+    torch.cuda.synchronize(dst_dev)
+    assert out.device == dst_dev and out.shape == src.shape and out.dtype == src.dtype
+    assert torch.equal(out.cpu(), src.cpu())
+    part = backend.p2psend_gentensor(src, 20, dst_dev.index)
+    torch.cuda.synchronize(dst_dev)
+    assert np.array_equal(part.cpu().numpy().reshape(-1)[:20], src.cpu().numpy().reshape(-1)[:20])
+
+
+class _B:
+    pass
+
+
+@pytest.mark.parametrize("n_dev", [2, 4])
+def test_prepare_and_post_transfer_match_the_reference_statement(backend, n_dev):
+    """prepare_transfer: tensor_list[src][dst] = feats[src][ids dst still needs]
+    (hiscache/comm.py:132-143); post_transfer: x_i[mask_i] = concat_dim1(tensor_2d_dst[i])
+    (:146-151).  With feature-sliced shards (each device holds F / n_dev columns of every node)
+    prepare -> all2all -> post reassembles exactly the rows of the full feature matrix."""
+    from hiscache import all2all, prepare_transfer
+    from hiscache.comm import post_transfer
+    rng = np.random.default_rng(5)
+    devs = _devices(n_dev)
+    N, F = 500, 8 * n_dev
+    full = rng.standard_normal((N, F)).astype(np.float32)
+    shards = [full[:, d * (F // n_dev):(d + 1) * (F // n_dev)].copy() for d in range(n_dev)]
+    feats = [torch.from_numpy(shards[d]).to(devs[d]) for d in range(n_dev)]
+    batches, masks, ids_np, masks_np = [], [], [], []
+    for d in range(n_dev):
+        n = 40 + 7 * d
+        ids = rng.choice(N, size=n, replace=False).astype(np.int64)
+        m = rng.random(n) < 0.6
+        b = _B()
+        b.sub_to_full = torch.from_numpy(ids).to(devs[d])
+        b.sub_to_fulls = {d: b.sub_to_full}       # the reference indexes sub_to_fulls[i]
+        b.x = torch.zeros(n, F, device=devs[d])
+        batches.append(b)
+        masks.append(torch.from_numpy(m).to(devs[d]))
+        ids_np.append(ids)
+        masks_np.append(m)
+    tl = prepare_transfer(batches, masks, feats)
+    for s in range(n_dev):
+        for d in range(n_dev):
+            want = shards[s][ids_np[d][masks_np[d]]]
+            assert tl[s][d].device == devs[s]
+            assert np.array_equal(tl[s][d].cpu().numpy(), want), (s, d)
+    got = all2all(tl)                      # got[dst][src] lives on dst
+    for d in range(n_dev):
+        for s in range(n_dev):
+            assert got[d][s].device == devs[d]
+    post_transfer(batches, masks, got)
+    for d in range(n_dev):
+        torch.cuda.synchronize(devs[d])
+        want = np.zeros((len(ids_np[d]), F), dtype=np.float32)
+        want[masks_np[d]] = full[ids_np[d][masks_np[d]]]
+        assert np.array_equal(batches[d].x.cpu().numpy(), want), d
