@@ -182,6 +182,8 @@ def conv0_bytes(batch, feat, elem):
     no history): E*F*s gathered + N_d*F*4 written + 8*(N_d+1+E) of ptr/idx."""
     nn, ne = batch.num_node_in_layer, batch.num_edge_in_layer
     n_d, e = int(nn[-2]), int(ne[-1])
+    if batch.mask is not None:     # fixed shape: padding rows have no edges and write zeros
+        e = int(batch.ptr[n_d])
     return e * feat * elem + n_d * feat * 4 + 8 * (n_d + 1 + e)
 
 
@@ -572,7 +574,12 @@ def run_ours(args):
 
 def hidden_fwd_bytes(batch, hidden):
     """Algorithmic bytes of the two hidden-layer aggregations of one step (fp32 rows)."""
-    nn, ne = [int(v) for v in batch.num_node_in_layer], [int(v) for v in batch.num_edge_in_layer]
+    nn = [int(v) for v in batch.num_node_in_layer]
+    if batch.mask is not None:     # fixed shape: the real edge counts are in ptr
+        ne = [int(batch.ptr[nn[0]]), int(batch.ptr[nn[1]])]
+        nn = [int(batch.mask[:nn[0]].sum()), int(batch.mask[:nn[1]].sum())]
+    else:
+        ne = [int(v) for v in batch.num_edge_in_layer]
     tot = 0
     for n_d, e in ((nn[1], ne[1]), (nn[0], ne[0])):
         tot += e * hidden * 4 + n_d * hidden * 4 + 8 * (n_d + 1 + e)

@@ -12,54 +12,108 @@
 
 namespace hc {
 
+// ---------------------------------------------------------------------------
+// Transposition = a stable sort of the block's edges by source.
+//
+// Edges are laid out by destination row (CSR), so a STABLE sort by source leaves every
+// source's list in ascending destination order: no per-list sort, no atomics, and the cost
+// does not depend on how skewed the source popularity is (a hub with 10^5 entries is just
+// 10^5 keys).  The sort is a least-significant-digit radix sort with 8-bit digits over
+// 32-bit keys (key = source, payload = destination row); edges that carry no gradient
+// (history-hit rows, sources served from the alternative table, the unused tail of idx)
+// get the key n_src and end up behind every real list.  ceil(bits(n_src)/8) passes of
+//   digit histogram per 4096-key chunk -> exclusive scan (digit-major) -> stable scatter.
+// ---------------------------------------------------------------------------
+constexpr int kRadixWarps = 8;
+constexpr int kRadixIters = 16;                                   // keys per lane and pass
+constexpr int kRadixChunk = kRadixWarps * kRadixIters * kWarp;    // 4096 keys per block
 constexpr int kTScan = 1024;
 
-// edges of miss rows whose source takes a gradient
-__device__ __forceinline__ bool edge_counts(const hc_aggr_args& a, int64_t r, int64_t s) {
-  (void)r;
-  return !(a.src_map && a.src_map[s] != -1);
-}
-
-__global__ void __launch_bounds__(256) tr_count_kernel(const hc_aggr_args a, long long* cnt) {
+// key/payload of every edge slot in [0, n_edges)
+__global__ void __launch_bounds__(256)
+    tr_expand_kernel(const hc_aggr_args a, const int64_t n_edges, uint32_t* __restrict__ key,
+                     uint32_t* __restrict__ val) {
   constexpr int G = 8;
   const int gl = threadIdx.x & (G - 1);
-  const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
-  if (r >= a.num_node) return;
-  if (a.hmap && a.hmap[r] != -1) return;
-  for (int64_t e = a.ptr[r] + gl; e < a.ptr[r + 1]; e += G) {
-    const int64_t s = a.idx[e];
-    if (edge_counts(a, r, s)) atomicAdd(reinterpret_cast<unsigned long long*>(cnt + s), 1ull);
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t r = gtid / G;
+  const uint32_t none = (uint32_t)a.n_src;
+  if (r < a.num_node) {
+    const bool row_counts = !(a.hmap && a.hmap[r] != -1);
+    int64_t b = a.ptr[r], e_end = a.ptr[r + 1];
+    if (e_end > n_edges) e_end = n_edges;
+    for (int64_t e = b + gl; e < e_end; e += G) {
+      const int64_t s = a.idx[e];
+      const bool ok = row_counts && s >= 0 && s < a.n_src && !(a.src_map && a.src_map[s] != -1);
+      key[e] = ok ? (uint32_t)s : none;
+      val[e] = (uint32_t)r;
+    }
+  }
+  // slots behind the last row's edges
+  int64_t tail = a.num_node > 0 ? a.ptr[a.num_node] : 0;
+  if (tail < 0) tail = 0;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t e = tail + gtid; e < n_edges; e += stride) {
+    key[e] = none;
+    val[e] = 0;
   }
 }
 
-// three-phase exclusive scan of cnt[0..n) into out[0..n], out[n] = total
-__global__ void __launch_bounds__(kTScan)
-    tr_block_sum_kernel(const long long* __restrict__ cnt, int64_t n, long long* __restrict__ sums) {
-  __shared__ long long sh[kTScan / 32];
-  const int64_t i = (int64_t)blockIdx.x * kTScan + threadIdx.x;
-  long long v = i < n ? cnt[i] : 0;
+// per-warp digit counts of this block's chunk, in shared memory cnt[warp][digit]
+__device__ __forceinline__ void radix_count(const uint32_t* __restrict__ key, int64_t n, int shift,
+                                            uint32_t (*cnt)[256]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < kRadixWarps * 256; i += blockDim.x) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kRadixChunk + (int64_t)warp * (kRadixIters * kWarp);
+#pragma unroll 4
+  for (int it = 0; it < kRadixIters; ++it) {
+    const int64_t i = base + it * kWarp + lane;
+    if (i < n) atomicAdd(&cnt[warp][(key[i] >> shift) & 255u], 1u);
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kRadixWarps * kWarp)
+    tr_hist_kernel(const uint32_t* __restrict__ key, int64_t n, int shift, int64_t nblk,
+                   uint32_t* __restrict__ hist) {
+  __shared__ uint32_t cnt[kRadixWarps][256];
+  radix_count(key, n, shift, cnt);
+  const int d = threadIdx.x;   // 256 threads, one digit each
+  uint32_t t = 0;
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(kFull, v, off);
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  for (int w = 0; w < kRadixWarps; ++w) t += cnt[w][d];
+  hist[(int64_t)d * nblk + blockIdx.x] = t;   // digit-major: the scan order of an LSD pass
+}
+
+// three-phase exclusive scan of v[0..n) in place (uint32)
+__global__ void __launch_bounds__(kTScan)
+    tr_block_sum_kernel(const uint32_t* __restrict__ v, int64_t n, uint32_t* __restrict__ sums) {
+  __shared__ uint32_t sh[kTScan / 32];
+  const int64_t i = (int64_t)blockIdx.x * kTScan + threadIdx.x;
+  uint32_t x = i < n ? v[i] : 0;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(kFull, x, off);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = x;
   __syncthreads();
   if (threadIdx.x == 0) {
-    long long t = 0;
+    uint32_t t = 0;
     for (int w = 0; w < kTScan / 32; ++w) t += sh[w];
     sums[blockIdx.x] = t;
   }
 }
-__global__ void __launch_bounds__(1024) tr_scan_sums_kernel(long long* sums, int64_t nb) {
-  __shared__ long long part[1024];
-  __shared__ long long carry;
+__global__ void __launch_bounds__(1024) tr_scan_sums_kernel(uint32_t* sums, int64_t nb) {
+  __shared__ uint32_t part[1024];
+  __shared__ uint32_t carry;
   if (threadIdx.x == 0) carry = 0;
   __syncthreads();
   for (int64_t base = 0; base < nb; base += 1024) {
     const int64_t b = base + threadIdx.x;
-    const long long c = b < nb ? sums[b] : 0;
+    const uint32_t c = b < nb ? sums[b] : 0;
     part[threadIdx.x] = c;
     __syncthreads();
     for (int off = 1; off < 1024; off <<= 1) {
-      const long long v = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
+      const uint32_t v = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
       __syncthreads();
       part[threadIdx.x] += v;
       __syncthreads();
@@ -71,109 +125,111 @@ __global__ void __launch_bounds__(1024) tr_scan_sums_kernel(long long* sums, int
   }
 }
 __global__ void __launch_bounds__(kTScan)
-    tr_scan_apply_kernel(const long long* __restrict__ cnt, int64_t n, const long long* __restrict__ sums,
-                         int64_t* __restrict__ out, long long* __restrict__ cursor) {
-  __shared__ long long wsum[kTScan / 32];
+    tr_scan_apply_kernel(uint32_t* __restrict__ v, int64_t n, const uint32_t* __restrict__ sums) {
+  __shared__ uint32_t wsum[kTScan / 32];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t i = (int64_t)blockIdx.x * kTScan + threadIdx.x;
-  const long long c = i < n ? cnt[i] : 0;
-  long long v = c;  // inclusive scan inside the warp
+  const uint32_t c = i < n ? v[i] : 0;
+  uint32_t x = c;  // inclusive scan inside the warp
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
-    const long long t = __shfl_up_sync(kFull, v, off);
-    if (lane >= off) v += t;
+    const uint32_t t = __shfl_up_sync(kFull, x, off);
+    if (lane >= off) x += t;
   }
-  if (lane == 31) wsum[warp] = v;
+  if (lane == 31) wsum[warp] = x;
   __syncthreads();
-  long long before = sums[blockIdx.x];
+  uint32_t before = sums[blockIdx.x];
   for (int w = 0; w < warp; ++w) before += wsum[w];
-  if (i < n) {
-    out[i] = before + v - c;
-    cursor[i] = before + v - c;
-    if (i == n - 1) out[n] = before + v;
+  if (i < n) v[i] = before + x - c;
+}
+
+// stable scatter of one pass: a key goes to (scanned start of its digit for this block) +
+// (keys of that digit in lower warps of the block) + (its rank among the warp's earlier keys)
+__global__ void __launch_bounds__(kRadixWarps * kWarp)
+    tr_scatter_kernel(const uint32_t* __restrict__ key, const uint32_t* __restrict__ val, int64_t n,
+                      int shift, int64_t nblk, const uint32_t* __restrict__ hist,
+                      uint32_t* __restrict__ key_out, uint32_t* __restrict__ val_out) {
+  __shared__ uint32_t cnt[kRadixWarps][256];
+  radix_count(key, n, shift, cnt);
+  {
+    const int d = threadIdx.x;
+    uint32_t run = hist[(int64_t)d * nblk + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kRadixWarps; ++w) {
+      const uint32_t c = cnt[w][d];
+      cnt[w][d] = run;     // from now on: next free position of digit d for warp w
+      run += c;
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  const int64_t base = (int64_t)blockIdx.x * kRadixChunk + (int64_t)warp * (kRadixIters * kWarp);
+  for (int it = 0; it < kRadixIters; ++it) {
+    const int64_t i = base + it * kWarp + lane;
+    const bool ok = i < n;
+    const uint32_t k = ok ? key[i] : 0u;
+    const uint32_t v = ok ? val[i] : 0u;
+    const uint32_t d = ok ? ((k >> shift) & 255u) : 256u;   // lanes past the end match only each other
+    const unsigned same = __match_any_sync(kFull, d);
+    const int rank = __popc(same & lt);
+    uint32_t pos = 0;
+    if (ok) pos = cnt[warp][d] + rank;
+    __syncwarp();
+    if (ok && rank == 0) cnt[warp][d] += __popc(same);
+    __syncwarp();
+    if (ok) {
+      key_out[pos] = k;
+      val_out[pos] = v;
+    }
   }
 }
 
+// list boundaries, destination rows and weights from the sorted (source, row) pairs
 __global__ void __launch_bounds__(256)
-    tr_fill_kernel(const hc_aggr_args a, long long* cursor, int64_t* __restrict__ t_dst) {
-  constexpr int G = 8;
-  const int gl = threadIdx.x & (G - 1);
-  const int64_t r = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
-  if (r >= a.num_node) return;
-  if (a.hmap && a.hmap[r] != -1) return;
-  for (int64_t e = a.ptr[r] + gl; e < a.ptr[r + 1]; e += G) {
-    const int64_t s = a.idx[e];
-    if (edge_counts(a, r, s)) {
-      const long long pos = (long long)atomicAdd(reinterpret_cast<unsigned long long*>(cursor + s), 1ull);
-      t_dst[pos] = r;
-    }
+    tr_finalize_kernel(const uint32_t* __restrict__ key, const uint32_t* __restrict__ val, int64_t n_edges,
+                       int64_t n_src, const int64_t* __restrict__ ptr, int64_t* __restrict__ t_ptr,
+                       int64_t* __restrict__ t_dst, float* __restrict__ t_w) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_edges) return;
+  const int64_t k = key[i];
+  const int64_t prev = i > 0 ? (int64_t)key[i - 1] : -1;
+  for (int64_t s = prev + 1; s <= k && s <= n_src; ++s) t_ptr[s] = i;   // lists of s in (prev, k] start here
+  if (i == n_edges - 1)
+    for (int64_t s = k + 1; s <= n_src; ++s) t_ptr[s] = n_edges;
+  if (k < n_src) {
+    const int64_t r = val[i];
+    t_dst[i] = r;
+    t_w[i] = __frcp_rn((float)(ptr[r + 1] - ptr[r]));
   }
-}
-
-// each source's list ascending by destination row: the order of the atomics above no longer matters
-__device__ __forceinline__ void tr_weights(const int64_t* __restrict__ ptr, const int64_t* v, float* w, int64_t k) {
-  for (int64_t i = 0; i < k; ++i) w[i] = __frcp_rn((float)(ptr[v[i] + 1] - ptr[v[i]]));
-}
-
-__global__ void tr_sort_kernel(const int64_t* __restrict__ ptr, const int64_t* __restrict__ t_ptr,
-                               int64_t n_src, int64_t* t_dst, float* t_w) {
-  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (s >= n_src) return;
-  const int64_t b = t_ptr[s], k = t_ptr[s + 1] - b;
-  int64_t* v = t_dst + b;
-  if (k < 2) {
-    tr_weights(ptr, v, t_w + b, k);
-    return;
-  }
-  if (k <= 32) {  // insertion sort
-    for (int64_t i = 1; i < k; ++i) {
-      const int64_t x = v[i];
-      int64_t j = i - 1;
-      while (j >= 0 && v[j] > x) { v[j + 1] = v[j]; --j; }
-      v[j + 1] = x;
-    }
-    tr_weights(ptr, v, t_w + b, k);
-    return;
-  }
-  // heap sort for the rare long lists
-  for (int64_t start = k / 2 - 1; start >= 0; --start) {
-    int64_t root = start;
-    for (;;) {
-      int64_t child = 2 * root + 1;
-      if (child >= k) break;
-      if (child + 1 < k && v[child] < v[child + 1]) ++child;
-      if (v[root] >= v[child]) break;
-      const int64_t t = v[root]; v[root] = v[child]; v[child] = t;
-      root = child;
-    }
-  }
-  for (int64_t end = k - 1; end > 0; --end) {
-    const int64_t t0 = v[0]; v[0] = v[end]; v[end] = t0;
-    int64_t root = 0;
-    for (;;) {
-      int64_t child = 2 * root + 1;
-      if (child >= end) break;
-      if (child + 1 < end && v[child] < v[child + 1]) ++child;
-      if (v[root] >= v[child]) break;
-      const int64_t t = v[root]; v[root] = v[child]; v[child] = t;
-      root = child;
-    }
-  }
-  tr_weights(ptr, v, t_w + b, k);
 }
 
 // grad_input[s, :] = sum over the transposed list of t_w * grad_out[r, :]; every row written once.
 // A warp takes kSW consecutive sources: their lists are one contiguous slice of t_dst / t_w,
 // fetched with one coalesced load when it has at most 32 entries, so that each source then
 // costs a single round of row loads.
+//
+// The lists may belong to a LARGER block than the one being differentiated (one transposition
+// of a batch's CSR serves every layer, because all layers share the CSR prefix): entries whose
+// destination row is >= num_node, or is served from history (hmap[r] != -1), are skipped.
+//
+// Lists longer than kLongList entries (hub sources of a skewed block) are left to the
+// long-list kernels below, which split them into chunks over many blocks and add the chunk
+// sums in chunk order, so the result stays bit-reproducible.
 constexpr int kSW = 8;
+constexpr int kLongList = 1024;
+
+__device__ __forceinline__ bool entry_counts(int64_t r, int64_t num_node, const int64_t* __restrict__ hmap) {
+  return r < num_node && !(hmap && hmap[r] != -1);
+}
 
 template <int G, int V>
 __global__ void __launch_bounds__(256)
     aggr_bwd_gather_kernel(const int64_t n_src, const int feat, const int64_t* __restrict__ t_ptr,
                            const int64_t* __restrict__ t_dst, const float* __restrict__ t_w,
                            const float* __restrict__ grad_out, float* __restrict__ grad_input,
-                           const int nvec) {
+                           const int nvec, const int64_t num_node, const int64_t* __restrict__ hmap,
+                           const int64_t* __restrict__ src_map) {
   constexpr int EPW = kWarp / G;
   constexpr int U = V == 1 ? 4 : (V == 2 ? 2 : 1);
   const int lane = threadIdx.x & 31;
@@ -184,14 +240,18 @@ __global__ void __launch_bounds__(256)
   const int64_t my_p = lane <= ns ? t_ptr[s0 + lane] : 0;
   const int64_t E0 = shfl64(my_p, 0), E1 = shfl64(my_p, ns);
   const bool one_chunk = (E1 - E0) <= kWarp;
-  int64_t my_r = 0;
+  int64_t my_r = -1;
   float my_w = 0.f;
   if (one_chunk && E0 + lane < E1) {
     my_r = t_dst[E0 + lane];
     my_w = t_w[E0 + lane];
+    if (!entry_counts(my_r, num_node, hmap)) my_r = -1;
   }
   for (int k = 0; k < ns; ++k) {
-    const int64_t begin = shfl64(my_p, k), end = shfl64(my_p, k + 1);
+    const int64_t begin = shfl64(my_p, k);
+    int64_t end = shfl64(my_p, k + 1);
+    if (end - begin > kLongList) continue;   // warp-uniform: written by the long-list kernels
+    if (src_map && src_map[s0 + k] != -1) end = begin;   // served from the other table: no gradient
     float4 acc[V];
 #pragma unroll
     for (int q = 0; q < V; ++q) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -201,15 +261,17 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int64_t jj = i + u * EPW + sub;
-        const bool ok = jj < end;
+        bool ok = jj < end;
         int64_t r;
         if (one_chunk) {
           const int from = (int)(jj - E0) & 31;
           r = shfl64(my_r, from);
           w[u] = __shfl_sync(kFull, my_w, from);
+          ok = ok && r >= 0;
         } else {
           r = ok ? t_dst[jj] : 0;
           w[u] = ok ? t_w[jj] : 0.f;
+          ok = ok && entry_counts(r, num_node, hmap);
         }
         if (!ok) w[u] = 0.f;
 #pragma unroll
@@ -250,13 +312,112 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// ---- long lists -----------------------------------------------------------
+// work items (source, chunk) of kLongList entries each; item i writes its partial sum to
+// partial[i, :]; a last kernel adds a source's partials in chunk order.
+struct LongWork {
+  unsigned long long* counters;  // [0] number of long sources, [1] number of items
+  int64_t* long_src;             // [max_long]
+  int64_t* long_base;            // [max_long] first item of the source
+  int64_t* item_src;             // [max_items]
+  int32_t* item_chunk;           // [max_items]
+  float* partial;                // [max_items, feat]
+  int64_t max_long, max_items;
+};
+
+__global__ void __launch_bounds__(256)
+    long_collect_kernel(const int64_t n_src, const int64_t* __restrict__ t_ptr, LongWork w) {
+  const int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= n_src) return;
+  const int64_t len = t_ptr[s + 1] - t_ptr[s];
+  if (len <= kLongList) return;
+  const int64_t chunks = ceil_div(len, kLongList);
+  const int64_t li = (int64_t)atomicAdd(&w.counters[0], 1ull);
+  const int64_t base = (int64_t)atomicAdd(&w.counters[1], (unsigned long long)chunks);
+  // the bounds hold by construction (every long list has more than kLongList of the n_edges entries)
+  if (li >= w.max_long || base + chunks > w.max_items) return;
+  w.long_src[li] = s;
+  w.long_base[li] = base;
+  for (int64_t c = 0; c < chunks; ++c) {
+    w.item_src[base + c] = s;
+    w.item_chunk[base + c] = (int32_t)c;
+  }
+}
+
+// one block per item: warp q takes entries q, q+8, ... of the chunk; the eight warp sums are
+// added in warp order through shared memory
+__global__ void __launch_bounds__(256)
+    long_items_kernel(const int feat, const int64_t* __restrict__ t_ptr, const int64_t* __restrict__ t_dst,
+                      const float* __restrict__ t_w, const float* __restrict__ grad_out, LongWork w,
+                      const int64_t num_node, const int64_t* __restrict__ hmap,
+                      const int64_t* __restrict__ src_map) {
+  extern __shared__ __align__(16) float sh[];   // [8][feat]
+  const int64_t n_items = (int64_t)w.counters[1] < w.max_items ? (int64_t)w.counters[1] : w.max_items;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t s = w.item_src[item];
+    const int64_t begin = t_ptr[s] + (int64_t)w.item_chunk[item] * kLongList;
+    int64_t end = begin + kLongList;
+    if (end > t_ptr[s + 1]) end = t_ptr[s + 1];
+    if (src_map && src_map[s] != -1) end = begin;
+    for (int c0 = 0; c0 < feat; c0 += 128) {   // 128 columns (one float4 per lane) at a time
+      const int col = c0 + 4 * lane;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int64_t j = begin + warp; j < end; j += 8) {
+        const int64_t r = t_dst[j];
+        if (!entry_counts(r, num_node, hmap)) continue;
+        const float wt = t_w[j];
+        if (col < feat) {
+          const float4 g = __ldg(reinterpret_cast<const float4*>(grad_out + r * feat + col));
+          acc.x = fmaf(wt, g.x, acc.x); acc.y = fmaf(wt, g.y, acc.y);
+          acc.z = fmaf(wt, g.z, acc.z); acc.w = fmaf(wt, g.w, acc.w);
+        }
+      }
+      if (col < feat) *reinterpret_cast<float4*>(sh + warp * feat + col) = acc;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < feat; c += blockDim.x) {
+      float t = sh[c];
+#pragma unroll
+      for (int q = 1; q < 8; ++q) t += sh[q * feat + c];
+      w.partial[item * feat + c] = t;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    long_reduce_kernel(const int feat, const int64_t* __restrict__ t_ptr, LongWork w,
+                       float* __restrict__ grad_input) {
+  const int64_t n_long = (int64_t)w.counters[0] < w.max_long ? (int64_t)w.counters[0] : w.max_long;
+  for (int64_t li = blockIdx.x; li < n_long; li += gridDim.x) {
+    const int64_t s = w.long_src[li], base = w.long_base[li];
+    const int64_t chunks = ceil_div(t_ptr[s + 1] - t_ptr[s], (int64_t)kLongList);
+    for (int c = threadIdx.x; c < feat; c += blockDim.x) {
+      float t = 0.f;
+      for (int64_t k = 0; k < chunks; ++k) t += w.partial[(base + k) * feat + c];
+      grad_input[s * feat + c] = t;
+    }
+  }
+}
+
 }  // namespace hc
 
 using namespace hc;
 
-extern "C" int64_t hc_transpose_scratch_bytes(int64_t n_src) {
-  const int64_t nb = ceil_div(n_src > 0 ? n_src : 1, kTScan);
-  return (2 * (n_src + 1) + nb + 8) * (int64_t)sizeof(int64_t);
+static int radix_passes(int64_t n_src) {
+  int bits = 1;
+  while (bits < 32 && ((int64_t)1 << bits) <= n_src) ++bits;   // the key n_src itself must fit
+  return (bits + 7) / 8;
+}
+
+extern "C" int64_t hc_transpose_scratch_bytes(int64_t n_src, int64_t n_edges) {
+  (void)n_src;
+  if (n_edges < 1) n_edges = 1;
+  const int64_t nblk = ceil_div(n_edges, kRadixChunk);
+  const int64_t nh = 256 * nblk;
+  const int64_t nsum = ceil_div(nh, kTScan);
+  return (4 * n_edges + nh + nsum + 64) * (int64_t)sizeof(uint32_t);
 }
 
 static int check_simple(const hc_aggr_args* a) {
@@ -267,47 +428,74 @@ static int check_simple(const hc_aggr_args* a) {
   return 0;
 }
 
-extern "C" int hc_transpose_block(const hc_aggr_args* a, int64_t* t_ptr, int64_t* t_dst,
-                                  float* t_w, void* scratch, void* stream) {
+extern "C" int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_t* t_ptr,
+                                  int64_t* t_dst, float* t_w, void* scratch, void* stream) {
   int rc = check_simple(a);
   if (rc) return rc;
   HC_REQUIRE(t_ptr != nullptr, HC_ERR_NULL);
+  HC_REQUIRE(n_edges >= 0 && n_edges < 0x7fffffffLL && a->n_src < 0x7fffffffLL &&
+                 a->num_node < 0x7fffffffLL, HC_ERR_SIZE);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (a->n_src == 0) {
-    HC_CUDA(cudaMemsetAsync(t_ptr, 0, sizeof(int64_t), st));
+  if (a->n_src == 0 || n_edges == 0 || a->num_node == 0) {
+    HC_CUDA(cudaMemsetAsync(t_ptr, 0, (size_t)(a->n_src + 1) * sizeof(int64_t), st));
     return 0;
   }
   HC_REQUIRE(scratch != nullptr && aligned_to(scratch, 8), HC_ERR_NULL);
-  HC_REQUIRE(a->num_node == 0 || (a->ptr && a->idx && t_dst && t_w), HC_ERR_NULL);
-  long long* cnt = reinterpret_cast<long long*>(scratch);
-  long long* cursor = cnt + (a->n_src + 1);
-  long long* sums = cursor + (a->n_src + 1);
-  const int64_t nb = ceil_div(a->n_src, kTScan);
-  HC_REQUIRE(nb <= 0x7fffffffLL, HC_ERR_SIZE);
-  HC_CUDA(cudaMemsetAsync(cnt, 0, (size_t)(a->n_src + 1) * sizeof(long long), st));
-  const int64_t rb = ceil_div((a->num_node > 0 ? a->num_node : 1) * 8, 256);
-  HC_REQUIRE(rb <= 0x7fffffffLL, HC_ERR_SIZE);
-  if (a->num_node > 0) tr_count_kernel<<<(unsigned)rb, 256, 0, st>>>(*a, cnt);
-  tr_block_sum_kernel<<<(unsigned)nb, kTScan, 0, st>>>(cnt, a->n_src, sums);
-  tr_scan_sums_kernel<<<1, 1024, 0, st>>>(sums, nb);
-  tr_scan_apply_kernel<<<(unsigned)nb, kTScan, 0, st>>>(cnt, a->n_src, sums, t_ptr, cursor);
-  if (a->num_node > 0) {
-    tr_fill_kernel<<<(unsigned)rb, 256, 0, st>>>(*a, cursor, t_dst);
-    tr_sort_kernel<<<(unsigned)ceil_div(a->n_src, 256), 256, 0, st>>>(a->ptr, t_ptr, a->n_src, t_dst, t_w);
+  HC_REQUIRE(a->ptr && a->idx && t_dst && t_w, HC_ERR_NULL);
+  const int64_t nblk = ceil_div(n_edges, kRadixChunk);
+  const int64_t nh = 256 * nblk, nsum = ceil_div(nh, kTScan);
+  HC_REQUIRE(nblk <= 0x7fffffffLL && nsum <= 0x7fffffffLL, HC_ERR_SIZE);
+  uint32_t* key[2];
+  uint32_t* val[2];
+  key[0] = reinterpret_cast<uint32_t*>(scratch);
+  key[1] = key[0] + n_edges;
+  val[0] = key[1] + n_edges;
+  val[1] = val[0] + n_edges;
+  uint32_t* hist = val[1] + n_edges;
+  uint32_t* sums = hist + nh;
+  // rows or leftover slots, whichever needs more threads (the tail loop is grid-strided)
+  int64_t eb = ceil_div(a->num_node * 8, 256);
+  const int64_t tail_b = ceil_div(n_edges, 256 * 8);
+  if (tail_b > eb) eb = tail_b;
+  HC_REQUIRE(eb <= 0x7fffffffLL, HC_ERR_SIZE);
+  tr_expand_kernel<<<(unsigned)eb, 256, 0, st>>>(*a, n_edges, key[0], val[0]);
+  const int passes = radix_passes(a->n_src);
+  int cur = 0;
+  for (int p = 0; p < passes; ++p) {
+    const int shift = 8 * p;
+    tr_hist_kernel<<<(unsigned)nblk, kRadixWarps * kWarp, 0, st>>>(key[cur], n_edges, shift, nblk, hist);
+    tr_block_sum_kernel<<<(unsigned)nsum, kTScan, 0, st>>>(hist, nh, sums);
+    tr_scan_sums_kernel<<<1, 1024, 0, st>>>(sums, nsum);
+    tr_scan_apply_kernel<<<(unsigned)nsum, kTScan, 0, st>>>(hist, nh, sums);
+    tr_scatter_kernel<<<(unsigned)nblk, kRadixWarps * kWarp, 0, st>>>(key[cur], val[cur], n_edges, shift, nblk,
+                                                                     hist, key[cur ^ 1], val[cur ^ 1]);
+    cur ^= 1;
   }
+  tr_finalize_kernel<<<(unsigned)ceil_div(n_edges, 256), 256, 0, st>>>(key[cur], val[cur], n_edges, a->n_src,
+                                                                      a->ptr, t_ptr, t_dst, t_w);
   HC_LAUNCH_OK();
   return 0;
 }
 
+static int64_t long_max_items(int64_t n_edges) { return 2 * (n_edges / kLongList) + 2; }
+static int64_t long_max_src(int64_t n_edges) { return n_edges / kLongList + 1; }
+
+extern "C" int64_t hc_gather_scratch_bytes(int64_t n_edges, int32_t feat) {
+  if (n_edges < 0) n_edges = 0;
+  const int64_t mi = long_max_items(n_edges), ml = long_max_src(n_edges);
+  return 256 + ml * 16 + mi * 16 + mi * (int64_t)feat * 4 + 64;
+}
+
 extern "C" int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, const int64_t* t_dst,
-                                  const float* t_w, const float* grad_out, float* grad_input,
-                                  void* stream) {
+                                  const float* t_w, int64_t n_edges, const float* grad_out,
+                                  float* grad_input, void* scratch, void* stream) {
   int rc = check_simple(a);
   if (rc) return rc;
   if (a->n_src == 0) return 0;
   HC_REQUIRE(t_ptr && grad_input, HC_ERR_NULL);
   HC_REQUIRE(a->num_node == 0 || (t_dst && t_w && grad_out), HC_ERR_NULL);
   HC_REQUIRE(a->feat % 4 == 0 && aligned16(grad_out) && aligned16(grad_input), HC_ERR_UNSUPPORTED);
+  HC_REQUIRE(n_edges >= 0, HC_ERR_SIZE);
   const int nvec = a->feat / 4;
   int G, V;
   if (nvec <= 8) { G = 8; V = 1; }
@@ -324,10 +512,33 @@ extern "C" int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, c
 #define HC_GATHER_CASE(gg, vv)                                                                   \
   if (G == gg && V == vv)                                                                        \
     aggr_bwd_gather_kernel<gg, vv><<<g, 256, 0, st>>>(a->n_src, a->feat, t_ptr, t_dst, t_w, grad_out, \
-                                                      grad_input, nvec);
+                                                      grad_input, nvec, a->num_node, a->hmap,  \
+                                                      a->src_map);
   HC_GATHER_CASE(8, 1) HC_GATHER_CASE(16, 1) HC_GATHER_CASE(32, 1) HC_GATHER_CASE(32, 2)
   HC_GATHER_CASE(32, 4) HC_GATHER_CASE(32, 8)
 #undef HC_GATHER_CASE
+  if (n_edges > kLongList) {   // only then can a list be long
+    HC_REQUIRE(scratch != nullptr && aligned_to(scratch, 16), HC_ERR_NULL);
+    LongWork w;
+    const int64_t mi = long_max_items(n_edges), ml = long_max_src(n_edges);
+    char* p = reinterpret_cast<char*>(scratch);
+    w.counters = reinterpret_cast<unsigned long long*>(p); p += 256;
+    w.long_src = reinterpret_cast<int64_t*>(p); p += ml * 8;
+    w.long_base = reinterpret_cast<int64_t*>(p); p += ml * 8;
+    w.item_src = reinterpret_cast<int64_t*>(p); p += mi * 8;
+    w.item_chunk = reinterpret_cast<int32_t*>(p); p += mi * 8;
+    w.partial = reinterpret_cast<float*>(p);
+    w.max_long = ml; w.max_items = mi;
+    HC_CUDA(cudaMemsetAsync(w.counters, 0, 16, st));
+    long_collect_kernel<<<(unsigned)ceil_div(a->n_src, 256), 256, 0, st>>>(a->n_src, t_ptr, w);
+    const unsigned ib = (unsigned)(mi < 148 * 8 ? mi : 148 * 8);
+    const size_t smem = (size_t)8 * a->feat * sizeof(float);
+    HC_REQUIRE(smem <= 48 * 1024, HC_ERR_UNSUPPORTED);
+    long_items_kernel<<<ib, 256, smem, st>>>(a->feat, t_ptr, t_dst, t_w, grad_out, w, a->num_node, a->hmap,
+                                             a->src_map);
+    const unsigned rb = (unsigned)(ml < 148 * 4 ? ml : 148 * 4);
+    long_reduce_kernel<<<rb, 256, 0, st>>>(a->feat, t_ptr, w, grad_input);
+  }
   HC_LAUNCH_OK();
   return 0;
 }

@@ -200,16 +200,16 @@ class _AggrFunction(torch.autograd.Function):
                        src_map, src_alt)
         g_in = torch.empty(inp.shape, dtype=torch.float32, device=dev) if need_in else None
         g_ev = torch.empty_like(edge_value) if need_ev else None
-        # large blocks: gather over the transposed block instead of the atomic scatter
+        # gather over the transposed block instead of the atomic scatter: always when a
+        # reproducible backward is asked for, else for blocks large enough to pay for it
         gathered = False
-        if (need_in and edge_value is None and inp.dim() == 2 and inp.shape[1] % 4 == 0
-                and GATHER_MIN_FEAT <= inp.shape[1] <= 1024
-                and idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES):
-            t_ptr, t_dst, t_w = transpose_block(PreparedAggr(a, None, dev, ""), idx_t.numel())
-            with on_device(dev), _span(_tag("hc_aggr_bwd_gather", inp), dev):
-                check(lib.hc_aggr_bwd_gather(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(grad_out),
-                                             ptr(g_in), stream_of(dev)), "hc_aggr_bwd_gather")
-            _called()
+        can_gather = (need_in and edge_value is None and inp.dim() == 2 and inp.shape[1] % 4 == 0
+                      and inp.shape[1] <= 1024)
+        if can_gather and (DETERMINISTIC_BWD or (inp.shape[1] >= GATHER_MIN_FEAT and
+                                                 idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES)):
+            t_ptr, t_dst, t_w, n_edges = shared_transpose(ptr_t, idx_t)
+            run_aggr_bwd_gather(PreparedAggr(a, None, dev, _tag("", inp)), t_ptr, t_dst, t_w, grad_out, g_in,
+                                n_edges=n_edges)
             gathered = True
         g_h = None
         if need_h:
@@ -307,27 +307,61 @@ GATHER_MIN_BYTES = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_BYTES", 64 << 20)
 GATHER_MIN_FEAT = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_FEAT", 256))
 
 
+# True: every aggregation backward that can takes the transposed gather, whose sums have a fixed
+# order, so a training step is reproducible bit for bit (the scatter's atomics are not)
+DETERMINISTIC_BWD = os.environ.get("HISCACHE_DETERMINISTIC_BWD", "0") not in ("", "0")
+
+
 def transpose_block(p: PreparedAggr, max_edges):
     """(t_ptr [n_src+1], t_dst [max_edges], t_w [max_edges]): per source the ascending list of
     miss destination rows that have it as a neighbour, with the weight 1/deg of each."""
     dev, a = p.dev, p.args
     n_src = int(a.n_src)
+    n_edges = max(int(max_edges), 1)
     t_ptr = torch.empty(n_src + 1, dtype=torch.int64, device=dev)
-    t_dst = torch.empty(max(int(max_edges), 1), dtype=torch.int64, device=dev)
-    t_w = torch.empty(max(int(max_edges), 1), dtype=torch.float32, device=dev)
-    sc = scratch(dev, lib.hc_transpose_scratch_bytes(n_src), "transpose")
+    t_dst = torch.empty(n_edges, dtype=torch.int64, device=dev)
+    t_w = torch.empty(n_edges, dtype=torch.float32, device=dev)
+    sc = scratch(dev, lib.hc_transpose_scratch_bytes(n_src, n_edges), "transpose")
     with on_device(dev), _span("hc_transpose_block", dev):
-        check(lib.hc_transpose_block(C.byref(a), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(sc),
+        check(lib.hc_transpose_block(C.byref(a), int(max_edges), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(sc),
                                      stream_of(dev)), "hc_transpose_block")
-    _called(7)
+    _called(2 + 5 * max(1, (max(n_src, 1).bit_length() + 7) // 8))
     return t_ptr, t_dst, t_w
 
 
-def run_aggr_bwd_gather(p: PreparedAggr, t_ptr, t_dst, t_w, grad_out, grad_input):
+_shared_t = {}
+
+
+def shared_transpose(ptr_t, idx_t):
+    """Transposition of a batch's whole CSR, built once and reused by the backward pass of every
+    layer: all layers of a sampled batch aggregate over a prefix of the same (ptr, idx), and a
+    source's list is sorted by destination row, so the list of a smaller layer is a prefix of it
+    (hc_aggr_bwd_gather skips the rest).  Keyed by the two tensors' storage; one entry per device."""
+    dev = ptr_t.device
+    key = (ptr_t.data_ptr(), idx_t.data_ptr(), ptr_t.shape[0], idx_t.shape[0], ptr_t._version, idx_t._version)
+    hit = _shared_t.get(dev)
+    if hit is not None and hit[0] == key:
+        return hit[1]
+    n_rows = ptr_t.shape[0] - 1
+    a = AggrArgs()
+    a.struct_size = C.sizeof(AggrArgs)
+    a.ptr, a.idx, a.num_node = ptr(ptr_t), ptr(idx_t), n_rows
+    a.feat, a.num_head = 4, 1
+    # any node of the batch may be a source: local ids are below the number of edges + rows
+    a.n_src = int(idx_t.shape[0]) + n_rows + 1
+    res = transpose_block(PreparedAggr(a, None, dev, ""), idx_t.shape[0]) + (int(idx_t.shape[0]),)
+    _shared_t[dev] = (key, res, (ptr_t, idx_t))   # the tensors stay alive with the entry
+    return res
+
+
+def run_aggr_bwd_gather(p: PreparedAggr, t_ptr, t_dst, t_w, grad_out, grad_input, n_edges=None):
+    n_edges = int(t_dst.shape[0] if n_edges is None else n_edges)
+    feat = int(p.args.feat)
+    sc = scratch(p.dev, lib.hc_gather_scratch_bytes(n_edges, feat), "gather") if n_edges > 1024 else None
     with torch.cuda.device(p.dev), _span("hc_aggr_bwd_gather" + p.tag, p.dev):
-        check(lib.hc_aggr_bwd_gather(C.byref(p.args), ptr(t_ptr), ptr(t_dst), ptr(t_w), ptr(grad_out),
-                                     ptr(grad_input), stream_of(p.dev)), "hc_aggr_bwd_gather")
-    _called()
+        check(lib.hc_aggr_bwd_gather(C.byref(p.args), ptr(t_ptr), ptr(t_dst), ptr(t_w), n_edges, ptr(grad_out),
+                                     ptr(grad_input), ptr(sc), stream_of(p.dev)), "hc_aggr_bwd_gather")
+    _called(4 if n_edges > 1024 else 1)
 
 
 def aggr_forward_history(input, ptr, idx, history_map, history_buffer, history_size, num_node):

@@ -56,9 +56,10 @@ _SIGS = {
     "hc_error_string": (C.c_char_p, [C.c_int]),
     "hc_aggr_fwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp]),
     "hc_aggr_bwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp, i32, vp, vp, vp, i32, vp]),
-    "hc_transpose_scratch_bytes": (i64, [i64]),
-    "hc_transpose_block": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, vp, vp]),
-    "hc_aggr_bwd_gather": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, vp, vp, vp]),
+    "hc_transpose_scratch_bytes": (i64, [i64, i64]),
+    "hc_transpose_block": (C.c_int, [C.POINTER(AggrArgs), i64, vp, vp, vp, vp, vp]),
+    "hc_gather_scratch_bytes": (i64, [i64, i32]),
+    "hc_aggr_bwd_gather": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, i64, vp, vp, vp, vp]),
     "hc_score_rows": (C.c_int, [vp, i64, i32, i64, i32, vp, vp]),
     "hc_select_scratch_bytes": (i64, [i64]),
     "hc_select_threshold": (C.c_int, [vp, i64, f32, vp, vp, vp]),
@@ -202,11 +203,17 @@ def rows2d(t, name="rows"):
 _scratch = {}
 
 
+_retired = []
+
+
 def scratch(dev: torch.device, nbytes: int, tag: str) -> torch.Tensor:
     """Per-device grow-only scratch (the C ABI never allocates)."""
     key = (dev.index, tag)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = torch.empty(max(int(nbytes), 4096), dtype=torch.uint8, device=dev)
+        if buf is not None:
+            # a captured CUDA graph may still hold the old address: never hand it back
+            _retired.append(buf)
+        buf = torch.empty(max(int(nbytes) * 5 // 4, 4096), dtype=torch.uint8, device=dev)
         _scratch[key] = buf
     return buf

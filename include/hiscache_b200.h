@@ -136,24 +136,36 @@ int hc_aggr_bwd(const hc_aggr_args* a, const float* grad_out, float* grad_input,
 
 /*
  * Backward as a gather over the transposed block (mean aggregation, one head,
- * no edge values): the alternative to the atomic scatter of hc_aggr_bwd for
- * blocks whose grad_input does not fit L2.  No reference counterpart (the
- * reference only scatters, history_aggr.cu:127-168).
- *   hc_transpose_block: t_ptr [n_src+1], t_dst / t_w [<= number of edges]: for
- *     every source s the ascending list of destination rows r < num_node with
- *     hmap[r] == -1 that have s as a neighbour (once per edge) and, beside each,
- *     the weight 1/deg(r); sources with src_map[s] != -1 are left empty.
- *     scratch >= hc_transpose_scratch_bytes(n_src).
+ * no edge values): the alternative to the atomic scatter of hc_aggr_bwd, with
+ * no atomics on the data, no zero-fill and a bit-reproducible result.  No
+ * reference counterpart (the reference only scatters, history_aggr.cu:127-168).
+ *   hc_transpose_block: a stable radix sort of the block's edge slots
+ *     [0, n_edges) by source (n_edges >= ptr[num_node]; slots behind it are
+ *     ignored).  t_ptr [n_src+1], t_dst / t_w [n_edges]: for every source s the
+ *     ascending list of destination rows r < num_node with hmap[r] == -1 that
+ *     have s as a neighbour (once per edge) and, beside each, the weight
+ *     1/deg(r); sources with src_map[s] != -1 are left empty.  The cost does
+ *     not depend on the skew of the source popularity.
+ *     scratch >= hc_transpose_scratch_bytes(n_src, n_edges).
  *   hc_aggr_bwd_gather: grad_input[s, :] = sum over that list of
- *     t_w * grad_out[r, :]; every row of grad_input is written (zeros for
- *     empty lists), so it needs no clearing, and the result is deterministic.
- *     feat must be a multiple of 4 and <= 1024.
+ *     t_w * grad_out[r, :] for s < n_src; every row of grad_input is written
+ *     (zeros for empty lists), so it needs no clearing.  The lists may come
+ *     from a transposition of a LARGER block that has this one as a prefix
+ *     (the layers of a sampled batch share one CSR): entries with
+ *     r >= num_node or hmap[r] != -1 are skipped, as are sources with
+ *     src_map[s] != -1.  Lists longer than 1024 entries are split over many
+ *     thread blocks and their chunk sums added in chunk order.
+ *     feat must be a multiple of 4 and <= 1024; n_edges as given to the
+ *     transposition; scratch >= hc_gather_scratch_bytes(n_edges, feat),
+ *     16-byte aligned (may be NULL when n_edges <= 1024).
  */
-int64_t hc_transpose_scratch_bytes(int64_t n_src);
-int hc_transpose_block(const hc_aggr_args* a, int64_t* t_ptr, int64_t* t_dst, float* t_w,
-                       void* scratch, void* stream);
+int64_t hc_transpose_scratch_bytes(int64_t n_src, int64_t n_edges);
+int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_t* t_ptr, int64_t* t_dst,
+                       float* t_w, void* scratch, void* stream);
+int64_t hc_gather_scratch_bytes(int64_t n_edges, int32_t feat);
 int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, const int64_t* t_dst,
-                       const float* t_w, const float* grad_out, float* grad_input, void* stream);
+                       const float* t_w, int64_t n_edges, const float* grad_out,
+                       float* grad_input, void* scratch, void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Scores and thresholds                                                    */

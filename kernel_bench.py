@@ -35,10 +35,17 @@ def time_launches(fn, reps, warmup=3):
     return e0.elapsed_time(e1) / reps
 
 
+SKEW = False    # True: sources drawn as floor(n_src * u^3), the popularity law of the bench graph
+
+
 def block(n_dst, deg, n_src, dev, seed=1):
     g = torch.Generator(device=dev)
     g.manual_seed(seed)
-    idx = torch.randint(0, n_src, (n_dst * deg,), generator=g, device=dev)
+    if SKEW:
+        u = torch.rand(n_dst * deg, generator=g, device=dev, dtype=torch.float64)
+        idx = (u.pow_(3.0) * n_src).to(torch.int64).clamp_(max=n_src - 1)
+    else:
+        idx = torch.randint(0, n_src, (n_dst * deg,), generator=g, device=dev)
     ptr = torch.arange(0, n_dst * deg + 1, deg, device=dev)
     return ptr, idx
 
@@ -127,7 +134,7 @@ def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0"):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "bwd_gather", "load"])
+    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "bwd_gather", "load", "fwd_bwd"])
     ap.add_argument("--dst", type=int, default=2_000_000)
     ap.add_argument("--deg", type=int, default=10)
     ap.add_argument("--src", type=int, default=16_000_000)
@@ -137,7 +144,11 @@ def main():
     ap.add_argument("--host", action="store_true", help="load: table in pinned host memory")
     ap.add_argument("--thp", action="store_true", help="load --host: back the table with 2 MB huge pages")
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--skew", action="store_true",
+                    help="neighbours drawn as floor(n_src * u^3) (hub sources) instead of uniformly")
     args = ap.parse_args()
+    global SKEW
+    SKEW = args.skew
     dt = torch.float16 if args.dtype == "f16" else torch.float32
     extra = {}
     if args.op == "fwd":
@@ -147,10 +158,25 @@ def main():
     elif args.op == "bwd_gather":
         ms, byts, ms_t = bench_bwd_gather(args.dst, args.deg, args.src, args.feat, args.reps)
         extra = {"transpose_ms": round(ms_t, 4)}
+    elif args.op == "fwd_bwd":
+        # forward + backward of one block as a training step runs them; the transposition is paid
+        # once per batch and serves the backward of all `layers` convs that share its CSR
+        layers = 3
+        ms_f, b_f = bench_fwd(args.dst, args.deg, args.src, args.feat, dt, args.reps)
+        torch.cuda.empty_cache()
+        ms_s, b_s = bench_bwd(args.dst, args.deg, args.src, args.feat, args.reps)
+        torch.cuda.empty_cache()
+        ms_g, b_g, ms_t = bench_bwd_gather(args.dst, args.deg, args.src, args.feat, args.reps)
+        ms, byts = ms_f + ms_g + ms_t / layers, b_f + b_g
+        extra = {"fwd_ms": round(ms_f, 4), "fwd_GBps": round(b_f / ms_f / 1e6, 1),
+                 "bwd_scatter_ms": round(ms_s, 4), "bwd_scatter_GBps": round(b_s / ms_s / 1e6, 1),
+                 "bwd_gather_ms": round(ms_g, 4), "bwd_gather_GBps": round(b_g / ms_g / 1e6, 1),
+                 "transpose_ms": round(ms_t, 4), "transpose_amortised_over_layers": layers,
+                 "fwd_plus_scatter_GBps": round((b_f + b_s) / (ms_f + ms_s) / 1e6, 1)}
     else:
         ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host, args.thp)
     print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
-                      "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate,
+                      "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate, "skew": args.skew,
                       "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1), **extra}))
 
 

@@ -65,3 +65,32 @@ def layered_batch(rng, n_seed, fanouts, total_nodes, dedup=True):
                 sub_to_full=np.asarray(sub_to_full, dtype=np.int64),
                 num_node_in_layer=np.asarray(layer_nodes, dtype=np.int64),
                 num_edge_in_layer=np.asarray(layer_edges, dtype=np.int64))
+
+
+WORST = {}   # label -> largest observed |error| / allowed, printed at the end of the session
+
+
+def close(got, want, rtol, bound=None, terms=64, label="aggr"):
+    """|got - want| <= rtol * |want| + (terms + 2) * 2^-23 * bound, element by element.
+
+    `want` comes from the oracle, which accumulates in fp64.  The library adds `terms` fp32 numbers
+    whose absolute values sum to `bound` (the oracle run on |inputs|), so its rounding error is at
+    most about terms * 2^-24 * bound: that is the whole absolute allowance, there is no free
+    constant.  Where a sum cancels, |want| is small but `bound` is not, which is what keeps the
+    test meaningful there.  With bound=None the allowance is relative only."""
+    got = got.detach().double().cpu().numpy()
+    want = np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape
+    allowed = rtol * np.abs(want)
+    if bound is not None:
+        allowed = allowed + (terms + 2) * 2.0 ** -23 * np.asarray(bound, dtype=np.float64)
+    err = np.abs(got - want)
+    bad = err > allowed
+    if err.size:
+        with np.errstate(divide="ignore", invalid="ignore"):
+            ratio = np.where(allowed > 0, err / allowed, np.where(err > 0, np.inf, 0.0))
+        WORST[label] = max(WORST.get(label, 0.0), float(ratio.max()))
+    assert not bad.any(), (f"{int(bad.sum())} of {err.size} elements outside the tolerance; worst error "
+                           f"{float(err.max()):.3e}, worst error/allowed {float(ratio.max()):.2f}")
+
+

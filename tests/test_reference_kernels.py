@@ -14,7 +14,7 @@ import numpy as np
 import pytest
 import torch
 
-from _gen import csr_block, layered_batch
+from _gen import close as _close, csr_block, layered_batch
 
 pytestmark = pytest.mark.gpu
 
@@ -36,9 +36,9 @@ def cu(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def close(t, want, rtol=1e-5, scale=8.0):
-    # the reference divides with --use_fast_math (CMakeLists.txt:58): a few ulp
-    np.testing.assert_allclose(t.detach().cpu().numpy(), want, rtol=rtol, atol=rtol * scale)
+def close(t, want, bound, terms, rtol=1e-5):
+    # the reference divides with --use_fast_math (CMakeLists.txt:58): a few ulp, inside rtol
+    _close(t, want, rtol, bound=bound, terms=terms, label="reference_kernels")
 
 
 @pytest.mark.parametrize("feat", [32, 128, 256])
@@ -54,18 +54,21 @@ def test_reference_aggr_fwd_bwd(ref, oracle, backend, feat):
     p, i, hm = cu(ptr), cu(idx), cu(hmap)
     out_ref = ref.aggr_forward_history(xs, p, i, hm, hb, feat, num_dst)
     want = oracle.aggr_fwd(ptr, idx, x, num_dst, hmap=hmap, hbuf=hbuf)
-    close(out_ref, want)
+    fb = oracle.aggr_fwd(ptr, idx, np.abs(x), num_dst, hmap=hmap, hbuf=np.abs(hbuf))
+    max_deg, in_deg = int(np.diff(ptr).max()), int(np.bincount(idx, minlength=n_src).max())
+    close(out_ref, want, fb, max_deg)
     out_ref.backward(cu(g))
     torch.cuda.synchronize()
     gi, gh, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, hmap=hmap, hsize=feat)
-    close(xs.grad, gi)
-    close(hb.grad, gh)
+    gib, ghb, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, np.abs(g), hmap=hmap, hsize=feat)
+    close(xs.grad, gi, gib, in_deg)
+    close(hb.grad, gh, ghb, 1)
     # and the new library against the reference directly
     xs2, hb2 = cu(x).requires_grad_(True), cu(hbuf).requires_grad_(True)
     out_new = backend.aggr_forward_history(xs2, p, i, hm, hb2, feat, num_dst)
-    close(out_new, out_ref.detach().cpu().numpy())
+    close(out_new, out_ref.detach().cpu().numpy(), fb, max_deg)
     out_new.backward(cu(g))
-    close(xs2.grad, xs.grad.cpu().numpy())
+    close(xs2.grad, xs.grad.cpu().numpy(), gib, in_deg)
     assert torch.equal(hb2.grad, hb.grad)
 
 
@@ -86,14 +89,17 @@ def test_reference_edge_value(ref, oracle, heads):
     p, i, hm, hb = cu(ptr), cu(idx), cu(hmap), cu(hbuf)
     out = ref.aggr_forward_history_edge_value(xs, p, i, evs, hm, hb, feat * heads, num_dst)
     want = oracle.aggr_fwd(ptr, idx, x, num_dst, edge_value=ev, hmap=hmap, hbuf=hbuf)
-    close(out, want, scale=16.0)
+    fb = oracle.aggr_fwd(ptr, idx, np.abs(x), num_dst, edge_value=np.abs(ev), hmap=hmap, hbuf=np.abs(hbuf))
+    close(out, want, fb, int(np.diff(ptr).max()))
     g = rng.standard_normal(want.shape, dtype=np.float32)
     out.backward(cu(g))
     torch.cuda.synchronize()
     gi, _, eg = oracle.aggr_bwd(ptr, idx, x, num_dst, g, edge_value=ev, hmap=hmap,
                                 hsize=feat * heads, want_edge_grad=True)
-    close(xs.grad, gi, scale=16.0)
-    close(evs.grad, eg, scale=64.0)
+    gib, _, egb = oracle.aggr_bwd(ptr, idx, np.abs(x), num_dst, np.abs(g), edge_value=np.abs(ev), hmap=hmap,
+                                  hsize=feat * heads, want_edge_grad=True)
+    close(xs.grad, gi, gib, int(np.bincount(idx, minlength=n_src).max()))
+    close(evs.grad, eg, egb, feat)
 
 
 def test_reference_used_masks_and_count(ref, oracle):

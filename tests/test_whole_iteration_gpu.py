@@ -95,9 +95,11 @@ def test_train_step_equals_cpu_restatement(backend, oracle, shape, monkeypatch):
         worst["loss"] = max(worst["loss"], abs(loss_gpu - loss_cpu) / abs(loss_cpu))
         np.testing.assert_allclose(loss_gpu, loss_cpu, rtol=1e-4)
         np.testing.assert_allclose(kept["his"], L["his"], rtol=1e-4, atol=1e-5)
-        np.testing.assert_allclose(kept["score"], L["score"], rtol=1e-4, atol=1e-9)
-        worst["score"] = max(worst["score"], float(np.max(np.abs(kept["score"] - L["score"]) /
-                                                          np.maximum(np.abs(L["score"]), 1e-12))))
+        # a score is the norm of a gradient row that went through the dense layers' fp32 GEMMs: its
+        # absolute error is a few 1e-7 of the largest scores, whatever its own size
+        np.testing.assert_allclose(kept["score"], L["score"], rtol=1e-4, atol=1e-3 * float(np.median(L["score"])))
+        worst["score"] = max(worst["score"], float(np.max(np.abs(kept["score"] - L["score"])) /
+                                                   float(np.median(L["score"]))))
         # ---- bit-exact: the admission (ids, slots, header)
         assert tr.table.header == int(cpu.header[0]), f"step {step}: header"
         assert np.array_equal(tr.table.full2embed.cpu().numpy(), cpu.full2embed), f"step {step}: full2embed"
@@ -115,4 +117,4 @@ def test_train_step_equals_cpu_restatement(backend, oracle, shape, monkeypatch):
                                    cpu.model.lin_r[i].weight.detach().numpy(), rtol=1e-3, atol=2e-4)
     np.testing.assert_allclose(tr.model.convs[-1].lin_l.bias.detach().cpu().numpy(),
                                cpu.model.lin_l[-1].bias.detach().numpy(), rtol=1e-3, atol=2e-4)
-    print("max relative error: loss %.2e, score %.2e" % (worst["loss"], worst["score"]))
+    print("max relative error: loss %.2e; max score error / median score %.2e" % (worst["loss"], worst["score"]))
