@@ -213,11 +213,13 @@ __global__ void __launch_bounds__(256)
 // of a batch's CSR serves every layer, because all layers share the CSR prefix): entries whose
 // destination row is >= num_node, or is served from history (hmap[r] != -1), are skipped.
 //
-// Lists longer than kLongList entries (hub sources of a skewed block) are left to the
-// long-list kernels below, which split them into chunks over many blocks and add the chunk
-// sums in chunk order, so the result stays bit-reproducible.
+// Lists longer than kLongList entries (popular sources of a skewed block) are left to the
+// block-per-list kernels below: one thread block per list of up to kChunk entries, hub lists
+// split into chunks of kChunk whose sums are added in chunk order, so the result stays
+// bit-reproducible.
 constexpr int kSW = 8;
-constexpr int kLongList = 1024;
+constexpr int kLongList = 64;     // longer lists take the block-per-list path
+constexpr int kChunk = 2048;       // entries per work item of that path
 
 __device__ __forceinline__ bool entry_counts(int64_t r, int64_t num_node, const int64_t* __restrict__ hmap) {
   return r < num_node && !(hmap && hmap[r] != -1);
@@ -313,16 +315,17 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- long lists -----------------------------------------------------------
-// work items (source, chunk) of kLongList entries each; item i writes its partial sum to
-// partial[i, :]; a last kernel adds a source's partials in chunk order.
+// work items (source, chunk).  A list of at most kChunk entries is one item that writes its
+// grad_input row itself; a longer one is split into chunks whose items write partial[slot, :],
+// added in chunk order by a last kernel.
 struct LongWork {
-  unsigned long long* counters;  // [0] number of long sources, [1] number of items
-  int64_t* long_src;             // [max_long]
-  int64_t* long_base;            // [max_long] first item of the source
+  unsigned long long* counters;  // [0] items, [1] partial slots, [2] split sources
   int64_t* item_src;             // [max_items]
-  int32_t* item_chunk;           // [max_items]
-  float* partial;                // [max_items, feat]
-  int64_t max_long, max_items;
+  int64_t* item_info;            // [max_items] chunk number << 32 | (partial slot + 1), 0 = direct
+  int64_t* split_src;            // [max_split]
+  int64_t* split_base;           // [max_split] first partial slot of the source
+  float* partial;                // [max_slots, feat]
+  int64_t max_items, max_slots, max_split;
 };
 
 __global__ void __launch_bounds__(256)
@@ -331,56 +334,91 @@ __global__ void __launch_bounds__(256)
   if (s >= n_src) return;
   const int64_t len = t_ptr[s + 1] - t_ptr[s];
   if (len <= kLongList) return;
-  const int64_t chunks = ceil_div(len, kLongList);
-  const int64_t li = (int64_t)atomicAdd(&w.counters[0], 1ull);
-  const int64_t base = (int64_t)atomicAdd(&w.counters[1], (unsigned long long)chunks);
-  // the bounds hold by construction (every long list has more than kLongList of the n_edges entries)
-  if (li >= w.max_long || base + chunks > w.max_items) return;
-  w.long_src[li] = s;
-  w.long_base[li] = base;
+  const int64_t chunks = ceil_div(len, kChunk);
+  const int64_t first = (int64_t)atomicAdd(&w.counters[0], (unsigned long long)chunks);
+  // the bounds hold by construction (lists are disjoint slices of the n_edges entries)
+  if (first + chunks > w.max_items) return;
+  if (chunks == 1) {
+    w.item_src[first] = s;
+    w.item_info[first] = 0;
+    return;
+  }
+  const int64_t slot = (int64_t)atomicAdd(&w.counters[1], (unsigned long long)chunks);
+  const int64_t li = (int64_t)atomicAdd(&w.counters[2], 1ull);
+  if (slot + chunks > w.max_slots || li >= w.max_split) return;
+  w.split_src[li] = s;
+  w.split_base[li] = slot;
   for (int64_t c = 0; c < chunks; ++c) {
-    w.item_src[base + c] = s;
-    w.item_chunk[base + c] = (int32_t)c;
+    w.item_src[first + c] = s;
+    w.item_info[first + c] = (c << 32) | (slot + c + 1);
   }
 }
 
-// one block per item: warp q takes entries q, q+8, ... of the chunk; the eight warp sums are
-// added in warp order through shared memory
+// one block per item: warp q takes entries q*U.., (q+8)*U.. of the item with U row loads in
+// flight per lane; the eight warp sums are added in warp order through shared memory
+template <int V>
 __global__ void __launch_bounds__(256)
-    long_items_kernel(const int feat, const int64_t* __restrict__ t_ptr, const int64_t* __restrict__ t_dst,
-                      const float* __restrict__ t_w, const float* __restrict__ grad_out, LongWork w,
+    long_items_kernel(const int feat, const int nvec, const int64_t* __restrict__ t_ptr,
+                      const int64_t* __restrict__ t_dst, const float* __restrict__ t_w,
+                      const float* __restrict__ grad_out, LongWork w, float* __restrict__ grad_input,
                       const int64_t num_node, const int64_t* __restrict__ hmap,
                       const int64_t* __restrict__ src_map) {
   extern __shared__ __align__(16) float sh[];   // [8][feat]
-  const int64_t n_items = (int64_t)w.counters[1] < w.max_items ? (int64_t)w.counters[1] : w.max_items;
+  constexpr int U = V == 1 ? 4 : (V == 2 ? 2 : 1);
+  int64_t n_items = (int64_t)w.counters[0];
+  if (n_items > w.max_items) n_items = w.max_items;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
     const int64_t s = w.item_src[item];
-    const int64_t begin = t_ptr[s] + (int64_t)w.item_chunk[item] * kLongList;
-    int64_t end = begin + kLongList;
+    const int64_t info = w.item_info[item];
+    const int64_t chunk = info >> 32, slot = (info & 0xffffffffLL) - 1;
+    const int64_t begin = t_ptr[s] + chunk * kChunk;
+    int64_t end = begin + kChunk;
     if (end > t_ptr[s + 1]) end = t_ptr[s + 1];
     if (src_map && src_map[s] != -1) end = begin;
-    for (int c0 = 0; c0 < feat; c0 += 128) {   // 128 columns (one float4 per lane) at a time
-      const int col = c0 + 4 * lane;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int64_t j = begin + warp; j < end; j += 8) {
-        const int64_t r = t_dst[j];
-        if (!entry_counts(r, num_node, hmap)) continue;
-        const float wt = t_w[j];
-        if (col < feat) {
-          const float4 g = __ldg(reinterpret_cast<const float4*>(grad_out + r * feat + col));
-          acc.x = fmaf(wt, g.x, acc.x); acc.y = fmaf(wt, g.y, acc.y);
-          acc.z = fmaf(wt, g.z, acc.z); acc.w = fmaf(wt, g.w, acc.w);
+    float4 acc[V];
+#pragma unroll
+    for (int q = 0; q < V; ++q) acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t j0 = begin + warp * U; j0 < end; j0 += 8 * U) {
+      float4 buf[U][V];
+      float wt[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t j = j0 + u;
+        bool ok = j < end;
+        const int64_t r = ok ? t_dst[j] : 0;
+        wt[u] = ok ? t_w[j] : 0.f;
+        ok = ok && entry_counts(r, num_node, hmap);
+        if (!ok) wt[u] = 0.f;
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+          const int v = lane + q * 32;
+          buf[u][q] = (ok && v < nvec) ? __ldg(reinterpret_cast<const float4*>(grad_out + r * feat) + v)
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
-      if (col < feat) *reinterpret_cast<float4*>(sh + warp * feat + col) = acc;
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int q = 0; q < V; ++q) {
+          acc[q].x = fmaf(wt[u], buf[u][q].x, acc[q].x);
+          acc[q].y = fmaf(wt[u], buf[u][q].y, acc[q].y);
+          acc[q].z = fmaf(wt[u], buf[u][q].z, acc[q].z);
+          acc[q].w = fmaf(wt[u], buf[u][q].w, acc[q].w);
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < V; ++q) {
+      const int v = lane + q * 32;
+      if (v < nvec) reinterpret_cast<float4*>(sh + warp * feat)[v] = acc[q];
     }
     __syncthreads();
+    float* dst = slot < 0 ? grad_input + s * feat : w.partial + slot * feat;
     for (int c = threadIdx.x; c < feat; c += blockDim.x) {
       float t = sh[c];
 #pragma unroll
       for (int q = 1; q < 8; ++q) t += sh[q * feat + c];
-      w.partial[item * feat + c] = t;
+      dst[c] = t;
     }
     __syncthreads();
   }
@@ -389,10 +427,11 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(256)
     long_reduce_kernel(const int feat, const int64_t* __restrict__ t_ptr, LongWork w,
                        float* __restrict__ grad_input) {
-  const int64_t n_long = (int64_t)w.counters[0] < w.max_long ? (int64_t)w.counters[0] : w.max_long;
-  for (int64_t li = blockIdx.x; li < n_long; li += gridDim.x) {
-    const int64_t s = w.long_src[li], base = w.long_base[li];
-    const int64_t chunks = ceil_div(t_ptr[s + 1] - t_ptr[s], (int64_t)kLongList);
+  int64_t n_split = (int64_t)w.counters[2];
+  if (n_split > w.max_split) n_split = w.max_split;
+  for (int64_t li = blockIdx.x; li < n_split; li += gridDim.x) {
+    const int64_t s = w.split_src[li], base = w.split_base[li];
+    const int64_t chunks = ceil_div(t_ptr[s + 1] - t_ptr[s], (int64_t)kChunk);
     for (int c = threadIdx.x; c < feat; c += blockDim.x) {
       float t = 0.f;
       for (int64_t k = 0; k < chunks; ++k) t += w.partial[(base + k) * feat + c];
@@ -477,20 +516,24 @@ extern "C" int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_
   return 0;
 }
 
-static int64_t long_max_items(int64_t n_edges) { return 2 * (n_edges / kLongList) + 2; }
-static int64_t long_max_src(int64_t n_edges) { return n_edges / kLongList + 1; }
+// every list longer than kLongList is at least one item; split lists add one item per chunk
+static int64_t long_max_items(int64_t n_edges) { return n_edges / kLongList + n_edges / kChunk + 2; }
+static int64_t long_max_slots(int64_t n_edges) { return 2 * (n_edges / kChunk) + 2; }
+static int64_t long_max_split(int64_t n_edges) { return n_edges / kChunk + 1; }
 
 extern "C" int64_t hc_gather_scratch_bytes(int64_t n_edges, int32_t feat) {
   if (n_edges < 0) n_edges = 0;
-  const int64_t mi = long_max_items(n_edges), ml = long_max_src(n_edges);
-  return 256 + ml * 16 + mi * 16 + mi * (int64_t)feat * 4 + 64;
+  return 256 + long_max_items(n_edges) * 16 + long_max_split(n_edges) * 16 +
+         long_max_slots(n_edges) * (int64_t)feat * 4 + 64;
 }
 
 extern "C" int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, const int64_t* t_dst,
-                                  const float* t_w, int64_t n_edges, const float* grad_out,
-                                  float* grad_input, void* scratch, void* stream) {
+                                  const float* t_w, int64_t t_n_src, int64_t n_edges,
+                                  const float* grad_out, float* grad_input, void* scratch,
+                                  void* stream) {
   int rc = check_simple(a);
   if (rc) return rc;
+  HC_REQUIRE(a->n_src <= t_n_src, HC_ERR_SIZE);   // t_ptr has t_n_src + 1 entries
   if (a->n_src == 0) return 0;
   HC_REQUIRE(t_ptr && grad_input, HC_ERR_NULL);
   HC_REQUIRE(a->num_node == 0 || (t_dst && t_w && grad_out), HC_ERR_NULL);
@@ -520,23 +563,29 @@ extern "C" int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, c
   if (n_edges > kLongList) {   // only then can a list be long
     HC_REQUIRE(scratch != nullptr && aligned_to(scratch, 16), HC_ERR_NULL);
     LongWork w;
-    const int64_t mi = long_max_items(n_edges), ml = long_max_src(n_edges);
+    w.max_items = long_max_items(n_edges);
+    w.max_slots = long_max_slots(n_edges);
+    w.max_split = long_max_split(n_edges);
     char* p = reinterpret_cast<char*>(scratch);
     w.counters = reinterpret_cast<unsigned long long*>(p); p += 256;
-    w.long_src = reinterpret_cast<int64_t*>(p); p += ml * 8;
-    w.long_base = reinterpret_cast<int64_t*>(p); p += ml * 8;
-    w.item_src = reinterpret_cast<int64_t*>(p); p += mi * 8;
-    w.item_chunk = reinterpret_cast<int32_t*>(p); p += mi * 8;
+    w.item_src = reinterpret_cast<int64_t*>(p); p += w.max_items * 8;
+    w.item_info = reinterpret_cast<int64_t*>(p); p += w.max_items * 8;
+    w.split_src = reinterpret_cast<int64_t*>(p); p += w.max_split * 8;
+    w.split_base = reinterpret_cast<int64_t*>(p); p += w.max_split * 8;
     w.partial = reinterpret_cast<float*>(p);
-    w.max_long = ml; w.max_items = mi;
-    HC_CUDA(cudaMemsetAsync(w.counters, 0, 16, st));
+    HC_CUDA(cudaMemsetAsync(w.counters, 0, 32, st));
     long_collect_kernel<<<(unsigned)ceil_div(a->n_src, 256), 256, 0, st>>>(a->n_src, t_ptr, w);
-    const unsigned ib = (unsigned)(mi < 148 * 8 ? mi : 148 * 8);
+    const unsigned ib = (unsigned)(w.max_items < 148 * 16 ? w.max_items : 148 * 16);
     const size_t smem = (size_t)8 * a->feat * sizeof(float);
     HC_REQUIRE(smem <= 48 * 1024, HC_ERR_UNSUPPORTED);
-    long_items_kernel<<<ib, 256, smem, st>>>(a->feat, t_ptr, t_dst, t_w, grad_out, w, a->num_node, a->hmap,
-                                             a->src_map);
-    const unsigned rb = (unsigned)(ml < 148 * 4 ? ml : 148 * 4);
+    const int LV = nvec <= 32 ? 1 : (nvec <= 64 ? 2 : (nvec <= 128 ? 4 : 8));
+#define HC_LONG_CASE(vv)                                                                              \
+  if (LV == vv)                                                                                       \
+    long_items_kernel<vv><<<ib, 256, smem, st>>>(a->feat, nvec, t_ptr, t_dst, t_w, grad_out, w,       \
+                                                 grad_input, a->num_node, a->hmap, a->src_map);
+    HC_LONG_CASE(1) HC_LONG_CASE(2) HC_LONG_CASE(4) HC_LONG_CASE(8)
+#undef HC_LONG_CASE
+    const unsigned rb = (unsigned)(w.max_split < 148 * 4 ? w.max_split : 148 * 4);
     long_reduce_kernel<<<rb, 256, 0, st>>>(a->feat, t_ptr, w, grad_input);
   }
   HC_LAUNCH_OK();

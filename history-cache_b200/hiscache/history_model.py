@@ -41,6 +41,39 @@ class MaskedBatchNorm1d(torch.nn.BatchNorm1d):
         return y
 
 
+class FusedNormAct(MaskedBatchNorm1d):
+    """BatchNorm1d + ReLU + dropout of one hidden layer.  Same parameters and buffers as
+    BatchNorm1d (state dicts are interchangeable).  `act(x, mask, p)` computes
+    dropout(relu(batch_norm(x))): while training on CUDA fp32 activations it is the library's
+    fused operator (two kernels forward, two backward: csrc/norm_act.cu); otherwise the three
+    torch calls of the reference (hiscache/history_model.py:141-143)."""
+
+    _next_seed = [0x5EED]
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        # dropout step counter of this layer (not part of the state dict)
+        self.register_buffer("_norm_state", torch.zeros(4, dtype=torch.int64), persistent=False)
+        FusedNormAct._next_seed[0] += 1
+        rank = 0
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            rank = torch.distributed.get_rank()      # replicas drop different elements
+        self.drop_seed = (FusedNormAct._next_seed[0] * 0x9E3779B1 + rank * 0x85EBCA77) & 0xFFFFFFFFFFFF
+        self.fused = True
+
+    def act(self, x, mask=None, p=0.0):
+        if (self.fused and self.training and self.track_running_stats and self.momentum is not None
+                and hb.norm_act_supported(x)):
+            with torch.no_grad():
+                self.num_batches_tracked.add_(1)
+            return hb.norm_act(x, self.weight, self.bias, self._norm_state, valid=mask,
+                               running_mean=self.running_mean, running_var=self.running_var,
+                               momentum=self.momentum, eps=self.eps, p=p, relu=True, seed=self.drop_seed)
+        x = self.forward(x, mask)
+        x = F.relu(x)
+        return F.dropout(x, p=p, training=self.training)
+
+
 class MySageConvHistory(torch.nn.Module):
     """lin_l(aggregate(x)) + lin_r(x[:num_node]) (hiscache/history_model.py:54-100)."""
 
@@ -98,7 +131,7 @@ class HistorySAGE(torch.nn.Module):
         self.bns = torch.nn.ModuleList()
         self.num_layers = num_layers
         for _ in range(self.num_layers - 1):
-            self.bns.append(MaskedBatchNorm1d(hidden_channels))
+            self.bns.append(FusedNormAct(hidden_channels))
         self.dropout = dropout
         self.table = table
         self.init_convs(**kwargs)
@@ -129,13 +162,12 @@ class HistorySAGE(torch.nn.Module):
                 t.history_out.append(his)
             else:
                 x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
-            x = self.bns[i](x)
-            x = F.relu(x)
-            x = F.dropout(x, p=self.dropout, training=self.training)
+            x = self.bns[i].act(x, None, self.dropout)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))
         return x.log_softmax(dim=-1)
 
     def forward(self, batch):
+        hb.declare_batch(batch.ptr, batch.idx, batch.x.shape[0])   # one transposition serves every layer
         if hasattr(self.table, "history_buffer_layered"):
             return self._forward_layered_tables(batch)
         x = batch.x
@@ -150,9 +182,7 @@ class HistorySAGE(torch.nn.Module):
             else:
                 x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
             mask = getattr(batch, "mask", None)   # fixed-shape batches carry a row mask
-            x = self.bns[i](x, None if mask is None else mask[:n])
-            x = F.relu(x)
-            x = F.dropout(x, p=self.dropout, training=self.training)
+            x = self.bns[i].act(x, None if mask is None else mask[:n], self.dropout)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))
         return x.log_softmax(dim=-1)
 
@@ -237,7 +267,7 @@ class HistoryRGCN(torch.nn.Module):
         self.in_channels, self.hidden_channels, self.out_channels = in_channels, hidden_channels, out_channels
         self.graph_type = graph_type
         self.num_layers = num_layers
-        self.bns = torch.nn.ModuleList(torch.nn.BatchNorm1d(hidden_channels) for _ in range(num_layers - 1))
+        self.bns = torch.nn.ModuleList(FusedNormAct(hidden_channels) for _ in range(num_layers - 1))
         self.dropout = dropout
         self.table = table
         self.num_rel = kwargs["num_rel"]
@@ -245,6 +275,7 @@ class HistoryRGCN(torch.nn.Module):
         self.init_convs(num_rel=self.num_rel)
 
     def forward(self, batch):
+        hb.declare_batch(batch.ptr, batch.idx, batch.x.shape[0])
         x = batch.x
         nn, ne = batch.num_node_in_layer, batch.num_edge_in_layer
         L = self.num_layers
@@ -268,9 +299,7 @@ class HistoryRGCN(torch.nn.Module):
                 self.table.produced_embedding.retain_grad()
             else:
                 x, his = conv(x, batch.ptr, batch.idx, et, None, None, None, used, 0, n)
-            x = self.bns[i](x)
-            x = F.relu(x)
-            x = F.dropout(x, p=self.dropout, training=self.training)
+            x = self.bns[i].act(x, None, self.dropout)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, etypes[:int(ne[0])], None, None, None,
                                 um[-2] if um is not None else None, 0, int(nn[0]))
         return x.log_softmax(dim=-1)

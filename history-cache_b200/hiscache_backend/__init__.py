@@ -207,9 +207,14 @@ class _AggrFunction(torch.autograd.Function):
                       and inp.shape[1] <= 1024)
         if can_gather and (DETERMINISTIC_BWD or (inp.shape[1] >= GATHER_MIN_FEAT and
                                                  idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES)):
-            t_ptr, t_dst, t_w, n_edges = shared_transpose(ptr_t, idx_t)
-            run_aggr_bwd_gather(PreparedAggr(a, None, dev, _tag("", inp)), t_ptr, t_dst, t_w, grad_out, g_in,
-                                n_edges=n_edges)
+            pa = PreparedAggr(a, None, dev, _tag("", inp))
+            shared = shared_transpose(ptr_t, idx_t)
+            if shared is not None and shared[0].shape[0] - 1 >= inp.shape[0]:
+                t_ptr, t_dst, t_w, n_edges = shared
+            else:       # a block nobody declared: its own transposition
+                n_edges = idx_t.numel()
+                t_ptr, t_dst, t_w = transpose_block(pa, n_edges)
+            run_aggr_bwd_gather(pa, t_ptr, t_dst, t_w, grad_out, g_in, n_edges=n_edges)
             gathered = True
         g_h = None
         if need_h:
@@ -330,25 +335,37 @@ def transpose_block(p: PreparedAggr, max_edges):
 
 
 _shared_t = {}
+_declared = {}
+
+
+def _graph_key(ptr_t, idx_t):
+    return (ptr_t.data_ptr(), idx_t.data_ptr(), ptr_t.shape[0], idx_t.shape[0], ptr_t._version, idx_t._version)
+
+
+def declare_batch(ptr_t, idx_t, n_nodes):
+    """Tells the library that (ptr, idx) is the CSR of one sampled batch over `n_nodes` local ids
+    that all layers aggregate over (layer k uses the rows [0, num_node_k)).  The backward passes
+    of the batch can then share ONE transposition (see shared_transpose)."""
+    _declared[ptr_t.device] = (_graph_key(ptr_t, idx_t), int(n_nodes))
 
 
 def shared_transpose(ptr_t, idx_t):
-    """Transposition of a batch's whole CSR, built once and reused by the backward pass of every
-    layer: all layers of a sampled batch aggregate over a prefix of the same (ptr, idx), and a
-    source's list is sorted by destination row, so the list of a smaller layer is a prefix of it
-    (hc_aggr_bwd_gather skips the rest).  Keyed by the two tensors' storage; one entry per device."""
+    """Transposition of a declared batch's whole CSR, built once and reused by the backward pass of
+    every layer: all layers aggregate over a prefix of the same (ptr, idx), and a source's list is
+    sorted by destination row, so the list of a smaller layer is a prefix of it
+    (hc_aggr_bwd_gather skips the rest).  None when (ptr, idx) was not declared."""
     dev = ptr_t.device
-    key = (ptr_t.data_ptr(), idx_t.data_ptr(), ptr_t.shape[0], idx_t.shape[0], ptr_t._version, idx_t._version)
+    key = _graph_key(ptr_t, idx_t)
+    decl = _declared.get(dev)
+    if decl is None or decl[0] != key:
+        return None
     hit = _shared_t.get(dev)
     if hit is not None and hit[0] == key:
         return hit[1]
-    n_rows = ptr_t.shape[0] - 1
     a = AggrArgs()
     a.struct_size = C.sizeof(AggrArgs)
-    a.ptr, a.idx, a.num_node = ptr(ptr_t), ptr(idx_t), n_rows
-    a.feat, a.num_head = 4, 1
-    # any node of the batch may be a source: local ids are below the number of edges + rows
-    a.n_src = int(idx_t.shape[0]) + n_rows + 1
+    a.ptr, a.idx, a.num_node = ptr(ptr_t), ptr(idx_t), ptr_t.shape[0] - 1
+    a.feat, a.num_head, a.n_src = 4, 1, decl[1]
     res = transpose_block(PreparedAggr(a, None, dev, ""), idx_t.shape[0]) + (int(idx_t.shape[0]),)
     _shared_t[dev] = (key, res, (ptr_t, idx_t))   # the tensors stay alive with the entry
     return res
@@ -357,11 +374,12 @@ def shared_transpose(ptr_t, idx_t):
 def run_aggr_bwd_gather(p: PreparedAggr, t_ptr, t_dst, t_w, grad_out, grad_input, n_edges=None):
     n_edges = int(t_dst.shape[0] if n_edges is None else n_edges)
     feat = int(p.args.feat)
-    sc = scratch(p.dev, lib.hc_gather_scratch_bytes(n_edges, feat), "gather") if n_edges > 1024 else None
+    sc = scratch(p.dev, lib.hc_gather_scratch_bytes(n_edges, feat), "gather") if n_edges > 64 else None
     with torch.cuda.device(p.dev), _span("hc_aggr_bwd_gather" + p.tag, p.dev):
-        check(lib.hc_aggr_bwd_gather(C.byref(p.args), ptr(t_ptr), ptr(t_dst), ptr(t_w), n_edges, ptr(grad_out),
-                                     ptr(grad_input), ptr(sc), stream_of(p.dev)), "hc_aggr_bwd_gather")
-    _called(4 if n_edges > 1024 else 1)
+        check(lib.hc_aggr_bwd_gather(C.byref(p.args), ptr(t_ptr), ptr(t_dst), ptr(t_w), t_ptr.shape[0] - 1,
+                                     n_edges, ptr(grad_out), ptr(grad_input), ptr(sc), stream_of(p.dev)),
+              "hc_aggr_bwd_gather")
+    _called(4 if n_edges > 64 else 1)
 
 
 def aggr_forward_history(input, ptr, idx, history_map, history_buffer, history_size, num_node):
@@ -395,6 +413,79 @@ def aggr_forward_history_edge_value(input, ptr, idx, edge_value, history_map, hi
 # ---------------------------------------------------------------------------
 # scores, threshold, admission, eviction
 # ---------------------------------------------------------------------------
+# ---------------------------------------------------------------------------
+# batch norm + ReLU + dropout in one forward pair / one backward pair
+# ---------------------------------------------------------------------------
+def _norm_args(x, valid, weight, bias, rmean, rvar, momentum, eps, p, relu, seed, state, save):
+    a = _capi.NormArgs()
+    a.struct_size = C.sizeof(_capi.NormArgs)
+    a.x, a.n, a.feat, a.x_stride = ptr(x), x.shape[0], x.shape[1], x.stride(0) if x.shape[0] > 1 else x.shape[1]
+    a.valid, a.weight, a.bias = ptr(valid), ptr(weight), ptr(bias)
+    a.running_mean, a.running_var = ptr(rmean), ptr(rvar)
+    a.momentum, a.eps, a.drop_p, a.relu, a.seed = float(momentum), float(eps), float(p), 1 if relu else 0, int(seed)
+    a.state = ptr(state)
+    a.save_mean, a.save_rstd, a.save_count = ptr(save[0]), ptr(save[1]), ptr(save[2])
+    return a
+
+
+class _NormActFunction(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, valid, rmean, rvar, momentum, eps, p, relu, seed, state):
+        dev = require_cuda(x, weight, bias, valid, rmean, rvar, state)
+        x = rows2d(x)
+        if x.dtype != torch.float32 or x.dim() != 2:
+            raise TypeError("norm_act: x must be a float32 matrix")
+        if valid is not None:
+            valid = valid.contiguous()
+            if valid.dtype == torch.bool:
+                valid = valid.view(torch.uint8)
+            if valid.shape[0] < x.shape[0]:
+                raise RuntimeError("norm_act: row mask shorter than x")
+        feat = x.shape[1]
+        save = (torch.empty(feat, dtype=torch.float32, device=dev), torch.empty(feat, dtype=torch.float32, device=dev),
+                torch.empty(1, dtype=torch.float32, device=dev))
+        y = torch.empty((x.shape[0], feat), dtype=torch.float32, device=dev)
+        a = _norm_args(x, valid, weight, bias, rmean, rvar, momentum, eps, p, relu, seed, state, save)
+        sc = scratch(dev, lib.hc_norm_scratch_bytes(feat), "norm")
+        with on_device(dev), _span("hc_norm_act_fwd", dev):
+            check(lib.hc_norm_act_fwd(C.byref(a), ptr(y), ptr(sc), stream_of(dev)), "hc_norm_act_fwd")
+        _called(2)
+        ctx.save_for_backward(x, weight, bias, valid, state, *save)
+        ctx.cfg = (momentum, eps, p, relu, seed)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        x, weight, bias, valid, state, sm, sr, scnt = ctx.saved_tensors
+        momentum, eps, p, relu, seed = ctx.cfg
+        dev = x.device
+        grad_y = grad_y.contiguous()
+        gx = torch.empty_like(x, memory_format=torch.contiguous_format)
+        gw = torch.empty_like(weight) if weight is not None and ctx.needs_input_grad[1] else None
+        gb = torch.empty_like(bias) if bias is not None and ctx.needs_input_grad[2] else None
+        a = _norm_args(x, valid, weight, bias, None, None, momentum, eps, p, relu, seed, state, (sm, sr, scnt))
+        sc = scratch(dev, lib.hc_norm_scratch_bytes(x.shape[1]), "norm")
+        with on_device(dev), _span("hc_norm_act_bwd", dev):
+            check(lib.hc_norm_act_bwd(C.byref(a), ptr(grad_y), ptr(gx), ptr(gw), ptr(gb), ptr(sc), stream_of(dev)),
+                  "hc_norm_act_bwd")
+        _called(2)
+        return gx, gw, gb, None, None, None, None, None, None, None, None, None
+
+
+def norm_act(x, weight, bias, state, *, valid=None, running_mean=None, running_var=None, momentum=0.1,
+             eps=1e-5, p=0.0, relu=True, seed=0):
+    """y = dropout(relu(batch_norm(x))) with batch statistics (training mode), as two kernels
+    forward and two backward (csrc/norm_act.cu).  `state`: int64[4] CUDA tensor, zero-initialised
+    once and private to the calling layer (dropout step counter).  `valid`: optional row mask."""
+    return _NormActFunction.apply(x, weight, bias, valid, running_mean, running_var, float(momentum),
+                                  float(eps), float(p), bool(relu), int(seed), state)
+
+
+def norm_act_supported(x) -> bool:
+    return x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[1] % 4 == 0 and x.shape[1] <= 1024
+
+
 def score_rows(x, kind=HC_SCORE_L2, out=None):
     """Per-row L2 / L1 norm in the library's fixed reduction order."""
     dev = require_cuda(x)

@@ -51,6 +51,17 @@ class Shard(C.Structure):
     ]
 
 
+class NormArgs(C.Structure):
+    """struct hc_norm_args"""
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("x", vp), ("n", i64), ("feat", i32), ("x_stride", i64), ("valid", vp),
+        ("weight", vp), ("bias", vp), ("running_mean", vp), ("running_var", vp),
+        ("momentum", f32), ("eps", f32), ("drop_p", f32), ("relu", i32), ("seed", C.c_uint64),
+        ("state", vp), ("save_mean", vp), ("save_rstd", vp), ("save_count", vp),
+    ]
+
+
 _SIGS = {
     "hc_abi_version": (C.c_int, []),
     "hc_error_string": (C.c_char_p, [C.c_int]),
@@ -59,7 +70,7 @@ _SIGS = {
     "hc_transpose_scratch_bytes": (i64, [i64, i64]),
     "hc_transpose_block": (C.c_int, [C.POINTER(AggrArgs), i64, vp, vp, vp, vp, vp]),
     "hc_gather_scratch_bytes": (i64, [i64, i32]),
-    "hc_aggr_bwd_gather": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, i64, vp, vp, vp, vp]),
+    "hc_aggr_bwd_gather": (C.c_int, [C.POINTER(AggrArgs), vp, vp, vp, i64, i64, vp, vp, vp, vp]),
     "hc_score_rows": (C.c_int, [vp, i64, i32, i64, i32, vp, vp]),
     "hc_select_scratch_bytes": (i64, [i64]),
     "hc_select_threshold": (C.c_int, [vp, i64, f32, vp, vp, vp]),
@@ -83,6 +94,9 @@ _SIGS = {
     "hc_gather_rows": (C.c_int, [vp, i32, i64, i64, i32, vp, i64, i32, vp, i32, i64, vp]),
     "hc_load_rows": (C.c_int, [vp, i32, i64, i64, vp, i32, i64, i64, i32, vp, vp, vp, i64, vp,
                                i32, i64, vp, vp, vp]),
+    "hc_norm_scratch_bytes": (i64, [i32]),
+    "hc_norm_act_fwd": (C.c_int, [C.POINTER(NormArgs), vp, vp, vp]),
+    "hc_norm_act_bwd": (C.c_int, [C.POINTER(NormArgs), vp, vp, vp, vp, vp, vp]),
     "hc_mix64": (C.c_uint64, [C.c_uint64]),
     "hc_bucket_scratch_bytes": (i64, [i64, i32]),
     "hc_bucket_by_owner": (C.c_int, [vp, vp, i64, i32, vp, vp, vp, vp, vp]),

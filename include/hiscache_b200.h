@@ -153,18 +153,20 @@ int hc_aggr_bwd(const hc_aggr_args* a, const float* grad_out, float* grad_input,
  *     from a transposition of a LARGER block that has this one as a prefix
  *     (the layers of a sampled batch share one CSR): entries with
  *     r >= num_node or hmap[r] != -1 are skipped, as are sources with
- *     src_map[s] != -1.  Lists longer than 1024 entries are split over many
- *     thread blocks and their chunk sums added in chunk order.
- *     feat must be a multiple of 4 and <= 1024; n_edges as given to the
- *     transposition; scratch >= hc_gather_scratch_bytes(n_edges, feat),
- *     16-byte aligned (may be NULL when n_edges <= 1024).
+ *     src_map[s] != -1.  Lists longer than 64 entries take a thread block
+ *     each; lists longer than 2048 are split into chunks over several blocks
+ *     and their chunk sums added in chunk order.
+ *     feat must be a multiple of 4 and <= 1024; t_n_src / n_edges: the n_src
+ *     and n_edges the transposition was built with (a->n_src <= t_n_src, else
+ *     HC_ERR_SIZE); scratch >= hc_gather_scratch_bytes(n_edges, feat),
+ *     16-byte aligned (may be NULL when n_edges <= 64).
  */
 int64_t hc_transpose_scratch_bytes(int64_t n_src, int64_t n_edges);
 int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_t* t_ptr, int64_t* t_dst,
                        float* t_w, void* scratch, void* stream);
 int64_t hc_gather_scratch_bytes(int64_t n_edges, int32_t feat);
 int hc_aggr_bwd_gather(const hc_aggr_args* a, const int64_t* t_ptr, const int64_t* t_dst,
-                       const float* t_w, int64_t n_edges, const float* grad_out,
+                       const float* t_w, int64_t t_n_src, int64_t n_edges, const float* grad_out,
                        float* grad_input, void* scratch, void* stream);
 
 /* ------------------------------------------------------------------------ */
@@ -610,6 +612,56 @@ int hc_relabel_reset(const int64_t* nodes, int64_t n, int32_t* local_map, void* 
 int64_t hc_relabel_scratch_bytes(int64_t m);
 int hc_relabel(const int64_t* nbr, int64_t m, int32_t* local_map, int64_t n_total,
                int64_t* new_nodes, int64_t* n_new, int64_t* out_idx, void* scratch, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Dense epilogue of a layer: batch norm (training statistics) + ReLU + dropout.
+ *
+ * Replaces, for the training step, the three torch modules the reference's
+ * models apply after every hidden conv (hiscache/history_model.py:141-143 for
+ * SAGE, :383-385 for RGCN): y = dropout(relu(batch_norm(x))).  Forward and
+ * backward are two kernels each, with no stored masks: ReLU's mask is
+ * recomputed from x, dropout's from (seed, step counter, element).
+ *   x [n, feat] fp32 (row stride x_stride, 0 = feat); valid: optional uint8 [n],
+ *   rows with 0 stay out of the statistics and give zeros (padding rows of
+ *   fixed-shape batches).  weight / bias [feat] or NULL (1 / 0).
+ *   running_mean / running_var: updated as torch.nn.BatchNorm1d does
+ *   (momentum, unbiased variance) or both NULL.
+ *   state: device int64[4], zeroed ONCE by the caller and private to one layer:
+ *     [0] dropout step counter (advanced by every forward with drop_p > 0),
+ *     [1] the step the last forward used (read by its backward), [2] internal.
+ *   save_mean / save_rstd [feat], save_count [1]: written by the forward, read
+ *   by the backward of the same call.
+ *   Column statistics are reproducible (fixed-order reduction in double).
+ *   feat % 4 == 0, feat <= 1024; x, y, grads 16-byte aligned.
+ *   scratch >= hc_norm_scratch_bytes(feat), 16-byte aligned; the same scratch
+ *   may serve every layer (calls on one stream).
+ * hc_norm_act_bwd: grad_x [n, feat]; grad_weight / grad_bias [feat] or NULL.
+ */
+typedef struct hc_norm_args {
+  uint32_t struct_size;    /* = sizeof(hc_norm_args) */
+  const float* x;
+  int64_t n;
+  int32_t feat;
+  int64_t x_stride;
+  const uint8_t* valid;
+  const float* weight;
+  const float* bias;
+  float* running_mean;
+  float* running_var;
+  float momentum;
+  float eps;
+  float drop_p;            /* 0 <= p < 1; 0 = no dropout */
+  int32_t relu;            /* 0 = identity instead of ReLU */
+  uint64_t seed;
+  int64_t* state;
+  float* save_mean;
+  float* save_rstd;
+  float* save_count;
+} hc_norm_args;
+int64_t hc_norm_scratch_bytes(int32_t feat);
+int hc_norm_act_fwd(const hc_norm_args* a, float* y, void* scratch, void* stream);
+int hc_norm_act_bwd(const hc_norm_args* a, const float* grad_y, float* grad_x, float* grad_weight,
+                    float* grad_bias, void* scratch, void* stream);
 
 #ifdef __cplusplus
 }

@@ -70,18 +70,19 @@ def layered_batch(rng, n_seed, fanouts, total_nodes, dedup=True):
 WORST = {}   # label -> largest observed |error| / allowed, printed at the end of the session
 
 
-def close(got, want, rtol, bound=None, terms=64, label="aggr"):
+def close(got, want, rtol, bound=None, terms=64, label="aggr", floor=0.0):
     """|got - want| <= rtol * |want| + (terms + 2) * 2^-23 * bound, element by element.
 
     `want` comes from the oracle, which accumulates in fp64.  The library adds `terms` fp32 numbers
     whose absolute values sum to `bound` (the oracle run on |inputs|), so its rounding error is at
     most about terms * 2^-24 * bound: that is the whole absolute allowance, there is no free
     constant.  Where a sum cancels, |want| is small but `bound` is not, which is what keeps the
-    test meaningful there.  With bound=None the allowance is relative only."""
+    test meaningful there.  With bound=None the allowance is relative only.  `floor` is an
+    absolute allowance for results stored in fp16, whose subnormal spacing is 2^-24."""
     got = got.detach().double().cpu().numpy()
     want = np.asarray(want, dtype=np.float64)
     assert got.shape == want.shape
-    allowed = rtol * np.abs(want)
+    allowed = rtol * np.abs(want) + floor
     if bound is not None:
         allowed = allowed + (terms + 2) * 2.0 ** -23 * np.asarray(bound, dtype=np.float64)
     err = np.abs(got - want)

@@ -87,13 +87,15 @@ def test_header_is_plain_c_and_struct_sizes_agree(tmp_path):
     import hiscache_backend._capi as capi
     src = tmp_path / "sz.c"
     src.write_text('#include <stdio.h>\n#include "hiscache_b200.h"\n'
-                   'int main(void){printf("%zu %zu\\n", sizeof(hc_aggr_args), sizeof(hc_shard));return 0;}\n')
+                   'int main(void){printf("%zu %zu\\n", sizeof(hc_aggr_args), sizeof(hc_shard));'
+                   'printf("%zu\\n", sizeof(hc_norm_args));return 0;}\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-I", os.path.dirname(HEADER), str(src), "-o", str(exe)],
                    check=True)
-    a, s = map(int, subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split())
+    a, s, nm = map(int, subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split())
     assert a == ctypes.sizeof(capi.AggrArgs)
     assert s == ctypes.sizeof(capi.Shard)
+    assert nm == ctypes.sizeof(capi.NormArgs)
 
 
 def test_peer_entry_points_check_arguments_without_gpu():
