@@ -37,81 +37,227 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
   return __uint_as_float(b);
 }
 
-// k-th smallest key (0-based); whole block must call. hist: shared uint32[256].
-__device__ uint32_t block_radix_select(const float* __restrict__ score, int64_t n, int64_t k,
-                                       uint32_t* hist, uint32_t* bcast) {
+// rank = q * (n - 1) in fp32 and the two order statistics around it (torch.quantile)
+struct Ranks {
+  int64_t n, k_lo, k_hi;
+  float w;
+};
+__device__ __forceinline__ Ranks quantile_ranks(int64_t n_all, const int64_t* n_dev, float q) {
+  // with n_dev the quantile is taken over the *n_dev smallest of the n_all scores: the caller
+  // sets the scores of padding rows to +inf, which sorts them last
+  Ranks r;
+  r.n = n_all;
+  if (n_dev) {
+    r.n = n_dev[0];
+    if (r.n > n_all) r.n = n_all;
+  }
+  if (r.n < 1) {
+    r.k_lo = r.k_hi = 0;
+    r.w = 0.f;
+    return r;
+  }
+  const float pos = __fmul_rn(q, (float)(r.n - 1));
+  r.k_lo = (int64_t)pos;  // truncation, pos >= 0
+  if (r.k_lo > r.n - 1) r.k_lo = r.n - 1;
+  if (r.k_lo < 0) r.k_lo = 0;
+  r.k_hi = (int64_t)ceilf(pos);
+  if (r.k_hi > r.n - 1) r.k_hi = r.n - 1;
+  if (r.k_hi < 0) r.k_hi = 0;
+  r.w = __fsub_rn(pos, (float)r.k_lo);
+  return r;
+}
+__device__ __forceinline__ float quantile_lerp(uint32_t key_lo, uint32_t key_hi, float w) {
+  const float lo = key_to_float(key_lo), hi = key_to_float(key_hi);
+  const float diff = __fsub_rn(hi, lo);
+  // torch's lerp with its fused multiply-add (CPU AVX2+ and CUDA builds)
+  return fabsf(w) < 0.5f ? __fmaf_rn(w, diff, lo) : __fmaf_rn(-diff, __fsub_rn(1.f, w), hi);
+}
+
+// ---- up to kSelSmall scores: one block, keys staged once in shared memory ----------------
+// One global read, then four 8-bit radix passes over shared memory find the k_lo-th key; the
+// k_hi-th (k_lo or k_lo + 1) is the same key when enough copies exist, else the smallest larger
+// key: one more pass.
+constexpr int kSelSmall = 48 * 1024;
+constexpr int kSelThreads = 1024;
+
+__global__ void __launch_bounds__(kSelThreads)
+    select_small_kernel(const float* __restrict__ score, int64_t n_all, const int64_t* n_dev, float q,
+                        float* __restrict__ thres) {
+  extern __shared__ uint32_t keys[];   // [n_all]
+  __shared__ uint32_t hist[256];
+  __shared__ uint32_t bcast[3];
+  const Ranks rk = quantile_ranks(n_all, n_dev, q);
+  if (rk.n < 1) {
+    if (threadIdx.x == 0) thres[0] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const int n = (int)n_all;
+  int has_nan = 0;
+  for (int i = threadIdx.x; i < n; i += kSelThreads) {
+    const float v = score[i];
+    has_nan |= (v != v);
+    keys[i] = order_key(v);
+  }
+  has_nan = __syncthreads_or(has_nan);
   uint32_t prefix = 0, mask = 0;
+  uint32_t k = (uint32_t)rk.k_lo, below = 0;   // below: keys smaller than the current prefix range
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+    for (int i = threadIdx.x; i < 256; i += kSelThreads) hist[i] = 0;
     __syncthreads();
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
-      const uint32_t key = order_key(score[i]);
+    for (int i = threadIdx.x; i < n; i += kSelThreads) {
+      const uint32_t key = keys[i];
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int64_t rem = k;
-      uint32_t d = 0;
-      for (; d < 255; ++d) {
-        if (rem < (int64_t)hist[d]) break;
-        rem -= hist[d];
+    if (threadIdx.x < 32) {   // one warp scans the 256 bins (8 per lane)
+      uint32_t c[8], tot = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { c[j] = hist[threadIdx.x * 8 + j]; tot += c[j]; }
+      uint32_t inc = tot;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(kFull, inc, off);
+        if ((int)threadIdx.x >= off) inc += t;
       }
-      bcast[0] = d;
-      bcast[1] = (uint32_t)rem;  // rem < hist[d] <= 2^32
-      bcast[2] = (uint32_t)(rem >> 32);
+      uint32_t run = inc - tot;   // keys in bins of lower lanes
+      if (k >= run && k < inc) {  // the wanted key is in one of this lane's bins
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (k < run + c[j]) {
+            bcast[0] = threadIdx.x * 8 + j;
+            bcast[1] = k - run;
+            bcast[2] = run;
+            break;
+          }
+          run += c[j];
+        }
+      }
     }
     __syncthreads();
-    const uint32_t d = bcast[0];
-    k = (int64_t)bcast[1] | ((int64_t)bcast[2] << 32);
-    prefix |= d << shift;
+    prefix |= bcast[0] << shift;
     mask |= 255u << shift;
+    k = bcast[1];
+    below += bcast[2];
     __syncthreads();
   }
-  return prefix;
+  const uint32_t key_lo = prefix;
+  // copies of key_lo occupy ranks [below, below + copies); key_hi is key_lo if k_hi falls inside
+  uint32_t key_hi = key_lo;
+  if (rk.k_hi != rk.k_lo) {
+    uint32_t copies = 0, next = 0xFFFFFFFFu;
+    for (int i = threadIdx.x; i < n; i += kSelThreads) {
+      const uint32_t key = keys[i];
+      copies += (key == key_lo);
+      if (key > key_lo && key < next) next = key;
+    }
+    if (threadIdx.x == 0) { hist[0] = 0; hist[1] = 0xFFFFFFFFu; }
+    __syncthreads();
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      copies += __shfl_xor_sync(kFull, copies, off);
+      const uint32_t o = __shfl_xor_sync(kFull, next, off);
+      next = o < next ? o : next;
+    }
+    if ((threadIdx.x & 31) == 0) {
+      atomicAdd(&hist[0], copies);
+      atomicMin(&hist[1], next);
+    }
+    __syncthreads();
+    if ((uint32_t)rk.k_hi >= below + hist[0]) key_hi = hist[1];
+  }
+  if (threadIdx.x == 0)
+    thres[0] = has_nan ? __int_as_float(0x7fc00000) : quantile_lerp(key_lo, key_hi, rk.w);
 }
 
-__global__ void __launch_bounds__(1024)
-    select_threshold_kernel(const float* __restrict__ score, int64_t n_all, const int64_t* n_dev, float q,
-                            float* __restrict__ thres) {
-  __shared__ uint32_t hist[256];
-  __shared__ uint32_t bcast[4];
-  // with n_dev the quantile is taken over the *n_dev smallest of the n_all scores: the caller
-  // sets the scores of padding rows to +inf, which sorts them last
-  int64_t n = n_all;
-  if (n_dev) {
-    n = n_dev[0];
-    if (n > n_all) n = n_all;
-    if (n < 1) {
-      if (threadIdx.x == 0) thres[0] = __int_as_float(0x7fc00000);
-      return;
+// ---- any size: histograms by many blocks, digit choice by one ----------------------------
+// Both order statistics descend together (two prefixes); four passes of
+//   sel_hist (grid over the scores) -> sel_pick (one block), state in caller scratch.
+struct SelState {
+  uint32_t prefix[2];
+  uint32_t mask;
+  int has_nan;
+  long long k[2];
+  uint32_t hist[2][256];
+};
+
+__global__ void __launch_bounds__(256) sel_init_kernel(SelState* st, int64_t n_all, const int64_t* n_dev, float q) {
+  const Ranks rk = quantile_ranks(n_all, n_dev, q);
+  if (threadIdx.x == 0) {
+    st->prefix[0] = st->prefix[1] = 0;
+    st->mask = 0;
+    st->has_nan = rk.n < 1 ? 1 : 0;   // no valid score: NaN
+    st->k[0] = rk.k_lo;
+    st->k[1] = rk.k_hi;
+  }
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) (&st->hist[0][0])[i] = 0;
+}
+
+__global__ void __launch_bounds__(256)
+    sel_hist_kernel(const float* __restrict__ score, int64_t n, int shift, SelState* st) {
+  __shared__ uint32_t h[2][256];
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) (&h[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t p0 = st->prefix[0], p1 = st->prefix[1], mask = st->mask;
+  int nan = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const float v = score[i];
+    nan |= (v != v);
+    const uint32_t key = order_key(v);
+    const uint32_t d = (key >> shift) & 255u;
+    if ((key & mask) == p0) atomicAdd(&h[0][d], 1u);
+    if ((key & mask) == p1) atomicAdd(&h[1][d], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+    const uint32_t c = (&h[0][0])[i];
+    if (c) atomicAdd(&(&st->hist[0][0])[i], c);
+  }
+  if (shift == 24 && __syncthreads_or(nan) && threadIdx.x == 0) atomicOr(&st->has_nan, 1);
+}
+
+__global__ void __launch_bounds__(64) sel_pick_kernel(SelState* st, int shift, float q, int64_t n_all,
+                                                      const int64_t* n_dev, float* __restrict__ thres) {
+  const int s = threadIdx.x >> 5, lane = threadIdx.x & 31;   // warp s handles order statistic s
+  uint32_t c[8];
+  unsigned long long tot = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { c[j] = st->hist[s][lane * 8 + j]; tot += c[j]; }
+  unsigned long long inc = tot;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const unsigned long long t = __shfl_up_sync(kFull, inc, off);
+    if (lane >= off) inc += t;
+  }
+  unsigned long long run = inc - tot;
+  const unsigned long long k = (unsigned long long)st->k[s];
+  uint32_t digit = 0xFFFFFFFFu;
+  long long rem = 0;
+  if (k >= run && k < inc) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (digit == 0xFFFFFFFFu && k < run + c[j]) { digit = lane * 8 + j; rem = (long long)(k - run); }
+      run += c[j];
     }
   }
-  // rank = q * (n - 1) in fp32; weights = rank - floor(rank)
-  const float pos = __fmul_rn(q, (float)(n - 1));
-  int64_t k_lo = (int64_t)pos;  // truncation, pos >= 0
-  if (k_lo > n - 1) k_lo = n - 1;
-  if (k_lo < 0) k_lo = 0;
-  int64_t k_hi = (int64_t)ceilf(pos);
-  if (k_hi > n - 1) k_hi = n - 1;
-  if (k_hi < 0) k_hi = 0;
-  const float w = __fsub_rn(pos, (float)k_lo);
-  // NaN anywhere makes the quantile NaN
-  int has_nan = 0;
-  for (int64_t i = threadIdx.x; i < n_all; i += blockDim.x) has_nan |= (score[i] != score[i]);
-  has_nan = __syncthreads_or(has_nan);
-  const uint32_t key_lo = block_radix_select(score, n_all, k_lo, hist, bcast);
-  const uint32_t key_hi = (k_hi == k_lo) ? key_lo : block_radix_select(score, n_all, k_hi, hist, bcast);
+  // exactly one lane found it (or none when there is no valid score)
+  const unsigned who = __ballot_sync(kFull, digit != 0xFFFFFFFFu);
+  const int src = who ? __ffs(who) - 1 : 0;
+  digit = __shfl_sync(kFull, digit, src);
+  rem = __shfl_sync(kFull, rem, src);
+  if (!who) { digit = 0; rem = 0; }
+  __syncthreads();    // all reads of hist are done
+  if (lane == 0) {
+    st->prefix[s] |= digit << shift;
+    st->k[s] = rem;
+  }
+  for (int i = lane; i < 256; i += 32) st->hist[s][i] = 0;
+  __syncthreads();
   if (threadIdx.x == 0) {
-    float r;
-    if (has_nan) {
-      r = __int_as_float(0x7fc00000);
-    } else {
-      const float lo = key_to_float(key_lo), hi = key_to_float(key_hi);
-      const float diff = __fsub_rn(hi, lo);
-      // torch's lerp with its fused multiply-add (CPU AVX2+ and CUDA builds)
-      r = fabsf(w) < 0.5f ? __fmaf_rn(w, diff, lo) : __fmaf_rn(-diff, __fsub_rn(1.f, w), hi);
+    st->mask |= 255u << shift;
+    if (shift == 0) {
+      const Ranks rk = quantile_ranks(n_all, n_dev, q);
+      thres[0] = st->has_nan ? __int_as_float(0x7fc00000) : quantile_lerp(st->prefix[0], st->prefix[1], rk.w);
     }
-    thres[0] = r;
   }
 }
 
@@ -420,31 +566,56 @@ extern "C" int hc_score_rows(const float* x, int64_t n, int32_t feat, int64_t st
 }
 
 extern "C" int64_t hc_select_scratch_bytes(int64_t n) {
-  (void)n;
-  return 256;
+  return n > kSelSmall ? (int64_t)sizeof(SelState) + 64 : 0;
+}
+
+static int select_launch(const float* score, int64_t n, const int64_t* n_valid, float q, float* thres,
+                         void* scratch, cudaStream_t st) {
+  if (n <= kSelSmall) {
+    const size_t smem = (size_t)n * sizeof(uint32_t);
+    if (smem > 40 * 1024) {
+      // raised once per device (not a stream operation, so keep it out of stream captures)
+      static bool raised[64] = {};
+      int devno = 0;
+      HC_CUDA(cudaGetDevice(&devno));
+      if (devno >= 0 && devno < 64 && !raised[devno]) {
+        HC_CUDA(cudaFuncSetAttribute(select_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     kSelSmall * (int)sizeof(uint32_t)));
+        raised[devno] = true;
+      }
+    }
+    select_small_kernel<<<1, kSelThreads, smem, st>>>(score, n, n_valid, q, thres);
+    HC_LAUNCH_OK();
+    return 0;
+  }
+  HC_REQUIRE(scratch != nullptr && aligned_to(scratch, 8), HC_ERR_NULL);
+  HC_REQUIRE(n < 0xffffffffLL, HC_ERR_SIZE);
+  SelState* state = reinterpret_cast<SelState*>(scratch);
+  int64_t blocks = ceil_div(n, 256 * 8);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sel_init_kernel<<<1, 256, 0, st>>>(state, n, n_valid, q);
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    sel_hist_kernel<<<(unsigned)blocks, 256, 0, st>>>(score, n, shift, state);
+    sel_pick_kernel<<<1, 64, 0, st>>>(state, shift, q, n, n_valid, thres);
+  }
+  HC_LAUNCH_OK();
+  return 0;
 }
 
 extern "C" int hc_select_threshold(const float* score, int64_t n, float q, float* thres,
                                    void* scratch, void* stream) {
-  (void)scratch;
   HC_REQUIRE(n > 0, HC_ERR_SIZE);
   HC_REQUIRE(score && thres, HC_ERR_NULL);
   HC_REQUIRE(q >= 0.f && q <= 1.f, HC_ERR_SIZE);
-  select_threshold_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(score, n, nullptr,
-                                                                                  q, thres);
-  HC_LAUNCH_OK();
-  return 0;
+  return select_launch(score, n, nullptr, q, thres, scratch, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int hc_select_threshold_counted(const float* score, int64_t n, const int64_t* n_valid,
-                                           float q, float* thres, void* stream) {
+                                           float q, float* thres, void* scratch, void* stream) {
   HC_REQUIRE(n > 0, HC_ERR_SIZE);
   HC_REQUIRE(score && thres && n_valid, HC_ERR_NULL);
   HC_REQUIRE(q >= 0.f && q <= 1.f, HC_ERR_SIZE);
-  select_threshold_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(score, n, n_valid,
-                                                                                  q, thres);
-  HC_LAUNCH_OK();
-  return 0;
+  return select_launch(score, n, n_valid, q, thres, scratch, reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int64_t hc_admit_scratch_bytes(int64_t n) {

@@ -16,7 +16,7 @@
 namespace hc {
 
 constexpr int kNormBlock = 256;
-constexpr int kNormMaxPartials = 296;   // blocks of the statistics kernels (2 per SM)
+constexpr int kNormMaxPartials = 148;   // blocks of the statistics kernels (one per SM)
 
 struct NormGeom {
   int nvec;   // float4 per row
@@ -38,6 +38,21 @@ __device__ __forceinline__ unsigned dropout_keep4(uint64_t seed, int64_t step, i
 #pragma unroll
   for (int q = 0; q < 4; ++q) m |= ((uint32_t)((h >> (16 * q)) & 0xFFFFu) >= thresh16 ? 1u : 0u) << q;
   return m;
+}
+
+// sum over blocks b of p[b * stride + c], in a fixed order, with eight loads in flight
+__device__ __forceinline__ double column_sum(const float* p, int64_t stride, unsigned nb, int c) {
+  double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  unsigned b = 0;
+  for (; b + 8 <= nb; b += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcg(p + (int64_t)(b + j) * stride + c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += (double)v[j];
+  }
+  for (int j = 0; b < nb; ++b, ++j) acc[j] += (double)__ldcg(p + (int64_t)b * stride + c);
+  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
 }
 
 struct NormArgs {
@@ -117,11 +132,8 @@ __global__ void __launch_bounds__(kNormBlock) norm_stats_kernel(const NormArgs a
   double n_valid = 0.0;
   for (unsigned b = 0; b < gridDim.x; ++b) n_valid += (double)__ldcg(a.partial_count + b);
   for (int c = threadIdx.x; c < a.feat; c += blockDim.x) {
-    double sum = 0.0, sq = 0.0;
-    for (unsigned b = 0; b < gridDim.x; ++b) {
-      sum += (double)__ldcg(a.partial + (int64_t)b * 2 * a.feat + c);
-      sq += (double)__ldcg(a.partial + (int64_t)b * 2 * a.feat + a.feat + c);
-    }
+    const double sum = column_sum(a.partial, 2 * a.feat, gridDim.x, c);
+    const double sq = column_sum(a.partial + a.feat, 2 * a.feat, gridDim.x, c);
     const double nn = n_valid > 0.0 ? n_valid : 1.0;
     const double mean = sum / nn;
     double var = sq / nn - mean * mean;
@@ -249,11 +261,8 @@ __global__ void __launch_bounds__(kNormBlock) norm_bwd_stats_kernel(const NormAr
   if (!is_last) return;
   __threadfence();
   for (int c = threadIdx.x; c < a.feat; c += blockDim.x) {
-    double sum = 0.0, sq = 0.0;
-    for (unsigned b = 0; b < gridDim.x; ++b) {
-      sum += (double)__ldcg(a.partial + (int64_t)b * 2 * a.feat + c);
-      sq += (double)__ldcg(a.partial + (int64_t)b * 2 * a.feat + a.feat + c);
-    }
+    const double sum = column_sum(a.partial, 2 * a.feat, gridDim.x, c);
+    const double sq = column_sum(a.partial + a.feat, 2 * a.feat, gridDim.x, c);
     bw.sum_dz[c] = (float)sum;
     bw.sum_dzx[c] = (float)sq;
     if (bw.grad_bias) bw.grad_bias[c] = (float)sum;

@@ -508,16 +508,21 @@ def select_threshold(score, q, out=None, n_valid=None):
     carry +inf)."""
     dev = require_cuda(score)
     score = score.contiguous()
+    if score.dtype != torch.float32:
+        raise TypeError("select_threshold: scores must be float32")
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=dev)
+    n = score.shape[0]
+    nbytes = int(lib.hc_select_scratch_bytes(n))
+    sc = scratch(dev, nbytes, "select") if nbytes else None
     with on_device(dev), _span("hc_select_threshold", dev):
         if n_valid is None:
-            check(lib.hc_select_threshold(ptr(score), score.shape[0], float(q), ptr(out), None,
+            check(lib.hc_select_threshold(ptr(score), n, float(q), ptr(out), ptr(sc),
                                           stream_of(dev)), "hc_select_threshold")
         else:
-            check(lib.hc_select_threshold_counted(ptr(score), score.shape[0], ptr(n_valid), float(q),
-                                                  ptr(out), stream_of(dev)), "hc_select_threshold_counted")
-    _called()
+            check(lib.hc_select_threshold_counted(ptr(score), n, ptr(n_valid), float(q),
+                                                  ptr(out), ptr(sc), stream_of(dev)), "hc_select_threshold_counted")
+    _called(9 if nbytes else 1)
     return out
 
 

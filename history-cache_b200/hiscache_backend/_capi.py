@@ -82,7 +82,7 @@ _SIGS = {
                                             vp, vp, vp, i64, vp, vp]),
     "hc_cache_admit": (C.c_int, [vp, i64, i64, vp, i32, i32, i32, i64, vp, vp, vp, vp, vp, i64,
                                  vp, vp, i64, vp, i32, vp, vp, vp, vp]),
-    "hc_select_threshold_counted": (C.c_int, [vp, i64, vp, f32, vp, vp]),
+    "hc_select_threshold_counted": (C.c_int, [vp, i64, vp, f32, vp, vp, vp]),
     "hc_evict_stale": (C.c_int, [vp, vp, vp, i64, i64, i64, vp]),
     "hc_evict_stale_dev": (C.c_int, [vp, vp, vp, i64, vp, i64, vp]),
     "hc_stamp_checkin": (C.c_int, [vp, i64, i64, vp, vp]),

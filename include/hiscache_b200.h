@@ -192,7 +192,11 @@ int hc_score_rows(const float* x, int64_t n, int32_t feat, int64_t stride,
  * radix select, combined as fma(w, hi-lo, lo) for w < 0.5 and
  * fma(-(hi-lo), 1-w, hi) otherwise (torch's lerp, whose multiply-add is fused
  * in its CPU and CUDA builds).  NaN in score gives NaN.
- * n == 0 is HC_ERR_SIZE.  scratch: device, >= hc_select_scratch_bytes(n).
+ * n == 0 is HC_ERR_SIZE.  Up to 49 152 scores are staged in shared memory by
+ * one thread block (one pass over global memory); more take four passes of a
+ * multi-block digit histogram with state in scratch: device, 8-byte aligned,
+ * >= hc_select_scratch_bytes(n) (0 bytes, and scratch may be NULL, for the
+ * small form).
  */
 int64_t hc_select_scratch_bytes(int64_t n);
 int hc_select_threshold(const float* score, int64_t n, float q, float* thres,
@@ -203,7 +207,7 @@ int hc_select_threshold(const float* score, int64_t n, float q, float* thres,
  * padding rows to +inf.  Nothing about the size has to be known on the host.
  */
 int hc_select_threshold_counted(const float* score, int64_t n, const int64_t* n_valid, float q,
-                                float* thres, void* stream);
+                                float* thres, void* scratch, void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Admission and eviction                                                   */

@@ -102,7 +102,7 @@ def bench_bwd_gather(n_dst, deg, n_src, feat, reps, dev="cuda:0"):
     return ms, byts, ms_t
 
 
-def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0"):
+def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0", sort_ids=False):
     """batch.x assembly.  bytes = rows read (F*s each) + rows written (F*s) + 8*n ids (+ 8*n map)."""
     es = 2 if dtype == torch.float16 else 4
     if host and thp:
@@ -127,6 +127,8 @@ def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0"):
         table = torch.randn((n_table, feat), device=dev).to(dtype)
     # fresh ids per launch: host rows read once are cached in L2 and would flatter the link
     pool = [torch.randint(0, n_table, (n,), device=dev) for _ in range(reps + 3)]
+    if sort_ids:     # requests issued in address order
+        pool = [torch.sort(p)[0] for p in pool]
     it = iter(pool * 2)
     ms = time_launches(lambda: hb.load_rows(table, None, next(it), None, None), reps)
     return ms, n * feat * es * 2 + 8 * n
@@ -144,6 +146,7 @@ def main():
     ap.add_argument("--host", action="store_true", help="load: table in pinned host memory")
     ap.add_argument("--thp", action="store_true", help="load --host: back the table with 2 MB huge pages")
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--sorted", action="store_true", help="load: row ids in ascending order")
     ap.add_argument("--skew", action="store_true",
                     help="neighbours drawn as floor(n_src * u^3) (hub sources) instead of uniformly")
     args = ap.parse_args()
@@ -174,7 +177,9 @@ def main():
                  "transpose_ms": round(ms_t, 4), "transpose_amortised_over_layers": layers,
                  "fwd_plus_scatter_GBps": round((b_f + b_s) / (ms_f + ms_s) / 1e6, 1)}
     else:
-        ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host, args.thp)
+        ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host, args.thp,
+                              sort_ids=args.sorted)
+        extra = {"sorted": args.sorted, "thp": args.thp}
     print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
                       "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate, "skew": args.skew,
                       "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1), **extra}))

@@ -23,7 +23,7 @@ def test_score_rows_bit_exact(backend, oracle, feat, kind):
     assert got.cpu().numpy().tobytes() == oracle.score_rows(x, kind).tobytes()
 
 
-@pytest.mark.parametrize("n", [1, 2, 3, 31, 1000, 1001, 16000, 200_003])
+@pytest.mark.parametrize("n", [1, 2, 3, 31, 1000, 1001, 16000, 49_152, 49_153, 200_003, 3_000_001])
 @pytest.mark.parametrize("q", [0.0, 0.1, 0.5, 0.9, 0.3333, 1.0])
 def test_threshold_bit_exact(backend, oracle, n, q):
     rng = np.random.default_rng(n)
@@ -35,6 +35,23 @@ def test_threshold_bit_exact(backend, oracle, n, q):
     # and the CPU implementation of torch.quantile, which the reference calls
     ref = torch.quantile(torch.from_numpy(s), q).numpy()
     assert np.float32(got).tobytes() == np.float32(ref).tobytes()
+
+
+@pytest.mark.parametrize("n,n_valid", [(500, 1), (500, 137), (5000, 4999), (60_000, 41_234), (60_000, 60_000)])
+def test_threshold_over_the_valid_prefix_of_a_padded_batch(backend, oracle, n, n_valid):
+    """Padding rows carry +inf; the quantile is over the n_valid smallest scores, with n_valid read
+    on the device (both the one-block and the multi-block form)."""
+    rng = np.random.default_rng(n + n_valid)
+    s = np.full(n, np.inf, dtype=np.float32)
+    pos = rng.choice(n, size=n_valid, replace=False)
+    s[pos] = rng.standard_normal(n_valid).astype(np.float32)
+    nv = torch.tensor([n_valid], dtype=torch.int64, device="cuda")
+    for q in (0.0, 0.5, 0.77, 1.0):
+        got = backend.select_threshold(cu(s), q, n_valid=nv).cpu().numpy()[0]
+        want = oracle.quantile(s[pos], q)
+        assert np.float32(got).tobytes() == np.float32(want).tobytes()
+    nv.zero_()
+    assert np.isnan(backend.select_threshold(cu(s), 0.5, n_valid=nv).cpu().numpy()[0])
 
 
 def test_threshold_special_values(backend, oracle):
