@@ -72,6 +72,11 @@ def parse():
     ap.add_argument("--exchange", default=os.environ.get("HC_EXCHANGE", "auto"), choices=["auto", "peer", "nccl"],
                     help="multi-GPU history exchange: peer memory (CUDA IPC + NVLink loads) or padded "
                          "all-to-alls; auto = peer memory when every rank can map every other")
+    ap.add_argument("--config", type=int, default=3, choices=[2, 3, 5],
+                    help="which configuration of BASELINE.json is the bench line: 3 = configs[2] (one GPU) / "
+                         "configs[3] (several), the default; 2 = configs[1]; 5 = configs[4] at reduced size")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="one GPU: do not append the short runs of configs[1] and configs[4]")
     ap.add_argument("--seed", type=int, default=0)
     return ap.parse_args()
 
@@ -560,6 +565,14 @@ def run_ours(args):
 
     if rank == 0 and world == 1 and not args.no_large_block:
         out["roofline_large_block"] = large_block_roofline(device, peak, bool(peaks))
+    if rank == 0 and world == 1 and not args.no_other_configs:
+        # the working set of the main configuration goes first: the other runs need the memory
+        del trainer, pipe, batches, host_batches, timed, timed_host
+        torch.cuda.empty_cache()
+        cs = 0 if args.no_cpu_baseline else None
+        out["other_configs"] = {
+            "configs[1]": bench_config2(device, **({} if cs is None else {"cpu_steps": 0})),
+            "configs[4]": bench_config5(device, **({} if cs is None else {"cpu_steps": 0}))}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         nat = loader.train_loader       # natural-shape batches of the same workload
         out["cpu_baseline"] = cpu_baseline(args, graph, uvm, [next(nat) for _ in range(args.cpu_steps + 1)],
@@ -584,6 +597,224 @@ def hidden_fwd_bytes(batch, hidden):
     for n_d, e in ((nn[1], ne[1]), (nn[0], ne[0])):
         tot += e * hidden * 4 + n_d * hidden * 4 + 8 * (n_d + 1 + e)
     return tot + 8 * nn[1]
+
+
+# ---------------------------------------------------------------------------
+# the other single-GPU configurations of BASELINE.json
+# ---------------------------------------------------------------------------
+MAG_REL_TABLE = [0, 1, 1,      # into a paper  from paper / author / institution
+                 2, 0, 3,      # into an author
+                 4, 4, 2]      # into an institution
+
+
+def _time_steps(step, batches, warmup):
+    for b in batches[:warmup]:
+        step(b)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for b in batches[warmup:]:
+        step(b)
+    e1.record()
+    issue = (time.perf_counter() - t0) * 1e3
+    torch.cuda.synchronize()
+    n = len(batches) - warmup
+    return e0.elapsed_time(e1) / n, issue / n
+
+
+def _e2e_steps(trainer, host_batches, warmup):
+    from hiscache.pipeline import HostBatchPipeline
+    pipe = HostBatchPipeline(trainer, host_batches)
+    pipe.run(host_batches[:warmup])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    pipe.run(host_batches[warmup:])
+    e1.record()
+    torch.cuda.synchronize()
+    n = len(host_batches) - warmup
+    return e0.elapsed_time(e1) / n, sum(b.nbytes() for b in host_batches[warmup:]) / n
+
+
+def _kernel_table(trainer, batches, n):
+    import hiscache_backend as hb
+    full = hb.KernelTimer()
+    hb.set_kernel_timer(full)
+    for b in batches[:n]:
+        trainer.train_step(b)
+    hb.set_kernel_timer(None)
+    return full.summary()
+
+
+def _peak():
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    return float(peaks.get("hbm_gbs", 6650.0)), ("measured" if peaks else "fallback")
+
+
+def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, seed=0):
+    """configs[1]: 3-layer SAGE (hidden 256, 47 classes) on a 2.4 M-node power-law graph (Zipf 2.0,
+    mean out-degree 26), fp32 dim-100 features in HBM, batch 1 000, fan-outs 15/10/5, per-layer
+    history tables with a staleness limit of 10 iterations (HistoryTableTrainer)."""
+    from hiscache import HistoryTableTrainer, HostFeatureStore, make_config
+    from hiscache.sampler import Loader, SyntheticGraph
+    feat, hidden, classes, fan = 100, 256, 47, [15, 10, 5]
+    graph = SyntheticGraph(nodes, 26.0, 2.0, classes, seed=seed, device=device, num_train=min(nodes, 200_000))
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    feats = torch.randn(nodes, feat, generator=g, device=device)
+    uvm = HostFeatureStore(feats, device)
+    cfg = make_config(feature_dim=feat, num_classes=classes, hidden_dim=hidden, num_layers=3, num_nodes=nodes,
+                      device=str(device), staleness_thres=10, batch_size=1000, rate=0.5, fanouts=fan,
+                      buffer_size=[400_000, 200_000], method="grad", feat_mode="memory")
+    loader = Loader(graph, fan, 1000, "memory", seed=seed, iters_per_epoch=1 << 30)
+    tr = HistoryTableTrainer(cfg, graph=graph, uvm=uvm, loader=loader, seed=seed)
+    tr.model.train()
+    it = loader.train_loader
+    batches = [next(it) for _ in range(warmup + steps)]
+    ms, issue = _time_steps(tr.train_step, batches, warmup)
+    hits = sum(int((m != -1).sum()) for m in tr.table.sub_to_history)
+    kt = _kernel_table(tr, batches[warmup:], min(steps, 20))
+    n_prof = min(steps, 20)
+    peak, src = _peak()
+    dom = f"hc_aggr_fwd[f32,F={feat}]"
+    roof = None
+    if dom in kt:
+        ms_l = kt[dom]["ms_total"] / kt[dom]["launches"]
+        byts = sum(conv0_bytes(b, feat, 4) for b in batches[warmup:warmup + n_prof]) / n_prof
+        roof = {"bound": "hbm", "kernel": "aggr_fwd_vec_kernel<float> (first conv, fp32 dim-100 rows)",
+                "achieved": round(byts / ms_l / 1e6, 1), "peak": peak, "peak_source": src, "unit": "GB/s",
+                "frac": round(byts / ms_l / 1e6 / peak, 4), "bytes_per_launch": int(byts),
+                "us_per_launch": round(ms_l * 1e3, 2), "traffic": None,
+                "note": "block far smaller than L2: latency bound; history hits counted as gathered"}
+    out = {"workload": "configs[1]: 3-layer SAGE, 2.4M-node power-law graph, fp32 dim-100 features in HBM, "
+                       "per-layer history tables, staleness limit 10",
+           "value": round(1e3 / ms, 2), "unit": "iters/s", "ms_per_step": round(ms, 4), "steps": steps,
+           "warmup": warmup, "host_issue_ms_per_step": round(issue, 4), "nodes": nodes, "edges": graph.num_edges,
+           "history_hits_last_step": hits, "roofline": roof,
+           "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt.items())}}
+    if cpu_steps > 0:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import hc_oracle
+        hc_oracle.build()
+        from cpu_trainer import CpuTrainer
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        host = feats.cpu().numpy()
+        ctr = CpuTrainer(host, nodes, feat, hidden, classes, 3, buffer_elems=600_000 * 256,
+                         sorted_indices=graph.sorted_indices.cpu().numpy()[:0], rate=0.5, staleness=10, seed=seed)
+        cb = [(b.ptr.cpu().numpy(), b.idx.cpu().numpy(), b.sub_to_full.cpu().numpy(), b.y.cpu().numpy(),
+               [int(v) for v in b.num_node_in_layer]) for b in batches[:cpu_steps + 1]]
+        ctr.step(*cb[0])
+        t0 = time.time()
+        for c in cb[1:]:
+            ctr.step(*c)
+        dt = time.time() - t0
+        out["cpu_baseline"] = {"value": round(cpu_steps / dt, 4), "unit": "iters/s", "cores": cores, "kind": "port",
+                               "sample": f"{cpu_steps} iterations of the same batches after 1 warm-up, CPU restatement "
+                                         "with ONE unified history buffer of the same number of rows (the per-layer "
+                                         "table trainer has no CPU restatement); history starts empty"}
+    del tr, feats, uvm, graph
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cpu_steps=2, seed=0):
+    """configs[4] at a stated reduced size: 2-layer RGCN (hidden 1024, 153 classes, 5 relations) on a
+    heterogeneous graph with three node types in the proportions 121 M : 122 M : 26 K, Zipf 2.0
+    degrees, fp16 dim-768 features in pinned host memory, batch 1 000, fan-outs 25/15.  The full
+    size (244 M nodes, 373 GB of features) cannot be held; per-batch work does not depend on it."""
+    from hiscache import HistoryTrainer, HostFeatureStore, make_config
+    from hiscache.sampler import Loader, SyntheticGraph
+    feat, hidden, classes, fan, R = 768, 1024, 153, [25, 15], 5
+    n_p = int(nodes * 121 / 243.026)
+    n_a = int(nodes * 122 / 243.026)
+    bounds = [0, n_p, n_p + n_a, nodes]
+    t0 = time.time()
+    graph = SyntheticGraph(nodes, 7.0, 2.0, classes, seed=seed, device=device, num_train=min(nodes, 200_000))
+    uvm = HostFeatureStore.synthetic(nodes, feat, torch.float16, seed, device)
+    prep_s = time.time() - t0
+    cfg = make_config(feature_dim=feat, num_classes=classes, hidden_dim=hidden, num_layers=2, num_nodes=nodes,
+                      model="rgcn", num_rel=R, device=str(device), limit=cache_gb, staleness_thres=10,
+                      batch_size=1000, rate=0.5, fanouts=fan, feat_mode="history_uvm")
+    cfg.dl.dataset["type_bounds"] = bounds
+    cfg.dl.dataset["rel_table"] = MAG_REL_TABLE
+    loader = Loader(graph, fan, 1000, "history_uvm", seed=seed, iters_per_epoch=1 << 30)
+    tr = HistoryTrainer(cfg, graph=graph, uvm=uvm, loader=loader, storage_dtype=torch.float16, seed=seed)
+    tr.model.train()
+    it = loader.train_loader
+    batches = [next(it) for _ in range(warmup + steps)]
+    tr.table.load_stats.zero_()
+    ms, issue = _time_steps(tr.train_step, batches, warmup)
+    stats = tr.table.load_stats.tolist()
+    host_rows = stats[0] / (steps + warmup)
+    ms_e2e, h2d = _e2e_steps(tr, [b.pin() for b in batches], warmup)
+    n_prof = min(steps, 10)
+    kt = _kernel_table(tr, batches[warmup:], n_prof)
+    peak, src = _peak()
+    link = measure_h2d_peak(device)
+    roofs = []
+    dom = f"hc_aggr_fwd[f16,F={feat}]"
+    if dom in kt:
+        ms_l = kt[dom]["ms_total"] / kt[dom]["launches"]
+        # relation-segmented aggregation of the first conv: every kept edge reads one 1.5 KB row,
+        # the (relation, destination) sums are written once
+        nn = [int(v) for v in batches[-1].num_node_in_layer]
+        ne = [int(v) for v in batches[-1].num_edge_in_layer]
+        byts = ne[1] * feat * 2 + R * nn[1] * feat * 4 + 8 * (R * nn[1] + 1 + ne[1]) + 4 * ne[1]
+        roofs.append({"bound": "hbm", "kernel": "aggr_fwd_vec_kernel<half, edge weights> over the relation-"
+                                                "segmented block of the first conv",
+                      "achieved": round(byts / ms_l / 1e6, 1), "peak": peak, "peak_source": src, "unit": "GB/s",
+                      "frac": round(byts / ms_l / 1e6 / peak, 4), "bytes_per_launch": int(byts),
+                      "us_per_launch": round(ms_l * 1e3, 2), "traffic": None,
+                      "note": "upper bound on the bytes: pruned edges are counted as gathered"})
+    if "hc_load_rows" in kt:
+        ms_l = kt["hc_load_rows"]["ms_total"] / kt["hc_load_rows"]["launches"]
+        byts = host_rows * feat * 2
+        roofs.append({"bound": "host-link", "kernel": "load_rows (batch.x assembly, 1.5 KB rows over the host link)",
+                      "achieved": round(byts / ms_l / 1e6, 2), "peak": link, "unit": "GB/s",
+                      "frac": round(byts / ms_l / 1e6 / link, 4) if link else None,
+                      "bytes_per_launch": int(byts), "ms_per_launch": round(ms_l, 4)})
+    out = {"workload": "configs[4] at reduced size: 2-layer RGCN (hidden 1024, 153 classes, 5 relations from 3 node "
+                       "types), fp16 dim-768 features in pinned host memory, batch 1 000, fan-outs 25/15",
+           "value": round(1e3 / ms, 2), "unit": "iters/s", "ms_per_step": round(ms, 4), "steps": steps,
+           "warmup": warmup, "host_issue_ms_per_step": round(issue, 4),
+           "e2e": {"value": round(1e3 / ms_e2e, 2), "unit": "iters/s", "h2d_bytes_per_step": int(h2d),
+                   "d2h_bytes_per_step": 4},
+           "nodes": nodes, "node_types": [bounds[1], bounds[2] - bounds[1], bounds[3] - bounds[2]],
+           "edges": graph.num_edges, "feature_cache_gb": cache_gb, "prep_s": round(prep_s, 1),
+           "full_size": "121 M / 122 M / 26 K nodes, ~1.7 B edges, 373 GB of features: cannot be held",
+           "host_rows_per_step": round(host_rows, 1), "roofline": roofs[0] if roofs else None,
+           "roofline_top": roofs,
+           "relation_edge_counts_last_layer": [int(v) for v in tr.model.convs[-1].last_count.tolist()],
+           "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt.items())}}
+    if cpu_steps > 0:
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import hc_oracle
+        hc_oracle.build()
+        from cpu_trainer import CpuRgcnTrainer
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        ctr = CpuRgcnTrainer(uvm.buffer.numpy(), nodes, feat, hidden, classes, 2, R, bounds, MAG_REL_TABLE,
+                             buffer_elems=int(cache_gb * 1024 ** 3 // 2),
+                             sorted_indices=graph.sorted_indices.cpu().numpy(), rate=0.5, staleness=10, seed=seed)
+        cb = [(b.ptr.cpu().numpy(), b.idx.cpu().numpy(), b.sub_to_full.cpu().numpy(), b.y.cpu().numpy(),
+               [int(v) for v in b.num_node_in_layer]) for b in batches[:cpu_steps + 1]]
+        ctr.step(*cb[0])
+        t0 = time.time()
+        for c in cb[1:]:
+            ctr.step(*c)
+        dt = time.time() - t0
+        out["cpu_baseline"] = {"value": round(cpu_steps / dt, 4), "unit": "iters/s", "cores": cores, "kind": "port",
+                               "sample": f"{cpu_steps} iterations of the same batches after 1 warm-up; "
+                                         "history starts empty"}
+    del tr, uvm, graph
+    torch.cuda.empty_cache()
+    return out
 
 
 def measure_h2d_peak(device):
@@ -695,10 +926,31 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_other(args):
+    """--config 2 / 5 as the bench line (one GPU)."""
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(device)
+    if int(os.environ.get("RANK", 0)) != 0:
+        return
+    cs = 0 if args.no_cpu_baseline else args.cpu_steps
+    if args.config == 2:
+        r = bench_config2(device, steps=args.steps, warmup=args.warmup, cpu_steps=cs, seed=args.seed)
+    else:
+        r = bench_config5(device, steps=args.steps, warmup=args.warmup, cpu_steps=cs, seed=args.seed,
+                          nodes=min(args.nodes, 16_000_000), cache_gb=args.cache_gb)
+    out = {"metric": "train iters/sec", "value": r["value"], "unit": "iters/s", "n_gpus": 1, "steps": r["steps"],
+           "warmup": r["warmup"], "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "f32 accumulate", "data": "synthetic", "config": {"workload": r["workload"]}}
+    out.update({k: v for k, v in r.items() if k not in out and k != "workload"})
+    print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config != 3:
+        run_other(args)
     else:
         sys.exit(run_ours(args))
 

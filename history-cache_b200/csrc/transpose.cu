@@ -9,6 +9,7 @@
 // once as the sum of its destinations' gradient rows: no atomics on the data, no
 // zero-fill, deterministic.
 #include "common.cuh"
+#include "radix.cuh"
 
 namespace hc {
 
@@ -24,11 +25,6 @@ namespace hc {
 // get the key n_src and end up behind every real list.  ceil(bits(n_src)/8) passes of
 //   digit histogram per 4096-key chunk -> exclusive scan (digit-major) -> stable scatter.
 // ---------------------------------------------------------------------------
-constexpr int kRadixWarps = 8;
-constexpr int kRadixIters = 16;                                   // keys per lane and pass
-constexpr int kRadixChunk = kRadixWarps * kRadixIters * kWarp;    // 4096 keys per block
-constexpr int kTScan = 1024;
-
 // key/payload of every edge slot in [0, n_edges)
 __global__ void __launch_bounds__(256)
     tr_expand_kernel(const hc_aggr_args a, const int64_t n_edges, uint32_t* __restrict__ key,
@@ -56,132 +52,6 @@ __global__ void __launch_bounds__(256)
   for (int64_t e = tail + gtid; e < n_edges; e += stride) {
     key[e] = none;
     val[e] = 0;
-  }
-}
-
-// per-warp digit counts of this block's chunk, in shared memory cnt[warp][digit]
-__device__ __forceinline__ void radix_count(const uint32_t* __restrict__ key, int64_t n, int shift,
-                                            uint32_t (*cnt)[256]) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < kRadixWarps * 256; i += blockDim.x) (&cnt[0][0])[i] = 0;
-  __syncthreads();
-  const int64_t base = (int64_t)blockIdx.x * kRadixChunk + (int64_t)warp * (kRadixIters * kWarp);
-#pragma unroll 4
-  for (int it = 0; it < kRadixIters; ++it) {
-    const int64_t i = base + it * kWarp + lane;
-    if (i < n) atomicAdd(&cnt[warp][(key[i] >> shift) & 255u], 1u);
-  }
-  __syncthreads();
-}
-
-__global__ void __launch_bounds__(kRadixWarps * kWarp)
-    tr_hist_kernel(const uint32_t* __restrict__ key, int64_t n, int shift, int64_t nblk,
-                   uint32_t* __restrict__ hist) {
-  __shared__ uint32_t cnt[kRadixWarps][256];
-  radix_count(key, n, shift, cnt);
-  const int d = threadIdx.x;   // 256 threads, one digit each
-  uint32_t t = 0;
-#pragma unroll
-  for (int w = 0; w < kRadixWarps; ++w) t += cnt[w][d];
-  hist[(int64_t)d * nblk + blockIdx.x] = t;   // digit-major: the scan order of an LSD pass
-}
-
-// three-phase exclusive scan of v[0..n) in place (uint32)
-__global__ void __launch_bounds__(kTScan)
-    tr_block_sum_kernel(const uint32_t* __restrict__ v, int64_t n, uint32_t* __restrict__ sums) {
-  __shared__ uint32_t sh[kTScan / 32];
-  const int64_t i = (int64_t)blockIdx.x * kTScan + threadIdx.x;
-  uint32_t x = i < n ? v[i] : 0;
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) x += __shfl_xor_sync(kFull, x, off);
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = x;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t t = 0;
-    for (int w = 0; w < kTScan / 32; ++w) t += sh[w];
-    sums[blockIdx.x] = t;
-  }
-}
-__global__ void __launch_bounds__(1024) tr_scan_sums_kernel(uint32_t* sums, int64_t nb) {
-  __shared__ uint32_t part[1024];
-  __shared__ uint32_t carry;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
-  for (int64_t base = 0; base < nb; base += 1024) {
-    const int64_t b = base + threadIdx.x;
-    const uint32_t c = b < nb ? sums[b] : 0;
-    part[threadIdx.x] = c;
-    __syncthreads();
-    for (int off = 1; off < 1024; off <<= 1) {
-      const uint32_t v = threadIdx.x >= off ? part[threadIdx.x - off] : 0;
-      __syncthreads();
-      part[threadIdx.x] += v;
-      __syncthreads();
-    }
-    if (b < nb) sums[b] = carry + part[threadIdx.x] - c;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry += part[1023];
-    __syncthreads();
-  }
-}
-__global__ void __launch_bounds__(kTScan)
-    tr_scan_apply_kernel(uint32_t* __restrict__ v, int64_t n, const uint32_t* __restrict__ sums) {
-  __shared__ uint32_t wsum[kTScan / 32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t i = (int64_t)blockIdx.x * kTScan + threadIdx.x;
-  const uint32_t c = i < n ? v[i] : 0;
-  uint32_t x = c;  // inclusive scan inside the warp
-#pragma unroll
-  for (int off = 1; off < 32; off <<= 1) {
-    const uint32_t t = __shfl_up_sync(kFull, x, off);
-    if (lane >= off) x += t;
-  }
-  if (lane == 31) wsum[warp] = x;
-  __syncthreads();
-  uint32_t before = sums[blockIdx.x];
-  for (int w = 0; w < warp; ++w) before += wsum[w];
-  if (i < n) v[i] = before + x - c;
-}
-
-// stable scatter of one pass: a key goes to (scanned start of its digit for this block) +
-// (keys of that digit in lower warps of the block) + (its rank among the warp's earlier keys)
-__global__ void __launch_bounds__(kRadixWarps * kWarp)
-    tr_scatter_kernel(const uint32_t* __restrict__ key, const uint32_t* __restrict__ val, int64_t n,
-                      int shift, int64_t nblk, const uint32_t* __restrict__ hist,
-                      uint32_t* __restrict__ key_out, uint32_t* __restrict__ val_out) {
-  __shared__ uint32_t cnt[kRadixWarps][256];
-  radix_count(key, n, shift, cnt);
-  {
-    const int d = threadIdx.x;
-    uint32_t run = hist[(int64_t)d * nblk + blockIdx.x];
-#pragma unroll
-    for (int w = 0; w < kRadixWarps; ++w) {
-      const uint32_t c = cnt[w][d];
-      cnt[w][d] = run;     // from now on: next free position of digit d for warp w
-      run += c;
-    }
-  }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned lt = (1u << lane) - 1u;
-  const int64_t base = (int64_t)blockIdx.x * kRadixChunk + (int64_t)warp * (kRadixIters * kWarp);
-  for (int it = 0; it < kRadixIters; ++it) {
-    const int64_t i = base + it * kWarp + lane;
-    const bool ok = i < n;
-    const uint32_t k = ok ? key[i] : 0u;
-    const uint32_t v = ok ? val[i] : 0u;
-    const uint32_t d = ok ? ((k >> shift) & 255u) : 256u;   // lanes past the end match only each other
-    const unsigned same = __match_any_sync(kFull, d);
-    const int rank = __popc(same & lt);
-    uint32_t pos = 0;
-    if (ok) pos = cnt[warp][d] + rank;
-    __syncwarp();
-    if (ok && rank == 0) cnt[warp][d] += __popc(same);
-    __syncwarp();
-    if (ok) {
-      key_out[pos] = k;
-      val_out[pos] = v;
-    }
   }
 }
 
@@ -453,10 +323,7 @@ static int radix_passes(int64_t n_src) {
 extern "C" int64_t hc_transpose_scratch_bytes(int64_t n_src, int64_t n_edges) {
   (void)n_src;
   if (n_edges < 1) n_edges = 1;
-  const int64_t nblk = ceil_div(n_edges, kRadixChunk);
-  const int64_t nh = 256 * nblk;
-  const int64_t nsum = ceil_div(nh, kTScan);
-  return (4 * n_edges + nh + nsum + 64) * (int64_t)sizeof(uint32_t);
+  return (4 * n_edges + radix_hist_words(n_edges)) * (int64_t)sizeof(uint32_t);
 }
 
 static int check_simple(const hc_aggr_args* a) {
@@ -482,8 +349,7 @@ extern "C" int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_
   HC_REQUIRE(scratch != nullptr && aligned_to(scratch, 8), HC_ERR_NULL);
   HC_REQUIRE(a->ptr && a->idx && t_dst && t_w, HC_ERR_NULL);
   const int64_t nblk = ceil_div(n_edges, kRadixChunk);
-  const int64_t nh = 256 * nblk, nsum = ceil_div(nh, kTScan);
-  HC_REQUIRE(nblk <= 0x7fffffffLL && nsum <= 0x7fffffffLL, HC_ERR_SIZE);
+  HC_REQUIRE(256 * nblk <= 0x7fffffffLL, HC_ERR_SIZE);
   uint32_t* key[2];
   uint32_t* val[2];
   key[0] = reinterpret_cast<uint32_t*>(scratch);
@@ -491,25 +357,13 @@ extern "C" int hc_transpose_block(const hc_aggr_args* a, int64_t n_edges, int64_
   val[0] = key[1] + n_edges;
   val[1] = val[0] + n_edges;
   uint32_t* hist = val[1] + n_edges;
-  uint32_t* sums = hist + nh;
   // rows or leftover slots, whichever needs more threads (the tail loop is grid-strided)
   int64_t eb = ceil_div(a->num_node * 8, 256);
   const int64_t tail_b = ceil_div(n_edges, 256 * 8);
   if (tail_b > eb) eb = tail_b;
   HC_REQUIRE(eb <= 0x7fffffffLL, HC_ERR_SIZE);
   tr_expand_kernel<<<(unsigned)eb, 256, 0, st>>>(*a, n_edges, key[0], val[0]);
-  const int passes = radix_passes(a->n_src);
-  int cur = 0;
-  for (int p = 0; p < passes; ++p) {
-    const int shift = 8 * p;
-    tr_hist_kernel<<<(unsigned)nblk, kRadixWarps * kWarp, 0, st>>>(key[cur], n_edges, shift, nblk, hist);
-    tr_block_sum_kernel<<<(unsigned)nsum, kTScan, 0, st>>>(hist, nh, sums);
-    tr_scan_sums_kernel<<<1, 1024, 0, st>>>(sums, nsum);
-    tr_scan_apply_kernel<<<(unsigned)nsum, kTScan, 0, st>>>(hist, nh, sums);
-    tr_scatter_kernel<<<(unsigned)nblk, kRadixWarps * kWarp, 0, st>>>(key[cur], val[cur], n_edges, shift, nblk,
-                                                                     hist, key[cur ^ 1], val[cur ^ 1]);
-    cur ^= 1;
-  }
+  const int cur = radix_sort_pairs(key, val, n_edges, radix_passes(a->n_src), hist, st);
   tr_finalize_kernel<<<(unsigned)ceil_div(n_edges, 256), 256, 0, st>>>(key[cur], val[cur], n_edges, a->n_src,
                                                                       a->ptr, t_ptr, t_dst, t_w);
   HC_LAUNCH_OK();

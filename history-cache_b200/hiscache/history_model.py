@@ -209,10 +209,17 @@ class HistorySAGE(torch.nn.Module):
 
 class MyRGCNConvHistory2(torch.nn.Module):
     """out[d] = (1/deg(d)) * sum_e x[src_e] @ W[rel_e], history rows overriding
-    (hiscache/history_model.py:220-278).  The reference sorts edges by relation and calls
-    cxgnncomp.RGCNOP_sorted, which is not part of the project; here each relation is a
-    masked weighted-sum aggregation (edge value 1 on the relation's edges) followed by one
-    dense product, normalised by the total in-degree as the reference does (:245,272)."""
+    (hiscache/history_model.py:220-278).
+
+    The reference gives edges with an unused source the relation num_rel (:250), sorts the edges
+    by relation (torch.sort), counts them per relation (count_num, :260) and calls
+    cxgnncomp.RGCNOP_sorted, which is not part of the project.  Here hc_rgcn_group does the
+    pruning, the sort (one stable radix pass) and builds a CSR over (relation, destination)
+    rows; ONE pass of the aggregation kernel then reads every source row once per kept edge and
+    leaves the per-(relation, destination) sums, and the typed transform is one product per
+    relation accumulated in place: out = sum_r A[r] @ W[r].  Normalisation is by the total
+    in-degree, as in the reference (:245,272).  Edges into destinations that are served from
+    history are pruned as well (their result is overwritten, :273-274)."""
 
     def __init__(self, in_channels, hidden_channels, num_rel, need_grad):
         super().__init__()
@@ -222,6 +229,7 @@ class MyRGCNConvHistory2(torch.nn.Module):
         self.linear = torch.nn.Parameter(torch.empty(num_rel, in_channels, hidden_channels))
         self.reset_parameters()
         self.need_grad = need_grad
+        self.last_count = None      # count_num of the last call (int32 [num_rel + 1], device)
 
     def reset_parameters(self):
         # glorot (torch_geometric.nn.inits.glorot in the reference, :240)
@@ -232,23 +240,23 @@ class MyRGCNConvHistory2(torch.nn.Module):
     def forward(self, x, ptr, idx, edge_types, count, history_map, history_buffer, used_mask,
                 history_size, num_node, indexed=False, score_out=None):
         num_node = int(num_node)
-        num_edge = int(ptr[num_node])
-        deg = (ptr[1:num_node + 1] - ptr[:num_node]).clamp(min=1).to(torch.float32)
-        src = idx[:num_edge]
-        rel = edge_types[:num_edge]
-        if used_mask is not None:
-            rel = torch.where(used_mask[src], rel, torch.full_like(rel, self.num_rel))  # :250
-        out = None
+        R = self.num_rel
+        has_hist = history_size > 0 and history_map is not None and history_map.numel() > 0
+        hmap = history_map[:num_node] if has_hist else None
+        ptr2, idx2, w2, _, rel = hb.rgcn_group(ptr, idx, edge_types, num_node, R, used_src=used_mask,
+                                               hmap=hmap, want_rel=True)
+        # segment sizes per relation, as the reference computes them (:260); value 0 is never
+        # counted there (grad_check.cu:169), so relation 0's size comes from the grouped CSR
+        self.last_count = hb.count_num(rel, R)
         xf = x if x.dtype in (torch.float32, torch.float16) else x.float()
-        for r in range(self.num_rel):
-            w = (rel == r).to(torch.float32)
-            agg = hb.aggr_forward(xf, ptr, idx, num_node, edge_value=w, force_grad=False)
-            term = agg @ self.linear[r]
-            out = term if out is None else out + term
-        out = out / deg.unsqueeze(-1)
-        if history_size > 0 and history_map is not None and history_map.numel() > 0:
-            hit = history_map[:num_node] != -1
-            rows = hb.gather_rows(history_buffer, history_map[:num_node] if indexed else
+        agg = hb.aggr_forward(xf, ptr2, idx2, R * num_node, edge_value=w2, force_grad=False)
+        agg = agg.view(R, num_node, -1)
+        out = agg[0] @ self.linear[0]
+        for r in range(1, R):
+            out = torch.addmm(out, agg[r], self.linear[r])
+        if has_hist:
+            hit = hmap != -1
+            rows = hb.gather_rows(history_buffer, hmap if indexed else
                                   torch.where(hit, torch.arange(num_node, device=x.device), -1),
                                   zero_missing=True, out_dtype=torch.float32)
             out = torch.where(hit.unsqueeze(-1), rows, out)
@@ -272,6 +280,11 @@ class HistoryRGCN(torch.nn.Module):
         self.table = table
         self.num_rel = kwargs["num_rel"]
         self.dataset_name = kwargs.get("dataset_name", "")
+        # node types as ranges of global ids + relation per (dst type, src type): when given, edge
+        # types are generated from the batch (the reference does so for "rmag240m", :340-357)
+        self.type_bounds = kwargs.get("type_bounds", None)
+        self.rel_table = kwargs.get("rel_table", None)
+        self.gen_rel = self.type_bounds is not None and self.rel_table is not None
         self.init_convs(num_rel=self.num_rel)
 
     def forward(self, batch):
@@ -280,7 +293,10 @@ class HistoryRGCN(torch.nn.Module):
         nn, ne = batch.num_node_in_layer, batch.num_edge_in_layer
         L = self.num_layers
         etypes = batch.edge_type
-        if etypes is None:  # :363-366
+        if etypes is None and self.gen_rel:
+            etypes = hb.edge_types(batch.ptr, batch.idx, batch.sub_to_full, int(nn[L - 1]),
+                                   self.type_bounds, self.rel_table)
+        elif etypes is None:  # :363-366
             etypes = torch.randint(0, self.num_rel, (int(ne[L - 1]),), device=x.device)
         um = self.table.used_masks
         for i, conv in enumerate(self.convs[:-1]):
@@ -337,6 +353,8 @@ def get_model(config, table):
     if kind == "rgcn":
         return model_dict[kind](in_channel, hidden_channel, out_channel, num_layers, dropout,
                                 graph_type, config, table, num_rel=config.train.model.num_rel,
-                                dataset_name=str(cfg_get(config, "dl.dataset.name", "")).lower())
+                                dataset_name=str(cfg_get(config, "dl.dataset.name", "")).lower(),
+                                type_bounds=cfg_get(config, "dl.dataset.type_bounds", None),
+                                rel_table=cfg_get(config, "dl.dataset.rel_table", None))
     return model_dict[kind](in_channel, hidden_channel, out_channel, num_layers, dropout,
                             graph_type, config, table)

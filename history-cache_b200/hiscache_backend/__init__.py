@@ -1113,6 +1113,62 @@ def relabel(nbr, local_map, n_total):
 
 
 # ---------------------------------------------------------------------------
+# heterogeneous layers
+# ---------------------------------------------------------------------------
+def edge_types(ptr_t, idx_t, sub_to_full, rows, type_bounds, rel_table):
+    """etype[e] = rel_table[type(dst)][type(src)], node types being ranges of global ids:
+    the counterpart of cxgnncomp_backend.gen_edge_type_mag240m (hiscache/history_model.py:354-357)."""
+    dev = require_cuda(ptr_t, idx_t, sub_to_full)
+    T = len(type_bounds) - 1
+    if T < 1 or T > 8 or len(rel_table) != T * T:
+        raise ValueError("edge_types: 1..8 node types, rel_table of n_types^2 entries")
+    out = torch.empty(idx_t.shape[0], dtype=torch.int64, device=dev)
+    rows = int(rows)
+    if idx_t.shape[0] and rows < ptr_t.shape[0] - 1:
+        out.fill_(0)     # edges behind the rows asked for
+    b = (C.c_int64 * (T + 1))(*[int(v) for v in type_bounds])
+    r = (C.c_int32 * (T * T))(*[int(v) for v in rel_table])
+    with on_device(dev), _span("hc_edge_types", dev):
+        check(lib.hc_edge_types(ptr(i64c(ptr_t)), ptr(i64c(idx_t)), ptr(i64c(sub_to_full)), rows, T, b, r,
+                                ptr(out), stream_of(dev)), "hc_edge_types")
+    _called()
+    return out
+
+
+def rgcn_group(ptr_t, idx_t, etype, num_node, num_rel, used_src=None, hmap=None, want_perm=False,
+               want_rel=False):
+    """The relation-segmented block of one RGCN layer (hc_rgcn_group): (ptr2 [num_rel*num_node+1],
+    idx2 [E], w2 [E], perm or None, rel or None)."""
+    dev = require_cuda(ptr_t, idx_t, etype, used_src, hmap)
+    ptr_t, idx_t, etype, hmap = i64c(ptr_t, "ptr"), i64c(idx_t, "idx"), i64c(etype, "edge_type"), i64c(hmap)
+    n_edges = min(int(idx_t.shape[0]), int(etype.shape[0]))
+    num_node, num_rel = int(num_node), int(num_rel)
+    if ptr_t.shape[0] < num_node + 1:
+        raise RuntimeError("rgcn_group: ptr shorter than num_node + 1")
+    if hmap is not None and hmap.shape[0] < num_node:
+        raise RuntimeError("rgcn_group: history map shorter than num_node")
+    if used_src is not None:
+        used_src = used_src.contiguous()
+        if used_src.dtype == torch.bool:
+            used_src = used_src.view(torch.uint8)
+        elif used_src.dtype != torch.uint8:
+            raise TypeError("rgcn_group: used mask must be bool")
+    ptr2 = torch.empty(num_rel * num_node + 1, dtype=torch.int64, device=dev)
+    idx2 = torch.empty(max(n_edges, 1), dtype=torch.int64, device=dev)
+    w2 = torch.empty(max(n_edges, 1), dtype=torch.float32, device=dev)
+    perm = torch.empty(max(n_edges, 1), dtype=torch.int64, device=dev) if want_perm else None
+    rel = torch.empty(max(n_edges, 1), dtype=torch.int64, device=dev) if want_rel else None
+    sc = scratch(dev, lib.hc_rgcn_group_scratch_bytes(n_edges), "rgcn")
+    with on_device(dev), _span("hc_rgcn_group", dev):
+        check(lib.hc_rgcn_group(ptr(ptr_t), ptr(idx_t), ptr(etype), num_node, n_edges, num_rel, ptr(used_src),
+                                ptr(hmap), ptr(ptr2), ptr(idx2), ptr(w2), ptr(perm), ptr(rel), ptr(sc),
+                                stream_of(dev)), "hc_rgcn_group")
+    _called(7)
+    return ptr2, idx2[:n_edges], w2[:n_edges], None if perm is None else perm[:n_edges], \
+        None if rel is None else rel[:n_edges]
+
+
+# ---------------------------------------------------------------------------
 # peer copies (kept for API compatibility; the multi-GPU path uses NCCL)
 # ---------------------------------------------------------------------------
 def p2psend(tsrc, tdst, num_element, target_device):

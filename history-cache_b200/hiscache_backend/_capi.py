@@ -97,6 +97,9 @@ _SIGS = {
     "hc_norm_scratch_bytes": (i64, [i32]),
     "hc_norm_act_fwd": (C.c_int, [C.POINTER(NormArgs), vp, vp, vp]),
     "hc_norm_act_bwd": (C.c_int, [C.POINTER(NormArgs), vp, vp, vp, vp, vp, vp]),
+    "hc_edge_types": (C.c_int, [vp, vp, vp, i64, i32, vp, vp, vp, vp]),
+    "hc_rgcn_group_scratch_bytes": (i64, [i64]),
+    "hc_rgcn_group": (C.c_int, [vp, vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
     "hc_mix64": (C.c_uint64, [C.c_uint64]),
     "hc_bucket_scratch_bytes": (i64, [i64, i32]),
     "hc_bucket_by_owner": (C.c_int, [vp, vp, i64, i32, vp, vp, vp, vp, vp]),

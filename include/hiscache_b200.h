@@ -667,6 +667,43 @@ int hc_norm_act_fwd(const hc_norm_args* a, float* y, void* scratch, void* stream
 int hc_norm_act_bwd(const hc_norm_args* a, const float* grad_y, float* grad_x, float* grad_weight,
                     float* grad_bias, void* scratch, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Heterogeneous (RGCN) layers: edge types and the relation-segmented block.
+ *
+ * hc_edge_types: etype[e] = rel_table[type(dst) * n_types + type(src)] for the
+ *   edges of rows [0, rows), where a node's type is the range of type_bounds
+ *   (HOST int64 [n_types + 1], ascending) its GLOBAL id sub_to_full[.] falls
+ *   in; rel_table: HOST int32 [n_types * n_types]; n_types <= 8.  Stand-in for
+ *   cxgnncomp_backend.gen_edge_type_mag240m(ptr, idx, sub_to_full)
+ *   (hiscache/history_model.py:354-357), which is not part of the reference.
+ *
+ * hc_rgcn_group: what MyRGCNConvHistory2.forward does with torch.sort before it
+ *   calls RGCNOP_sorted (hiscache/history_model.py:244-266).  Edge e of row d
+ *   (e in [ptr[d], ptr[d+1]), d < num_node; slots up to n_edges) keeps its
+ *   relation etype[e] unless its source is unused (used_src[idx[e]] == 0, :250),
+ *   d is served from history (hmap[d] != -1, optional) or etype[e] is outside
+ *   [0, num_rel): then it gets num_rel and drops out.  The edges are sorted by
+ *   relation with ONE stable radix pass, so inside a relation they stay in
+ *   destination order.  Outputs:
+ *     ptr2 int64 [num_rel * num_node + 1], idx2 int64 [n_edges], w2 fp32
+ *       [n_edges]: a CSR whose row r * num_node + d lists the sources of d's
+ *       relation-r edges with the weight 1 / (ptr[d+1] - ptr[d]) beside each
+ *       (the reference divides by the total in-degree, :245,272);
+ *       ptr2[num_rel * num_node] = number of edges kept;
+ *     perm int64 [n_edges] or NULL: the sorted order (torch.sort's indices);
+ *     rel_out int64 [n_edges] or NULL: the relation of every edge after
+ *       pruning, in edge order (the array the reference passes to count_num).
+ *   num_rel <= 255.  scratch >= hc_rgcn_group_scratch_bytes(n_edges).
+ */
+int hc_edge_types(const int64_t* ptr, const int64_t* idx, const int64_t* sub_to_full, int64_t rows,
+                  int32_t n_types, const int64_t* type_bounds, const int32_t* rel_table,
+                  int64_t* etype, void* stream);
+int64_t hc_rgcn_group_scratch_bytes(int64_t n_edges);
+int hc_rgcn_group(const int64_t* ptr, const int64_t* idx, const int64_t* etype, int64_t num_node,
+                  int64_t n_edges, int32_t num_rel, const uint8_t* used_src, const int64_t* hmap,
+                  int64_t* ptr2, int64_t* idx2, float* w2, int64_t* perm, int64_t* rel_out,
+                  void* scratch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

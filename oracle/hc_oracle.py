@@ -337,3 +337,38 @@ def sample_batch(gptr, gidx, seeds, fanouts, batch_seed):
                 sub_to_full=np.asarray(nodes, dtype=np.int64),
                 num_node_in_layer=np.asarray(layer_nodes, dtype=np.int64),
                 num_edge_in_layer=np.asarray(layer_edges, dtype=np.int64))
+
+
+# ---------------------------------------------------------------------------
+# heterogeneous layers
+# ---------------------------------------------------------------------------
+def rgcn_sorted_edges(ptr, idx, edge_types, num_node, num_rel, used_mask=None, hmap=None):
+    """What MyRGCNConvHistory2.forward hands to RGCNOP_sorted (hiscache/history_model.py:244-266):
+    (src[perm], dst[perm], rel after pruning, perm, count).  Edges with an unused source get the
+    relation num_rel (:250); `hmap` additionally drops the edges of destinations served from
+    history, whose result the layer overwrites anyway (:273-274).  The sort is the stable one (the
+    reference's torch.sort leaves the order inside a relation unspecified); count is count_num
+    (grad_check.cu:165-182), which never counts value 0."""
+    ptr, idx = np.asarray(ptr, dtype=np.int64), np.asarray(idx, dtype=np.int64)
+    num_edge = int(ptr[num_node])
+    deg = ptr[1:num_node + 1] - ptr[:num_node]
+    dst = np.repeat(np.arange(num_node, dtype=np.int64), deg)
+    src = idx[:num_edge]
+    rel = np.asarray(edge_types, dtype=np.int64)[:num_edge].copy()
+    if used_mask is not None:
+        rel[~np.asarray(used_mask, dtype=bool)[src]] = num_rel
+    if hmap is not None:
+        rel[np.asarray(hmap)[dst] != -1] = num_rel
+    perm = np.argsort(rel, kind="stable")
+    return src[perm], dst[perm], rel, perm, count_num(rel, num_rel)
+
+
+def edge_types(ptr, idx, sub_to_full, rows, type_bounds, rel_table):
+    """etype[e] = rel_table[type(dst)][type(src)] with node types given as ranges of global ids."""
+    ptr, idx, s2f = (np.asarray(a, dtype=np.int64) for a in (ptr, idx, sub_to_full))
+    T = len(type_bounds) - 1
+    typ = np.clip(np.searchsorted(np.asarray(type_bounds, dtype=np.int64), s2f, side="right") - 1, 0, T - 1)
+    deg = ptr[1:rows + 1] - ptr[:rows]
+    dst = np.repeat(np.arange(rows, dtype=np.int64), deg)
+    src = idx[:int(ptr[rows])]
+    return np.asarray(rel_table, dtype=np.int64).reshape(T, T)[typ[dst], typ[src]]

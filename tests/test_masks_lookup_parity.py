@@ -157,3 +157,48 @@ def test_fixed_shape_exchange_helpers(backend, oracle, world, slots):
     win = backend.last_occurrence(cu(dup), claim)
     assert torch.equal(win.cpu(), _cpu_ops.last_occurrence(torch.from_numpy(dup), None))
     assert int((claim != -1).sum()) == 0   # the claim map is left clean
+
+
+@pytest.mark.parametrize("with_used,with_hist", [(False, False), (True, False), (True, True)])
+def test_rgcn_group_matches_the_sorted_edge_lists(backend, oracle, with_used, with_hist):
+    """hc_rgcn_group against the numpy statement of hiscache/history_model.py:244-266: pruning,
+    stable order by relation, count_num, and the (relation, destination) CSR built from them."""
+    rng = np.random.default_rng(7 + with_used + 2 * with_hist)
+    b = layered_batch(rng, 60, [25, 15], total_nodes=9000)
+    ptr, idx = b["ptr"], b["idx"]
+    n_all, n1 = int(b["num_node_in_layer"][-1]), int(b["num_node_in_layer"][1])
+    R = 5
+    for num_node in (n1, int(b["num_node_in_layer"][0])):
+        E = int(ptr[num_node])
+        et = rng.integers(0, R, size=len(idx)).astype(np.int64)
+        used = (rng.random(n_all) < 0.7) if with_used else None
+        hmap = np.where(rng.random(num_node) < 0.3, 1, -1).astype(np.int64) if with_hist else None
+        ptr2, idx2, w2, perm, rel = backend.rgcn_group(cu(ptr), cu(idx), cu(et), num_node, R,
+                                                       used_src=cu(used), hmap=cu(hmap), want_perm=True,
+                                                       want_rel=True)
+        src_s, dst_s, rel_w, perm_w, count_w = oracle.rgcn_sorted_edges(ptr, idx, et, num_node, R, used, hmap)
+        rel_g, perm_g = rel.cpu().numpy(), perm.cpu().numpy()
+        assert np.array_equal(rel_g[:E], rel_w) and (rel_g[E:] == R).all()
+        keep = int((rel_w < R).sum())
+        assert np.array_equal(perm_g[:keep], perm_w[:keep])          # same order of the kept edges
+        assert np.array_equal(backend.count_num(rel[:E], R).cpu().numpy(), count_w)
+        p2, i2, ww = ptr2.cpu().numpy(), idx2.cpu().numpy(), w2.cpu().numpy()
+        assert p2[-1] == keep and p2[0] == 0 and (np.diff(p2) >= 0).all()
+        assert np.array_equal(i2[:keep], src_s[:keep])
+        row2 = rel_w[perm_w[:keep]] * num_node + dst_s[:keep]
+        assert np.array_equal(np.repeat(np.arange(R * num_node), np.diff(p2)), row2)
+        deg = np.diff(ptr)[:num_node]
+        assert np.array_equal(ww[:keep], (np.float32(1.0) / deg[dst_s[:keep]].astype(np.float32)))
+
+
+def test_edge_types_follow_node_type_ranges(backend, oracle):
+    rng = np.random.default_rng(21)
+    b = layered_batch(rng, 50, [10, 5], total_nodes=5000)
+    bounds = [0, 2400, 4900, 5000]                      # three node types
+    table = [0, 1, 1, 2, 0, 3, 4, 4, 2]
+    rows = int(b["num_node_in_layer"][1])
+    got = backend.edge_types(cu(b["ptr"]), cu(b["idx"]), cu(b["sub_to_full"]), rows, bounds, table)
+    want = oracle.edge_types(b["ptr"], b["idx"], b["sub_to_full"], rows, bounds, table)
+    E = int(b["ptr"][rows])
+    assert np.array_equal(got.cpu().numpy()[:E], want)
+    assert set(np.unique(want).tolist()) <= {0, 1, 2, 3, 4}
