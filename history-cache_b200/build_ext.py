@@ -45,18 +45,30 @@ def _stale(target, inputs):
     return any(os.path.getmtime(i) > t for i in inputs)
 
 
+CHECKED_LIB_PATH = os.path.join(LIB_DIR, "libhiscache_b200_checked.so")
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compiles every kernel source and links the shared library; returns its path."""
+    """Compiles every kernel source and links the shared library; returns its path.  Also builds
+    libhiscache_b200_checked.so: the same sources with -DHC_CHECK_BOUNDS (index checks in front
+    of the aggregation operators, see hc_last_status in the header)."""
+    path = _build_one(force, verbose, OBJ_DIR, LIB_PATH, [])
+    _build_one(force, False, os.path.join(LIB_DIR, "obj_checked"), CHECKED_LIB_PATH, ["-DHC_CHECK_BOUNDS"])
+    return path
+
+
+def _build_one(force, verbose, obj_dir, lib_path, extra):
     nvcc = os.environ.get("NVCC", "nvcc")
-    os.makedirs(OBJ_DIR, exist_ok=True)
+    os.makedirs(obj_dir, exist_ok=True)
     deps = _deps()
     jobs = []
     objs = []
     for src in _sources():
-        obj = os.path.join(OBJ_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + deps):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            cmd = ([nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) +
+                   ["-c", src, "-o", obj])
             jobs.append(cmd)
 
     def run(cmd):
@@ -69,13 +81,13 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(" ".join(cmd) + "\n" + p.stdout + p.stderr)
             if p.returncode != 0:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
-    if force or jobs or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs
+    if force or jobs or _stale(lib_path, objs):
+        cmd = [nvcc, "-shared", "-o", lib_path] + objs
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             sys.stderr.write(p.stdout + p.stderr)
             raise RuntimeError("link failed")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":

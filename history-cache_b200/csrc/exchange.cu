@@ -203,6 +203,7 @@ extern "C" const char* hc_error_string(int code) {
     case HC_ERR_ALIGN: return "hiscache_b200: pointer not aligned to its element type";
     case HC_ERR_UNSUPPORTED: return "hiscache_b200: this combination of options is not implemented";
     case HC_ERR_STRUCT: return "hiscache_b200: struct_size does not match this build of the library";
+    case HC_ERR_RANGE: return "hiscache_b200: an index of the block lies outside its table (see hc_last_status)";
     case HC_ERR_LIMIT: return "hiscache_b200: more rows than this entry point's fixed capacity (hc_noalloc_max_rows, or max_ids of a published area)";
     default: return "hiscache_b200: unknown error code";
   }

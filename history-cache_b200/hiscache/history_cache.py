@@ -80,7 +80,7 @@ class HistoryCache:
         self._cached_embedding = None
         self.distributed_store = False
         self.buffer = None
-        self.feat2full = None
+        self.feat2full = self.feat2full_by_slot = None
         self.embed2full = None
         self.overall_feat_num = self.overall_embed_num = 0
         if "history" in self.feat_mode:
@@ -120,7 +120,7 @@ class HistoryCache:
             if os.path.exists(p):
                 sorted_indices = torch.from_numpy(np.fromfile(p, dtype=np.int64))
         if sorted_indices is None or self.uvm is None:
-            self.feat2full = torch.zeros(0, dtype=torch.int64, device=self.device)
+            self.feat2full = self.feat2full_by_slot = torch.zeros(0, dtype=torch.int64, device=self.device)
             return
         indice = sorted_indices.to(self.device)
         cache_indice = indice if self.overall_feat_num > N else indice[-self.overall_feat_num:]
@@ -129,6 +129,16 @@ class HistoryCache:
             new_id += self.overall_feat_num - N
         self.feat2full = cache_indice + N
         self.full2embed[self.feat2full] = new_id
+        # The admission unmaps the feature rows its ring overwrites by SLOT number.  When the buffer
+        # holds every node the slots are offset (new_id above), so feat2full, which the reference
+        # indexes by slot all the same (:226), would name the wrong nodes: the admission gets a
+        # slot-indexed copy whose unused prefix points at the dummy entry 2N.
+        if self.overall_feat_num > N:
+            self.feat2full_by_slot = torch.full((self.overall_feat_num,), 2 * N, dtype=torch.int64,
+                                                device=self.device)
+            self.feat2full_by_slot[self.overall_feat_num - N:] = self.feat2full
+        else:
+            self.feat2full_by_slot = self.feat2full
         view = self.buffer.view(-1, self.in_channels)
         first = view.shape[0] - cache_indice.shape[0]
         step = 1 << 20
@@ -231,6 +241,6 @@ class HistoryCache:
         hb.cache_admit(prod.detach(), self.buffer, self.hidden_channels, self.in_channels,
                        self.overall_embed_num, batch.sub_to_full[:num_node], self.sub2embed, score,
                        self._thres, self.full2embed, self.total_num_node, self.embed2full,
-                       self.feat2full, self._header, reset_header=reset, n_admitted=self._n_admitted,
+                       self.feat2full_by_slot, self._header, reset_header=reset, n_admitted=self._n_admitted,
                        valid=valid)
         self.produced_embedding = None

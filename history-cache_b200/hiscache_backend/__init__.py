@@ -134,11 +134,13 @@ def _aggr_args(inp, ptr_t, idx_t, num_node, edge_value, hmap, hbuf, h_indexed, s
         a.src_map, a.src_alt = ptr(src_map), ptr(src_alt)
         a.alt_dtype = dtype_code(src_alt)
         a.alt_stride = src_alt.stride(0) if src_alt.shape[0] > 1 else H * F
+        a.alt_rows = src_alt.shape[0]
     a.edge_value = ptr(edge_value)
     if hmap is not None:
         a.hmap, a.hbuf, a.h_dtype = ptr(hmap), ptr(hbuf), dtype_code(hbuf)
         a.h_indexed = 1 if h_indexed else 0
         a.hsize = hbuf.stride(0) if hbuf.dim() > 1 and hbuf.shape[0] > 1 else hbuf.shape[-1]
+        a.h_rows = hbuf.shape[0] if hbuf.dim() > 1 else 1
     return a
 
 
@@ -1110,6 +1112,44 @@ def relabel(nbr, local_map, n_total):
                              ptr(out_idx), ptr(sc), stream_of(dev)), "hc_relabel")
     _called(6)
     return new_nodes[:int(n_new)], out_idx
+
+
+def sample_fixed(gptr, gidx, seeds, local_map, seed, batch_no, fanouts, caps, edge_cap, out=None):
+    """A whole batch in the fixed shape (caps, edge_cap) without any device->host read
+    (hc_sample_fixed).  `batch_no`: device int64[1], advanced by the call.  Returns the dict of
+    output tensors (ptr, idx, sub_to_full, mask, counters); `out` reuses a previous one."""
+    dev = require_cuda(gptr, gidx, seeds, local_map, batch_no)
+    L = len(fanouts)
+    if len(caps) != L + 1 or L < 1 or L > 8:
+        raise ValueError("sample_fixed: one cap per layer (hops + 1), 1..8 hops")
+    if local_map.dtype != torch.int32 or batch_no.dtype != torch.int64:
+        raise TypeError("sample_fixed: local_map int32, batch_no int64")
+    seeds = i64c(seeds, "seeds")
+    if seeds.shape[0] > caps[0]:
+        raise RuntimeError("sample_fixed: more seeds than caps[0]")
+    if out is None:
+        out = {"ptr": torch.empty(caps[L - 1] + 1, dtype=torch.int64, device=dev),
+               "idx": torch.empty(max(int(edge_cap), 1), dtype=torch.int64, device=dev),
+               "sub_to_full": torch.empty(caps[L], dtype=torch.int64, device=dev),
+               "mask": torch.empty(caps[L], dtype=torch.bool, device=dev),
+               "counters": torch.zeros(4, dtype=torch.int64, device=dev)}
+    b = _capi.FixedBatch()
+    b.struct_size = C.sizeof(_capi.FixedBatch)
+    b.num_hops = L
+    for h in range(L):
+        b.fanout[h] = int(fanouts[h])
+    for k in range(L + 1):
+        b.caps[k] = int(caps[k])
+    b.edge_cap = int(edge_cap)
+    b.ptr, b.idx, b.sub_to_full = ptr(out["ptr"]), ptr(out["idx"]), ptr(out["sub_to_full"])
+    b.mask, b.counters = ptr(out["mask"]), ptr(out["counters"])
+    sc = scratch(dev, int(lib.hc_sample_fixed_scratch_bytes(C.byref(b))), "sample_fixed")
+    with on_device(dev), _span("hc_sample_fixed", dev):
+        check(lib.hc_sample_fixed(ptr(gptr), ptr(gidx), ptr(seeds), seeds.shape[0], ptr(local_map),
+                                  C.c_uint64(int(seed) & 0xFFFFFFFFFFFFFFFF), ptr(batch_no), C.byref(b),
+                                  ptr(sc), stream_of(dev)), "hc_sample_fixed")
+    _called(2 + 11 * L)
+    return out
 
 
 # ---------------------------------------------------------------------------

@@ -38,6 +38,7 @@ class AggrArgs(C.Structure):
         ("src_map", vp), ("src_alt", vp), ("alt_dtype", i32), ("alt_stride", i64),
         ("edge_value", vp),
         ("hmap", vp), ("hbuf", vp), ("h_dtype", i32), ("h_indexed", i32), ("hsize", i64),
+        ("h_rows", i64), ("alt_rows", i64),
     ]
 
 
@@ -48,6 +49,14 @@ class Shard(C.Structure):
         ("full_to_slot", vp), ("map_len", i64), ("slot_to_full", vp), ("checkin", vp),
         ("capacity", i64), ("table", vp), ("dtype", i32), ("feat", i32), ("header", vp),
         ("iter_dev", vp), ("claim", vp), ("staleness", i64), ("n_admitted", vp),
+    ]
+
+
+class FixedBatch(C.Structure):
+    """struct hc_fixed_batch"""
+    _fields_ = [
+        ("struct_size", C.c_uint32), ("num_hops", i32), ("fanout", i32 * 8), ("caps", i64 * 9),
+        ("edge_cap", i64), ("ptr", vp), ("idx", vp), ("sub_to_full", vp), ("mask", vp), ("counters", vp),
     ]
 
 
@@ -66,6 +75,7 @@ _SIGS = {
     "hc_abi_version": (C.c_int, []),
     "hc_error_string": (C.c_char_p, [C.c_int]),
     "hc_aggr_fwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp]),
+    "hc_last_status": (C.c_int, [vp, i32, vp]),
     "hc_aggr_bwd": (C.c_int, [C.POINTER(AggrArgs), vp, vp, i32, vp, vp, vp, i32, vp]),
     "hc_transpose_scratch_bytes": (i64, [i64, i64]),
     "hc_transpose_block": (C.c_int, [C.POINTER(AggrArgs), i64, vp, vp, vp, vp, vp]),
@@ -100,6 +110,8 @@ _SIGS = {
     "hc_edge_types": (C.c_int, [vp, vp, vp, i64, i32, vp, vp, vp, vp]),
     "hc_rgcn_group_scratch_bytes": (i64, [i64]),
     "hc_rgcn_group": (C.c_int, [vp, vp, vp, i64, i64, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
+    "hc_sample_fixed_scratch_bytes": (i64, [C.POINTER(FixedBatch)]),
+    "hc_sample_fixed": (C.c_int, [vp, vp, vp, i64, vp, C.c_uint64, vp, C.POINTER(FixedBatch), vp, vp]),
     "hc_mix64": (C.c_uint64, [C.c_uint64]),
     "hc_bucket_scratch_bytes": (i64, [i64, i32]),
     "hc_bucket_by_owner": (C.c_int, [vp, vp, i64, i32, vp, vp, vp, vp, vp]),

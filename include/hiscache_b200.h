@@ -49,6 +49,7 @@ extern "C" {
 #define HC_ERR_UNSUPPORTED 5 /* combination of options not implemented        */
 #define HC_ERR_STRUCT 6    /* args->struct_size does not match this build     */
 #define HC_ERR_LIMIT 7     /* more rows than a fixed-capacity entry point takes */
+#define HC_ERR_RANGE 8     /* an index of the block is outside its table (checked build) */
 
 /* score kinds */
 #define HC_SCORE_L2 0 /* sqrt(sum x^2): HistoryCache.update_history, history_cache.py:205 */
@@ -102,6 +103,10 @@ typedef struct hc_aggr_args {
   int32_t h_indexed;       /* 0: read row r (reference layout, row-aligned
                               buffer); 1: read row hmap[r] of the table       */
   int64_t hsize;           /* == feat, or == num_head*feat (per-head rows)   */
+  /* row counts of the two optional tables, used only by the index checks of a
+   * library built with HC_CHECK_BOUNDS (0 = unknown, not checked)            */
+  int64_t h_rows;          /* rows of hbuf                                   */
+  int64_t alt_rows;        /* rows of src_alt                                */
 } hc_aggr_args;
 
 /*
@@ -133,6 +138,24 @@ int hc_aggr_fwd(const hc_aggr_args* a, float* out, void* stream);
 int hc_aggr_bwd(const hc_aggr_args* a, const float* grad_out, float* grad_input,
                 int32_t zero_grad_input, float* grad_history, float* edge_grad,
                 float* row_score, int32_t score_kind, void* stream);
+
+/*
+ * Index checks (a library built with -DHC_CHECK_BOUNDS, libhiscache_b200_checked.so).
+ *
+ * The aggregation kernels trust ptr, idx, src_map and hmap; the reference does too, and a value
+ * outside its table is an out-of-range access on the device (its 32-bit index arithmetic,
+ * history_aggr.cu:34-35, was one way to get there).  In the checked build hc_aggr_fwd and
+ * hc_aggr_bwd first run a validation kernel over the block: ptr must be non-decreasing from a
+ * non-negative start, idx[e] in [0, n_src), src_map[s] in [-1, alt_rows), hmap[r] in
+ * [-1, h_rows) when h_indexed (row-aligned: num_node <= h_rows).  The first violation is
+ * recorded in a status word on the device and the operator's kernels then return without
+ * touching memory: nothing faults, nothing traps, out / gradients are left as they were.
+ *   hc_last_status: waits for `stream`, then out[0] = 0 (clean) or HC_ERR_RANGE, out[1] = which
+ *     array (1 ptr, 2 idx, 3 src_map, 4 hmap), out[2] = position in it, out[3] = the offending
+ *     value; clear != 0 resets the word (a set word blocks every later aggregation call).
+ *     In the regular build it returns -HC_ERR_UNSUPPORTED.
+ */
+int hc_last_status(int64_t out[4], int32_t clear, void* stream);
 
 /*
  * Backward as a gather over the transposed block (mean aggregation, one head,
@@ -616,6 +639,37 @@ int hc_relabel_reset(const int64_t* nodes, int64_t n, int32_t* local_map, void* 
 int64_t hc_relabel_scratch_bytes(int64_t m);
 int hc_relabel(const int64_t* nbr, int64_t m, int32_t* local_map, int64_t n_total,
                int64_t* new_nodes, int64_t* n_new, int64_t* out_idx, void* scratch, void* stream);
+
+/*
+ * A whole sampled batch in a fixed shape, with no device->host read (see the hc_sample_* notes
+ * above for the draws and the layout).  caps[k] = rows of layer k (caps[0] >= number of seeds;
+ * the new nodes of hop h take rows [caps[h], caps[h+1])), fanout[h] draws per node of hop h's
+ * frontier, edge_cap entries of idx.  Outputs, all device: ptr int64 [caps[L-1] + 1], idx int64
+ * [edge_cap] (zero behind the last edge), sub_to_full int64 [caps[L]] and mask uint8 [caps[L]]
+ * (padding rows: node 0, mask 0, no neighbours), counters int64[4] = real nodes, real edges, new
+ * nodes cut because their layer was full, edges cut because idx was full.  A cut node gets no row
+ * and the edges to it become self loops of their destination row; a batch that fits its caps
+ * (counters[2] == counters[3] == 0) equals the one hc_sample_counts / hc_sample_picks / hc_relabel
+ * build for the same seeds and batch number.  seeds: n_seeds distinct nodes.  batch_no: device
+ * int64, read for the draws' seed and advanced by one.  local_map as for hc_relabel; it is restored
+ * before the call returns.  scratch >= hc_sample_fixed_scratch_bytes(b).
+ */
+typedef struct hc_fixed_batch {
+  uint32_t struct_size;
+  int32_t num_hops;          /* L, 1..8 */
+  int32_t fanout[8];
+  int64_t caps[9];
+  int64_t edge_cap;
+  int64_t* ptr;
+  int64_t* idx;
+  int64_t* sub_to_full;
+  uint8_t* mask;
+  int64_t* counters;
+} hc_fixed_batch;
+int64_t hc_sample_fixed_scratch_bytes(const hc_fixed_batch* b);
+int hc_sample_fixed(const int64_t* gptr, const int64_t* gidx, const int64_t* seeds, int64_t n_seeds,
+                    int32_t* local_map, uint64_t seed, int64_t* batch_no, const hc_fixed_batch* b,
+                    void* scratch, void* stream);
 
 /* ---------------------------------------------------------------------------
  * Dense epilogue of a layer: batch norm (training statistics) + ReLU + dropout.

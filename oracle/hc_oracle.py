@@ -372,3 +372,27 @@ def edge_types(ptr, idx, sub_to_full, rows, type_bounds, rel_table):
     dst = np.repeat(np.arange(rows, dtype=np.int64), deg)
     src = idx[:int(ptr[rows])]
     return np.asarray(rel_table, dtype=np.int64).reshape(T, T)[typ[dst], typ[src]]
+
+
+def cache_fill(sorted_indices, host_table, total_num_node, in_c, hidden, limit_bytes, elem_size=4):
+    """HistoryCache.allocate + fill (hiscache/history_cache.py:95-178): buffer length rounded up to a
+    multiple of lcm(in, hidden) elements (:108-109), the hottest overall_feat_num nodes of the
+    degree order cached at the back of the buffer (:131-134,161-166), slots offset by
+    overall_feat_num - N when everything fits (:136-139).  Returns dict(buffer_len,
+    overall_feat_num, overall_embed_num, feat2full, full2embed, feature_rows)."""
+    N = int(total_num_node)
+    lcm = int(np.lcm(in_c, hidden))
+    nbytes = (int(limit_bytes) + elem_size * lcm - 1) // (elem_size * lcm) * (elem_size * lcm)
+    nelem = nbytes // elem_size
+    feat_num, embed_num = nelem // in_c, nelem // hidden
+    order = np.asarray(sorted_indices, dtype=np.int64)
+    cache_indice = order if feat_num > N else order[-feat_num:]
+    new_id = np.arange(len(cache_indice), dtype=np.int64)
+    if feat_num > N:
+        new_id += feat_num - N
+    full2embed = np.full(2 * N + 1, -1, dtype=np.int64)
+    feat2full = cache_indice + N
+    full2embed[feat2full] = new_id
+    return dict(buffer_len=nelem, overall_feat_num=feat_num, overall_embed_num=embed_num,
+                feat2full=feat2full, full2embed=full2embed,
+                feature_rows=np.asarray(host_table)[cache_indice].astype(np.float32))

@@ -14,6 +14,7 @@ inputs and outputs of:
   * HistoryTable.lookup              (hiscache/history_table.py:94-125)
   * HistoryTable.evict_by_staleness / evict_by_both (hiscache/history_table.py:189-254)
   * invalidate()                     (test/test_cache.py:165-174), one used-mask step
+  * HistoryCache.allocate / fill     (hiscache/history_cache.py:95-178), both buffer-size branches
 
 Stand-ins, and what they mean for pinning: `hiscache.count_history_reconstruct` and
 `hiscache_backend.record_history` are CUDA operators, served here by the oracle (so those two
@@ -264,6 +265,54 @@ def gen_invalidate(ref, seed, out):
     np.savez_compressed(out, **rec)
 
 
+def gen_fill(HistoryCache, seed, out):
+    """The reference's own allocate() + fill() (hiscache/history_cache.py:95-178) on CPU tensors,
+    for a buffer smaller than the feature table and for one larger than it (the "cache
+    everything" branch, where slots are offset by overall_feat_num - N, :136-139).  A temporary
+    directory holds the sorted_indices.dat that fill() reads; torch.cuda.mem_get_info is
+    answered with "plenty", so that history.limit decides the size (:104-107)."""
+    import tempfile
+
+    class Cfg(dict):     # the two accesses fill() makes: config["dl"]["dataset"]["path"], config.dl.dataset.name
+        __getattr__ = dict.__getitem__
+    rng = np.random.default_rng(seed)
+    N, in_c, hidden = 300, 6, 4
+    rec = {"N": N, "in_c": in_c, "hidden": hidden}
+    order = rng.permutation(N).astype(np.int64)
+    table = rng.standard_normal((N, in_c)).astype(np.float32)
+    rec["sorted_indices"], rec["host_table"] = order, table
+    real = torch.cuda.mem_get_info
+    torch.cuda.mem_get_info = lambda *a, **k: (1 << 40, 1 << 40)
+    try:
+        with tempfile.TemporaryDirectory() as d:
+            os.makedirs(os.path.join(d, "processed"))
+            order.tofile(os.path.join(d, "processed", "sorted_indices.dat"))
+            for tag, nbytes in (("small", 4800), ("large", 12000)):
+                c = object.__new__(HistoryCache)
+                c.in_channels, c.hidden_channels, c.total_num_node = in_c, hidden, N
+                c.device = torch.device("cpu")
+                c.limit = nbytes / 1024 ** 3
+                c.feat_mode = "history_uvm"
+                c.full2embed = torch.ones(2 * N + 1, dtype=torch.int64) * -1
+                c.uvm = FakeUVM(torch.from_numpy(table))
+                cfg = Cfg(dl=Cfg(dataset=Cfg(path=d, name="synthetic")))
+                c.allocate()
+                c.fill(cfg)
+                n_feat = min(N, c.overall_feat_num)
+                rec[f"{tag}_limit_gb"] = c.limit
+                rec[f"{tag}_overall_feat_num"] = c.overall_feat_num
+                rec[f"{tag}_overall_embed_num"] = c.overall_embed_num
+                rec[f"{tag}_buffer_len"] = c.buffer.shape[0]
+                rec[f"{tag}_feat2full"] = c.feat2full.numpy().copy()
+                rec[f"{tag}_full2embed"] = c.full2embed.numpy().copy()
+                rec[f"{tag}_embed2full_len"] = c.embed2full.shape[0]
+                # only the rows fill() writes are defined (the rest is torch.empty)
+                rec[f"{tag}_feature_rows"] = c.buffer.view(-1, in_c)[-n_feat:].numpy().copy()
+    finally:
+        torch.cuda.mem_get_info = real
+    np.savez_compressed(out, **rec)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("HISCACHE_REFERENCE"), required="HISCACHE_REFERENCE" not in os.environ,
@@ -275,6 +324,7 @@ def main():
     gen_cache_sequence(HistoryCache, 12, 500, 6, 4, 7, os.path.join(HERE, "cache_seq_in6_h4.npz"))
     gen_table(HistoryTable, 21, os.path.join(HERE, "table_lookup_evict.npz"))
     gen_invalidate(args.ref, 31, os.path.join(HERE, "invalidate_steps.npz"))
+    gen_fill(HistoryCache, 41, os.path.join(HERE, "cache_fill.npz"))
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)), "bytes")

@@ -93,7 +93,8 @@ def test_grad_history_row_aligned(backend, oracle, feat):
     assert np.array_equal(hb.grad.cpu().numpy(), want_h)  # hit rows are exact copies
 
 
-@pytest.mark.parametrize("feat,heads", [(32, 1), (100, 1), (128, 1), (16, 4), (33, 3)])
+@pytest.mark.parametrize("feat,heads", [(32, 1), (100, 1), (128, 1), (16, 4), (33, 3), (64, 4), (128, 2), (256, 8),
+                                        (1024, 2), (4, 5)])
 @pytest.mark.parametrize("hist_per_head", [False, True])
 def test_edge_value_variants(backend, oracle, feat, heads, hist_per_head):
     rng = np.random.default_rng(feat * heads + hist_per_head)

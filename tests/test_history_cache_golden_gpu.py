@@ -97,3 +97,57 @@ def test_history_table_replays_reference_lookup_and_eviction():
         assert np.array_equal(t.full_to_history_layered[i].cpu().numpy(), g[f"f2h2_{i}"])
         assert np.array_equal(t.history_to_full_layered[i].cpu().numpy(), g[f"h2f2_{i}"])
         assert np.array_equal(t.checkin_iter[i].cpu().numpy(), g[f"chk2_{i}"])
+
+
+@pytest.mark.parametrize("tag", ["small", "large"])
+def test_allocate_and_fill_replay_the_reference(backend, oracle, tag):
+    """HistoryCache(config) -> allocate() + fill() against the fixture produced by the reference's
+    own allocate()/fill() (hiscache/history_cache.py:95-178): buffer size, slot counts, feat2full,
+    full2embed and the cached feature rows, for a buffer smaller than the feature table and for one
+    larger ("cache everything": slots offset by overall_feat_num - N).  In the second case an
+    admission whose ring runs into the feature region must unmap exactly the nodes whose rows it
+    overwrites."""
+    from hiscache import HistoryCache, HostFeatureStore, make_config
+    d = np.load(os.path.join(GOLDEN, "cache_fill.npz"))
+    N, in_c, hidden = int(d["N"]), int(d["in_c"]), int(d["hidden"])
+    dev = torch.device("cuda:0")
+    uvm = HostFeatureStore(torch.from_numpy(d["host_table"]).pin_memory(), dev)
+    cfg = make_config(feature_dim=in_c, num_classes=3, hidden_dim=hidden, num_layers=3, num_nodes=N,
+                      device="cuda:0", limit=float(d[f"{tag}_limit_gb"]), staleness_thres=100)
+    c = HistoryCache(uvm=uvm, config=cfg, mode="history_uvm", total_num_node=N,
+                     sorted_indices=torch.from_numpy(d["sorted_indices"]), storage_dtype=torch.float32)
+    assert c.buffer.numel() == int(d[f"{tag}_buffer_len"])
+    assert c.overall_feat_num == int(d[f"{tag}_overall_feat_num"])
+    assert c.overall_embed_num == int(d[f"{tag}_overall_embed_num"])
+    assert c.embed2full.shape[0] == int(d[f"{tag}_embed2full_len"])
+    assert np.array_equal(c.feat2full.cpu().numpy(), d[f"{tag}_feat2full"])
+    assert np.array_equal(c.full2embed.cpu().numpy(), d[f"{tag}_full2embed"])
+    n_feat = min(N, c.overall_feat_num)
+    assert np.array_equal(c.buffer.view(-1, in_c)[-n_feat:].cpu().numpy(), d[f"{tag}_feature_rows"])
+    # every cached node is served from its slot
+    ids = torch.arange(N, device=dev)
+    slot = c.full2embed[ids + N]
+    hit = slot != -1
+    assert torch.equal(c.buffer.view(-1, in_c)[slot[hit]], uvm.buffer.to(dev)[ids[hit]])
+    if tag != "large":
+        return
+    # ring admissions that grow into the feature region: overwritten feature rows lose their mapping
+    rng = np.random.default_rng(3)
+    off = c.overall_feat_num - N
+    n_adm = (off * in_c) // hidden + 40           # 40 embedding slots beyond the free prefix
+    prod = torch.from_numpy(rng.standard_normal((n_adm, hidden)).astype(np.float32)).to(dev)
+    s2f = torch.from_numpy(rng.choice(N, size=n_adm, replace=False).astype(np.int64)).to(dev)
+    c.sub2embed = torch.full((n_adm,), -1, dtype=torch.int64, device=dev)
+    import hiscache_backend as hb
+    score = torch.zeros(n_adm, device=dev)
+    thres = torch.ones(1, device=dev)
+    hb.cache_admit(prod, c.buffer, hidden, in_c, c.overall_embed_num, s2f, c.sub2embed, score, thres,
+                   c.full2embed, N, c.embed2full, c.feat2full_by_slot, c._header, reset_header=True)
+    assert c.header == n_adm
+    first_feat_elem = off * in_c
+    overwritten = -(-(n_adm * hidden - first_feat_elem) // in_c)          # feature slots touched
+    slots = torch.arange(off, off + N, device=dev)
+    owners = torch.from_numpy(d["large_feat2full"]).to(dev)               # node + N per feature slot
+    mapped = c.full2embed[owners]
+    assert bool((mapped[:overwritten] == -1).all()), "an overwritten feature row is still mapped"
+    assert torch.equal(mapped[overwritten:], slots[overwritten:]), "an intact feature row lost its mapping"

@@ -150,3 +150,19 @@ def test_aggregation_oracle_vs_torch_autograd(oracle):
     gi, gh, _ = oracle.aggr_bwd(ptr, idx, x.detach().numpy(), num_dst, g.numpy(), hmap=hmap, hsize=F)
     np.testing.assert_allclose(gi, x.grad.numpy(), rtol=1e-5, atol=1e-5)
     np.testing.assert_allclose(gh, hbuf.grad.numpy(), rtol=0, atol=0)
+
+
+@pytest.mark.parametrize("tag", ["small", "large"])
+def test_cache_fill_fixture(oracle, tag):
+    """The oracle's allocate/fill against the fixture made by the reference's own allocate() and
+    fill() (both branches: buffer smaller / larger than the feature table)."""
+    d = np.load(os.path.join(GOLDEN, "cache_fill.npz"))
+    N, in_c, hidden = int(d["N"]), int(d["in_c"]), int(d["hidden"])
+    got = oracle.cache_fill(d["sorted_indices"], d["host_table"], N, in_c, hidden,
+                            int(float(d[f"{tag}_limit_gb"]) * 1024 ** 3))
+    assert got["buffer_len"] == int(d[f"{tag}_buffer_len"])
+    assert got["overall_feat_num"] == int(d[f"{tag}_overall_feat_num"])
+    assert got["overall_embed_num"] == int(d[f"{tag}_overall_embed_num"])
+    assert np.array_equal(got["feat2full"], d[f"{tag}_feat2full"])
+    assert np.array_equal(got["full2embed"], d[f"{tag}_full2embed"])
+    assert np.array_equal(got["feature_rows"], d[f"{tag}_feature_rows"])
