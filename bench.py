@@ -389,10 +389,27 @@ def run_ours(args):
     clocks = sampler.stop()
 
     # ---- the same step with the batch sampled inside it (hc_sample_* / hc_relabel kernels)
-    n_samp = min(K, 30)
-    ms_samp, _, _ = _region(trainer, [None] * n_samp, world, device, barrier,
-                            feed=lambda xs: [trainer.train_step(next(it)) for _ in xs])
+    n_samp = min(max(K, 30), 200)
+    samp_note = "each step also samples its batch on the GPU (sizes read back per hop)"
+    cut = None
+    if use_graph and world == 1:
+        # the device-side fixed-shape sampler is captured in front of the step: one launch per step
+        trainer.enable_sampled_cuda_graph(caps, ecap)
+        samp_feed = lambda xs: [trainer.train_step_sampled() for _ in xs]
+        samp_note = ("sampling (hc_sample_fixed, no host read-back) and the step replayed as ONE CUDA graph; "
+                     "seeds are windows of a shuffled order of the training nodes")
+    elif use_graph:
+        itf = loader.iterate_fixed(1 << 30, caps, ecap, reuse=4)
+        samp_feed = lambda xs: [trainer.train_step(next(itf)) for _ in xs]
+        samp_note = ("each step samples its batch with the device-side fixed-shape sampler (hc_sample_fixed, "
+                     "no host read-back) and replays the captured segments")
+    else:
+        samp_feed = lambda xs: [trainer.train_step(next(it)) for _ in xs]
+    samp_feed([None] * 3)
+    ms_samp, _, _ = _region(trainer, [None] * n_samp, world, device, barrier, feed=samp_feed)
     ms_samp = max_over_ranks(ms_samp)
+    if use_graph and world == 1:
+        cut = [int(v) for v in trainer.sampled.counters.tolist()]
 
     # ---- untimed pass with every library call bracketed by events: per-kernel table
     full = hb.KernelTimer()
@@ -527,8 +544,8 @@ def run_ours(args):
                 "pipelined": "batch k+1 is copied host->device on a second stream during step k; the loss of "
                              "step k is read on the host during step k+1 (hiscache/pipeline.py)",
                 "blocking_value": round(world * K / (statistics.median(blk_ms) * 1e-3), 2)},
-        "with_sampling": {"value": round(world * n_samp / (ms_samp * 1e-3), 2), "unit": "iters/s",
-                          "note": "each step also samples its batch on the GPU (sizes read back per hop)"},
+        "with_sampling": {"value": round(world * n_samp / (ms_samp * 1e-3), 2), "unit": "iters/s", "steps": n_samp,
+                          "note": samp_note, "last_batch_counters_nodes_edges_cutnodes_cutedges": cut},
         "gpu_launches": int(launches),
         "gpu_launches_note": "library kernels per K-step region (PyTorch's own kernels not counted)",
         "host_issue_ms_per_step": round(statistics.median(reg_issue) / K, 4),

@@ -73,6 +73,64 @@ class GraphedStep:
         return self.loss
 
 
+class _SeedWindow:
+    """Distinct seeds for the captured sampler: consecutive windows of a shuffled order of the
+    training nodes, copied into a static buffer before every replay (no size ever reaches the host)."""
+
+    def __init__(self, loader, batch):
+        self.loader = loader
+        n = loader.train_ids.shape[0]
+        self.bs = min(int(batch), n)
+        self.order = loader.train_ids[torch.randperm(n, generator=loader._gen, device=loader.graph.device)]
+        self.cursor = 0
+        self.static = self.order[:self.bs].clone()
+
+    def advance(self):
+        n = self.order.shape[0]
+        if self.cursor + self.bs > n:
+            self.cursor = 0
+        self.static.copy_(self.order[self.cursor:self.cursor + self.bs], non_blocking=True)
+        self.cursor += self.bs
+
+
+class GraphedSampledStep:
+    """Sampling AND the training iteration as one CUDA graph (one GPU): the device-side fixed-shape
+    sampler (hc_sample_fixed) needs no host read-back, so it is captured in front of
+    `trainer._step_body`; a replay draws the next batch and trains on it with a single launch."""
+
+    def __init__(self, trainer, loader, caps, edge_cap, warmup=2):
+        import hiscache_backend as hb
+        self.trainer, self.loader = trainer, loader
+        self.caps, self.edge_cap = list(caps), int(edge_cap)
+        dev = trainer.device
+        self.seeds = _SeedWindow(loader, min(loader.batch_size, self.caps[0]))
+        sampler = loader.sampler
+        self.fixed = None
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            for _ in range(max(1, warmup)):
+                self.seeds.advance()
+                b = sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
+                self.fixed = b.fixed
+                trainer._step_body(b)
+        torch.cuda.current_stream(dev).wait_stream(s)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        self.seeds.advance()
+        before = hb.launch_count()
+        with torch.cuda.graph(self.graph):
+            b = sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
+            self.loss = trainer._step_body(b)
+        self.library_kernels_per_step = hb.launch_count() - before
+        self.counters = self.fixed["counters"]
+
+    def run(self):
+        self.seeds.advance()
+        self.graph.replay()
+        return self.loss
+
+
 class GraphedDataParallelStep:
     """The data-parallel iteration (MultiGpuHistoryTrainer.train_step) as TWO captured segments
     with the collectives issued eagerly between and after them, so that no collective is ever

@@ -80,7 +80,8 @@ class HistoryCache:
         self._cached_embedding = None
         self.distributed_store = False
         self.buffer = None
-        self.feat2full = self.feat2full_by_slot = None
+        self.feat2full = None
+        self._by_slot = None
         self.embed2full = None
         self.overall_feat_num = self.overall_embed_num = 0
         if "history" in self.feat_mode:
@@ -120,7 +121,7 @@ class HistoryCache:
             if os.path.exists(p):
                 sorted_indices = torch.from_numpy(np.fromfile(p, dtype=np.int64))
         if sorted_indices is None or self.uvm is None:
-            self.feat2full = self.feat2full_by_slot = torch.zeros(0, dtype=torch.int64, device=self.device)
+            self.feat2full = torch.zeros(0, dtype=torch.int64, device=self.device)
             return
         indice = sorted_indices.to(self.device)
         cache_indice = indice if self.overall_feat_num > N else indice[-self.overall_feat_num:]
@@ -129,16 +130,7 @@ class HistoryCache:
             new_id += self.overall_feat_num - N
         self.feat2full = cache_indice + N
         self.full2embed[self.feat2full] = new_id
-        # The admission unmaps the feature rows its ring overwrites by SLOT number.  When the buffer
-        # holds every node the slots are offset (new_id above), so feat2full, which the reference
-        # indexes by slot all the same (:226), would name the wrong nodes: the admission gets a
-        # slot-indexed copy whose unused prefix points at the dummy entry 2N.
-        if self.overall_feat_num > N:
-            self.feat2full_by_slot = torch.full((self.overall_feat_num,), 2 * N, dtype=torch.int64,
-                                                device=self.device)
-            self.feat2full_by_slot[self.overall_feat_num - N:] = self.feat2full
-        else:
-            self.feat2full_by_slot = self.feat2full
+
         view = self.buffer.view(-1, self.in_channels)
         first = view.shape[0] - cache_indice.shape[0]
         step = 1 << 20
@@ -146,6 +138,22 @@ class HistoryCache:
             ids = cache_indice[b:b + step]
             rows = hb.load_rows(self.uvm.buffer, None, ids, None, None, out_dtype=self.storage_dtype)
             view[first + b:first + b + ids.shape[0]] = rows
+
+    @property
+    def feat2full_by_slot(self):
+        """feat2full indexed by feature SLOT, which is how the admission unmaps the feature rows its
+        ring overwrites.  When the buffer holds every node the slots are offset by
+        overall_feat_num - N (fill(), :136-139) while the reference indexes feat2full by slot all the
+        same (:226) and so names the wrong nodes; here the admission gets a copy whose unused
+        prefix points at the dummy entry 2N."""
+        f, N = self.feat2full, self.total_num_node
+        if f is None or self.overall_feat_num <= N or f.shape[0] != N:
+            return f
+        if self._by_slot is None or self._by_slot[0] is not f:
+            t = torch.full((self.overall_feat_num,), 2 * N, dtype=torch.int64, device=f.device)
+            t[self.overall_feat_num - N:] = f
+            self._by_slot = (f, t)
+        return self._by_slot[1]
 
     @property
     def embedding_table(self):

@@ -137,6 +137,23 @@ class HistoryTrainer:
         self.graphed = GraphedStep(self, caps, edge_cap, warmup_batches)
         return self.graphed
 
+    def enable_sampled_cuda_graph(self, caps, edge_cap):
+        """Captures sampling + step as one graph (hiscache/graphed.py:GraphedSampledStep);
+        `train_step_sampled()` then draws and trains on the next batch with one launch."""
+        from .graphed import GraphedSampledStep
+        self.model.train()
+        self.sampled = GraphedSampledStep(self, self.loader, caps, edge_cap)
+        return self.sampled
+
+    def train_step_sampled(self):
+        if self.table.staleness_thres > 0 and (self.glb_iter % self.table.staleness_thres) == 0:
+            self.table._header.zero_()
+        loss = self.sampled.run()
+        self.table.glb_iter += 1
+        self.scheduler.step()
+        self.glb_iter += 1
+        return loss
+
     def cxg_train_epoch(self):
         self.model.train()
         tepoch = time.time()

@@ -22,13 +22,15 @@ import torch
 
 class Batch:
     __slots__ = ("ptr", "idx", "sub_to_full", "y", "num_node_in_layer", "num_edge_in_layer", "x",
-                 "edge_type", "typed_num_node_in_layer", "mask")
+                 "edge_type", "typed_num_node_in_layer", "mask", "counters", "fixed")
 
     def __init__(self):
         self.x = None
         self.edge_type = None
         self.typed_num_node_in_layer = None
         self.mask = None
+        self.counters = None
+        self.fixed = None
 
     def to(self, device, non_blocking=True):
         b = Batch()
@@ -107,6 +109,36 @@ class NeighborSampler:
         self.seed = int(seed)
         self.batch_no = 0
         self.local = torch.full((graph.num_nodes,), hb.ABSENT, dtype=torch.int32, device=graph.device)
+        self._batch_no_dev = None     # device-side batch counter of sample_fixed
+
+    @torch.no_grad()
+    def sample_fixed(self, seeds: torch.Tensor, caps, edge_cap, out=None) -> "Batch":
+        """The batch of sample_padded built entirely on the device (hc_sample_fixed): no size is
+        read back, so the call is a fixed sequence of launches that can run on a second stream or
+        inside a captured step.  `seeds` must be distinct.  What does not fit the caps is cut and
+        counted in batch.counters ([2] nodes, [3] edges) instead of being reported to the host.
+        `out`: the dict a previous call returned in batch.fixed (its tensors are overwritten)."""
+        hb, g, dev = self.hb, self.g, self.g.device
+        if self._batch_no_dev is None:
+            self._batch_no_dev = torch.zeros(1, dtype=torch.int64, device=dev)
+        if int(self.batch_no) != getattr(self, "_batch_no_seen", -1):
+            self._batch_no_dev.fill_(int(self.batch_no))     # follow the host-side counter
+        L = len(self.fanouts)
+        o = hb.sample_fixed(g.ptr, g.idx, seeds, self.local, self.seed, self._batch_no_dev, self.fanouts,
+                            list(caps), int(edge_cap), out=out)
+        self.batch_no += 1
+        self._batch_no_seen = int(self.batch_no)
+        b = Batch()
+        b.ptr, b.idx, b.sub_to_full, b.mask = o["ptr"], o["idx"][:int(edge_cap)], o["sub_to_full"], o["mask"]
+        if out is None or "y" not in o:
+            o["y"] = torch.full((caps[0],), -100, dtype=torch.int64, device=dev)
+        o["y"].fill_(-100)
+        o["y"][:seeds.shape[0]] = g.labels[seeds]
+        b.y = o["y"]
+        b.num_node_in_layer = torch.tensor(list(caps), dtype=torch.int64)
+        b.num_edge_in_layer = torch.tensor([int(edge_cap)] * L, dtype=torch.int64)
+        b.counters, b.fixed = o["counters"], o
+        return b
 
     @torch.no_grad()
     def sample_padded(self, seeds: torch.Tensor, caps, edge_cap):
@@ -314,6 +346,26 @@ class Loader:
             if b is None:
                 self.sampler.batch_no = no
                 b = self.sampler.sample(seeds)
+            yield b
+
+    def iterate_fixed(self, n_iters, caps, edge_cap, reuse=2):
+        """Fixed-shape batches built without any device->host read (NeighborSampler.sample_fixed).
+        Seeds are a window of a shuffled order of the training nodes, so they are distinct without
+        a de-duplication (whose size would have to reach the host).  `reuse` output buffers are
+        cycled: a yielded batch stays valid until `reuse` more batches have been drawn."""
+        n = self.train_ids.shape[0]
+        bs = min(self.batch_size, n, int(caps[0]))
+        if getattr(self, "_order", None) is None:
+            self._order = self.train_ids[torch.randperm(n, generator=self._gen, device=self.graph.device)]
+            self._cursor = 0
+        outs = [None] * max(1, int(reuse))
+        for k in range(n_iters):
+            if self._cursor + bs > n:
+                self._cursor = 0
+            seeds = self._order[self._cursor:self._cursor + bs]
+            self._cursor += bs
+            b = self.sampler.sample_fixed(seeds, caps, edge_cap, out=outs[k % len(outs)])
+            outs[k % len(outs)] = b.fixed
             yield b
 
     @property
