@@ -15,17 +15,18 @@
 
 namespace hc {
 
-constexpr int kNormBlock = 256;
+constexpr int kNormBlock = 256;     // apply kernels
+constexpr int kStatsBlock = 1024;   // statistics kernels: one block per SM, 32 warps of loads in flight
 constexpr int kNormMaxPartials = 148;   // blocks of the statistics kernels (one per SM)
 
 struct NormGeom {
   int nvec;   // float4 per row
   int rpi;    // rows per block iteration
 };
-__host__ __device__ inline NormGeom norm_geom(int feat) {
+__host__ __device__ inline NormGeom norm_geom(int feat, int threads) {
   NormGeom g;
   g.nvec = feat / 4;
-  g.rpi = kNormBlock / g.nvec;
+  g.rpi = threads / g.nvec;
   if (g.rpi < 1) g.rpi = 1;
   return g;
 }
@@ -41,18 +42,50 @@ __device__ __forceinline__ unsigned dropout_keep4(uint64_t seed, int64_t step, i
 }
 
 // sum over blocks b of p[b * stride + c], in a fixed order, with eight loads in flight
-__device__ __forceinline__ double column_sum(const float* p, int64_t stride, unsigned nb, int c) {
-  double acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  unsigned b = 0;
-  for (; b + 8 <= nb; b += 8) {
-    float v[8];
+// Sum over blocks b of p[b * stride + c] in a fixed order, by the whole block: thread t takes
+// column t % feat and the blocks b = t / feat, t / feat + parts, ... (eight loads in flight), the
+// `parts` partial sums of a column are then added in part order.  red: shared double [2][parts * feat].
+// Returns the two column sums (p and p + feat) to the threads with t < feat; all threads must call.
+__device__ __forceinline__ void column_sums(const float* p, int feat, unsigned nb, double* red, double* s0,
+                                            double* s1) {
+  const int parts = blockDim.x / feat > 0 ? blockDim.x / feat : 1;
+  const int64_t stride = 2 * (int64_t)feat;
+  for (int base = 0; base < feat; base += blockDim.x) {      // feat > blockDim.x: several rounds
+    const int t = threadIdx.x;
+    const int c = base + (parts > 1 ? t % feat : t);
+    const int part = parts > 1 ? t / feat : 0;
+    double a0 = 0.0, a1 = 0.0;
+    if (c < feat && part < parts) {
+      unsigned b = part;
+      for (; b + 3u * parts < nb; b += 4u * parts) {
+        float v[4], q[4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = __ldcg(p + (int64_t)(b + j) * stride + c);
+        for (int j = 0; j < 4; ++j) {
+          v[j] = __ldcg(p + (int64_t)(b + j * parts) * stride + c);
+          q[j] = __ldcg(p + (int64_t)(b + j * parts) * stride + feat + c);
+        }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] += (double)v[j];
+        for (int j = 0; j < 4; ++j) { a0 += (double)v[j]; a1 += (double)q[j]; }
+      }
+      for (; b < nb; b += parts) {
+        a0 += (double)__ldcg(p + (int64_t)b * stride + c);
+        a1 += (double)__ldcg(p + (int64_t)b * stride + feat + c);
+      }
+      red[part * feat + (c - base)] = a0;
+      red[(parts + part) * feat + (c - base)] = a1;
+    }
+    __syncthreads();
+    if (c < feat && part == 0) {
+      double t0 = 0.0, t1 = 0.0;
+      for (int k = 0; k < parts; ++k) {
+        t0 += red[k * feat + (c - base)];
+        t1 += red[(parts + k) * feat + (c - base)];
+      }
+      s0[base / blockDim.x] = t0;
+      s1[base / blockDim.x] = t1;
+    }
+    __syncthreads();
   }
-  for (int j = 0; b < nb; ++b, ++j) acc[j] += (double)__ldcg(p + (int64_t)b * stride + c);
-  return ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
 }
 
 struct NormArgs {
@@ -71,7 +104,7 @@ struct NormArgs {
 
 // thread layout shared by all four kernels: column vector `cv`, row slot `rs`
 #define HC_NORM_LAYOUT(a)                                  \
-  const NormGeom g = norm_geom((a).feat);                  \
+  const NormGeom g = norm_geom((a).feat, blockDim.x);      \
   const int cv = threadIdx.x % g.nvec;                     \
   const int rs = threadIdx.x / g.nvec;                     \
   const bool active = rs < g.rpi && threadIdx.x < g.nvec * g.rpi;
@@ -79,9 +112,9 @@ struct NormArgs {
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 
 // ---- forward 1: column sums -------------------------------------------------
-__global__ void __launch_bounds__(kNormBlock) norm_stats_kernel(const NormArgs a) {
+__global__ void __launch_bounds__(kStatsBlock) norm_stats_kernel(const NormArgs a) {
   extern __shared__ __align__(16) float sh[];   // [rpi][nvec] float4 x 2
-  __shared__ float sh_cnt[kNormBlock];
+  __shared__ float sh_cnt[kStatsBlock];
   __shared__ bool is_last;
   HC_NORM_LAYOUT(a)
   float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = s;
@@ -131,9 +164,10 @@ __global__ void __launch_bounds__(kNormBlock) norm_stats_kernel(const NormArgs a
   __threadfence();
   double n_valid = 0.0;
   for (unsigned b = 0; b < gridDim.x; ++b) n_valid += (double)__ldcg(a.partial_count + b);
-  for (int c = threadIdx.x; c < a.feat; c += blockDim.x) {
-    const double sum = column_sum(a.partial, 2 * a.feat, gridDim.x, c);
-    const double sq = column_sum(a.partial + a.feat, 2 * a.feat, gridDim.x, c);
+  double cs0[1], cs1[1];
+  column_sums(a.partial, a.feat, gridDim.x, reinterpret_cast<double*>(sh), cs0, cs1);
+  for (int c = threadIdx.x; c < a.feat; c += blockDim.x) {   // feat <= 1024 = blockDim.x: one round
+    const double sum = cs0[0], sq = cs1[0];
     const double nn = n_valid > 0.0 ? n_valid : 1.0;
     const double mean = sum / nn;
     double var = sq / nn - mean * mean;
@@ -209,7 +243,7 @@ struct NormBwd {
   float* sum_dz; float* sum_dzx;          // [feat] scratch handed to the second kernel
 };
 
-__global__ void __launch_bounds__(kNormBlock) norm_bwd_stats_kernel(const NormArgs a, const NormBwd bw) {
+__global__ void __launch_bounds__(kStatsBlock) norm_bwd_stats_kernel(const NormArgs a, const NormBwd bw) {
   extern __shared__ __align__(16) float sh[];
   __shared__ bool is_last;
   HC_NORM_LAYOUT(a)
@@ -260,9 +294,10 @@ __global__ void __launch_bounds__(kNormBlock) norm_bwd_stats_kernel(const NormAr
   __syncthreads();
   if (!is_last) return;
   __threadfence();
+  double cs0[1], cs1[1];
+  column_sums(a.partial, a.feat, gridDim.x, reinterpret_cast<double*>(sh), cs0, cs1);
   for (int c = threadIdx.x; c < a.feat; c += blockDim.x) {
-    const double sum = column_sum(a.partial, 2 * a.feat, gridDim.x, c);
-    const double sq = column_sum(a.partial + a.feat, 2 * a.feat, gridDim.x, c);
+    const double sum = cs0[0], sq = cs1[0];
     bw.sum_dz[c] = (float)sum;
     bw.sum_dzx[c] = (float)sq;
     if (bw.grad_bias) bw.grad_bias[c] = (float)sum;
@@ -336,11 +371,16 @@ static int fill(const hc_norm_args* p, void* scratch, NormArgs* a, NormBwd* bw) 
 }
 
 static void grids(const NormArgs& a, unsigned* stats_blocks, unsigned* apply_blocks, size_t* smem) {
-  const NormGeom g = norm_geom(a.feat);
-  const int64_t iters = ceil_div(a.n > 0 ? a.n : 1, g.rpi);
-  *stats_blocks = (unsigned)(iters < kNormMaxPartials ? iters : kNormMaxPartials);
-  *apply_blocks = (unsigned)(iters < 148 * 8 ? iters : 148 * 8);
-  *smem = (size_t)2 * g.rpi * g.nvec * sizeof(float4);
+  const NormGeom gs = norm_geom(a.feat, kStatsBlock), ga = norm_geom(a.feat, kNormBlock);
+  const int64_t n = a.n > 0 ? a.n : 1;
+  const int64_t si = ceil_div(n, gs.rpi), ai = ceil_div(n, ga.rpi);
+  *stats_blocks = (unsigned)(si < kNormMaxPartials ? si : kNormMaxPartials);
+  *apply_blocks = (unsigned)(ai < 148 * 8 ? ai : 148 * 8);
+  // block partial sums (float4 x 2 per row slot), reused by the last block for the column sums
+  size_t need = (size_t)2 * gs.rpi * gs.nvec * sizeof(float4);
+  const int parts = kStatsBlock / a.feat > 0 ? kStatsBlock / a.feat : 1;
+  const size_t fin = (size_t)2 * parts * a.feat * sizeof(double);
+  *smem = need > fin ? need : fin;
 }
 
 }  // namespace hc
@@ -363,7 +403,7 @@ extern "C" int hc_norm_act_fwd(const hc_norm_args* p, float* y, void* scratch, v
   size_t smem;
   grids(a, &sb, &ab, &smem);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  norm_stats_kernel<<<sb, kNormBlock, smem, st>>>(a);
+  norm_stats_kernel<<<sb, kStatsBlock, smem, st>>>(a);
   norm_apply_kernel<<<ab, kNormBlock, 0, st>>>(a, y);
   HC_LAUNCH_OK();
   return 0;
@@ -390,7 +430,7 @@ extern "C" int hc_norm_act_bwd(const hc_norm_args* p, const float* grad_y, float
   unsigned sb, ab;
   size_t smem;
   grids(a, &sb, &ab, &smem);
-  norm_bwd_stats_kernel<<<sb, kNormBlock, smem, st>>>(a, bw);
+  norm_bwd_stats_kernel<<<sb, kStatsBlock, smem, st>>>(a, bw);
   norm_bwd_apply_kernel<<<ab, kNormBlock, 0, st>>>(a, bw, grad_x);
   HC_LAUNCH_OK();
   return 0;

@@ -134,9 +134,24 @@ def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0", sor
     return ms, n * feat * es * 2 + 8 * n
 
 
+def bench_norm(n, feat, reps, p=0.5, dev="cuda:0"):
+    """Fused batch norm + ReLU + dropout, forward and backward.  bytes: forward reads x twice and
+    writes y; backward reads x and grad_y twice and writes grad_x (all fp32 [n, feat])."""
+    x = torch.randn(n, feat, device=dev)
+    w, b = torch.ones(feat, device=dev), torch.zeros(feat, device=dev)
+    rm, rv = torch.zeros(feat, device=dev), torch.ones(feat, device=dev)
+    state = torch.zeros(4, dtype=torch.int64, device=dev)
+    gy = torch.randn(n, feat, device=dev)
+    xr = x.clone().requires_grad_(True)
+    ms_f = time_launches(lambda: hb.norm_act(x, w, b, state, running_mean=rm, running_var=rv, p=p), reps)
+    y = hb.norm_act(xr, w, b, state, running_mean=rm, running_var=rv, p=p)
+    ms_b = time_launches(lambda: torch.autograd.grad(y, xr, gy, retain_graph=True), reps)
+    return ms_f, 3 * n * feat * 4, ms_b, 5 * n * feat * 4
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "bwd_gather", "load", "fwd_bwd"])
+    ap.add_argument("--op", default="fwd", choices=["fwd", "bwd", "bwd_gather", "load", "fwd_bwd", "norm"])
     ap.add_argument("--dst", type=int, default=2_000_000)
     ap.add_argument("--deg", type=int, default=10)
     ap.add_argument("--src", type=int, default=16_000_000)
@@ -161,6 +176,10 @@ def main():
     elif args.op == "bwd_gather":
         ms, byts, ms_t = bench_bwd_gather(args.dst, args.deg, args.src, args.feat, args.reps)
         extra = {"transpose_ms": round(ms_t, 4)}
+    elif args.op == "norm":
+        ms, byts, ms_b, b_b = bench_norm(args.dst, args.feat, args.reps)
+        extra = {"fwd_ms": round(ms, 4), "fwd_GBps": round(byts / ms / 1e6, 1), "bwd_ms": round(ms_b, 4),
+                 "bwd_GBps": round(b_b / ms_b / 1e6, 1), "rows": args.dst}
     elif args.op == "fwd_bwd":
         # forward + backward of one block as a training step runs them; the transposition is paid
         # once per batch and serves the backward of all `layers` convs that share its CSR

@@ -134,18 +134,20 @@ def test_allocate_and_fill_replay_the_reference(backend, oracle, tag):
     # ring admissions that grow into the feature region: overwritten feature rows lose their mapping
     rng = np.random.default_rng(3)
     off = c.overall_feat_num - N
-    n_adm = (off * in_c) // hidden + 40           # 40 embedding slots beyond the free prefix
+    h0 = (off * in_c) // hidden - 20              # the ring stands 20 slots before the feature region
+    n_adm = 60                                    # and grows 40 slots into it
     prod = torch.from_numpy(rng.standard_normal((n_adm, hidden)).astype(np.float32)).to(dev)
     s2f = torch.from_numpy(rng.choice(N, size=n_adm, replace=False).astype(np.int64)).to(dev)
     c.sub2embed = torch.full((n_adm,), -1, dtype=torch.int64, device=dev)
+    c._header.fill_(h0)
     import hiscache_backend as hb
     score = torch.zeros(n_adm, device=dev)
     thres = torch.ones(1, device=dev)
     hb.cache_admit(prod, c.buffer, hidden, in_c, c.overall_embed_num, s2f, c.sub2embed, score, thres,
-                   c.full2embed, N, c.embed2full, c.feat2full_by_slot, c._header, reset_header=True)
-    assert c.header == n_adm
+                   c.full2embed, N, c.embed2full, c.feat2full_by_slot, c._header, reset_header=False)
+    assert c.header == h0 + n_adm
     first_feat_elem = off * in_c
-    overwritten = -(-(n_adm * hidden - first_feat_elem) // in_c)          # feature slots touched
+    overwritten = -(-((h0 + n_adm) * hidden - first_feat_elem) // in_c)   # feature slots touched
     slots = torch.arange(off, off + N, device=dev)
     owners = torch.from_numpy(d["large_feat2full"]).to(dev)               # node + N per feature slot
     mapped = c.full2embed[owners]

@@ -43,7 +43,7 @@ def test_caps_that_are_too_small_cut_safely(backend):
     fanouts = [15, 10, 5]
     s = NeighborSampler(g, fanouts, seed=2)
     seeds = g.train_ids[:256]
-    caps, ecap = [256, 600, 1500, 2500], 6000          # far below what the batch needs
+    caps, ecap = [256, 600, 1500, 2500], 2500          # far below what the batch needs
     b = s.sample_fixed(seeds, caps, ecap)
     c = b.counters.tolist()
     assert c[2] > 0 and c[3] > 0, c

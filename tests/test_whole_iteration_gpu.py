@@ -94,7 +94,8 @@ def test_train_step_equals_cpu_restatement(backend, oracle, shape, monkeypatch):
         # ---- within tolerance: loss, produced embedding, admission scores
         worst["loss"] = max(worst["loss"], abs(loss_gpu - loss_cpu) / abs(loss_cpu))
         np.testing.assert_allclose(loss_gpu, loss_cpu, rtol=1e-4)
-        np.testing.assert_allclose(kept["his"], L["his"], rtol=1e-4, atol=1e-5)
+        # a mean of post-activation rows that went through two layers of fp32 GEMMs and batch norm
+        np.testing.assert_allclose(kept["his"], L["his"], rtol=1e-4, atol=1e-4)
         # a score is the norm of a gradient row that went through the dense layers' fp32 GEMMs: its
         # absolute error is a few 1e-7 of the largest scores, whatever its own size
         np.testing.assert_allclose(kept["score"], L["score"], rtol=1e-4, atol=1e-3 * float(np.median(L["score"])))
