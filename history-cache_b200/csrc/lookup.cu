@@ -6,7 +6,6 @@
 // masked host read followed by two more full-width passes; here one kernel
 // decides per row between the host-resident table, the raw-feature cache in
 // HBM and zeros, and writes the row once.
-#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -407,11 +406,7 @@ extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t 
   if (a.cache_mode < worst) worst = a.cache_mode;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int row_bytes = feat * dtype_size(x_dtype);
-  static const bool bulk_enabled = [] {
-    const char* e = getenv("HC_LOAD_BULK");
-    return e == nullptr || e[0] != '0';
-  }();
-  if (bulk_enabled && worst == 2 && x_stride == feat && row_bytes <= 512 && n >= kBulkTile) {
+  if (worst == 2 && x_stride == feat && row_bytes <= 512 && n >= kBulkTile) {
     const int64_t tiles = ceil_div(n, kBulkTile);
     const size_t smem = (size_t)kBulkWarps * 2 * kBulkTile * row_bytes;
     int64_t blocks = ceil_div(tiles, kBulkWarps);

@@ -208,7 +208,7 @@ class _AggrFunction(torch.autograd.Function):
         can_gather = (need_in and edge_value is None and inp.dim() == 2 and inp.shape[1] % 4 == 0
                       and inp.shape[1] <= 1024)
         if can_gather and (DETERMINISTIC_BWD or (inp.shape[1] >= GATHER_MIN_FEAT and
-                                                 idx_t.numel() * inp.shape[1] * 4 >= GATHER_MIN_BYTES)):
+                                                 inp.shape[0] * inp.shape[1] * 4 >= GATHER_MIN_BYTES)):
             pa = PreparedAggr(a, None, dev, _tag("", inp))
             shared = shared_transpose(ptr_t, idx_t)
             if shared is not None and shared[0].shape[0] - 1 >= inp.shape[0]:
@@ -306,12 +306,13 @@ def run_aggr_bwd(p: PreparedAggr, grad_out, grad_input=None, grad_history=None, 
     _called()
 
 
-# blocks whose scatter would move at least this many bytes take the transposed-gather
-# backward (the scatter is faster below: fewer launches, and its lines stay in L2)
-GATHER_MIN_BYTES = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_BYTES", 64 << 20))
-# measured on B200 (1 M x 10 edges, transpose included): 1 KB gradient rows 3.0 ms against
-# 4.2 ms for the scatter; 512-byte rows 5.3 ms against 4.3 ms, so narrow rows keep the scatter
-GATHER_MIN_FEAT = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_FEAT", 256))
+# The scatter is bound by read-modify-write DRAM traffic once grad_input no longer fits the 126 MB
+# L2; below that its lines stay in L2 and it needs fewer launches.  Blocks whose grad_input is at
+# least this large take the transposed-gather backward.
+GATHER_MIN_BYTES = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_BYTES", 128 << 20))
+# measured on B200 (1 M x 10 edges into 4 M rows, transposition included): 512-byte gradient rows
+# 2.12 ms against 2.14 ms for the scatter, 1 KB rows 3.25 ms against 4.14 ms
+GATHER_MIN_FEAT = int(os.environ.get("HISCACHE_BWD_GATHER_MIN_FEAT", 128))
 
 
 # True: every aggregation backward that can takes the transposed gather, whose sums have a fixed
