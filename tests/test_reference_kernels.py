@@ -144,3 +144,55 @@ def test_reference_record_history_same_up_to_slot_order(ref, oracle):
     ids = np.nonzero(f2h != -1)[0]
     assert np.array_equal(r_buf[r_f2h[ids]], buf[f2h[ids]])   # same rows stored per node
     assert np.array_equal(r_h2f[r_f2h[ids]], ids)
+
+
+@pytest.mark.parametrize("feat", [128, 256])
+def test_large_block_agrees_with_reference_kernels(ref, backend, feat, capsys):
+    """A block larger than L2 (500 K destination rows x 10 neighbours from 4 M fp32 source rows,
+    25 % history rows): the library's forward and both of its backward forms against the reference's
+    own kernels on the same inputs.  The CUDA-event times of the calls are printed (run with -s);
+    nothing is asserted about them."""
+    dev = "cuda"
+    n_dst, deg, n_src = 500_000, 10, 4_000_000
+    g = torch.Generator(device=dev)
+    g.manual_seed(0)
+    x = torch.randn(n_src, feat, device=dev)
+    idx = torch.randint(0, n_src, (n_dst * deg,), generator=g, device=dev)
+    ptr = torch.arange(0, n_dst * deg + 1, deg, device=dev)
+    hmap = torch.where(torch.rand(n_dst, device=dev) < 0.25, torch.arange(n_dst, device=dev), -1)
+    hbuf = torch.randn(n_dst, feat, device=dev)
+    go = torch.randn(n_dst, feat, device=dev)
+
+    def timed(fn, reps=3):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return out, e0.elapsed_time(e1) / reps
+
+    with torch.no_grad():
+        want, t_ref_f = timed(lambda: ref.aggr_forward_history(x, ptr, idx, hmap, hbuf, feat, n_dst))
+        p = backend.prepare_aggr(x, ptr, idx, n_dst, history_map=hmap, history_buffer=hbuf)
+        out = torch.empty(n_dst, feat, device=dev)
+        _, t_new_f = timed(lambda: backend.run_aggr_fwd(p, out))
+    # mean of 10 N(0,1) rows: |terms| sum to about 8 per element; fast-math division in the reference
+    torch.testing.assert_close(out, want, rtol=1e-5, atol=12 * 2.0 ** -23 * 8.0)
+    xr = x.clone().requires_grad_(True)
+    o = ref.aggr_forward_history(xr, ptr, idx, hmap, hbuf, feat, n_dst)
+    (g_ref,), t_ref_b = timed(lambda: torch.autograd.grad(o, xr, go, retain_graph=True))
+    gi = torch.empty_like(x)
+    _, t_new_b = timed(lambda: backend.run_aggr_bwd(p, go, gi))
+    bound = 64 * 2.0 ** -23 * 8.0      # at most a few tens of terms of magnitude ~0.1 each per source row
+    torch.testing.assert_close(gi, g_ref, rtol=1e-5, atol=bound)
+    (t_ptr, t_dst, t_w), t_tr = timed(lambda: backend.transpose_block(p, idx.numel()))
+    gg = torch.empty_like(x)
+    _, t_new_g = timed(lambda: backend.run_aggr_bwd_gather(p, t_ptr, t_dst, t_w, go, gg))
+    torch.testing.assert_close(gg, g_ref, rtol=1e-5, atol=bound)
+    with capsys.disabled():
+        print(f"\nF={feat}: reference fwd {t_ref_f:.3f} ms, library fwd {t_new_f:.3f} ms; reference bwd "
+              f"{t_ref_b:.3f} ms, library scatter {t_new_b:.3f} ms, library gather {t_new_g:.3f} ms "
+              f"(+ transposition {t_tr:.3f} ms)")
