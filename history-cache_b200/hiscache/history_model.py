@@ -15,6 +15,11 @@ import hiscache_backend as hb
 from .util import cfg_get
 
 
+import os
+
+FUSE_ROOT_PRODUCT = os.environ.get("HISCACHE_FUSE_ROOT_PRODUCT", "1") not in ("", "0")
+
+
 class MaskedBatchNorm1d(torch.nn.BatchNorm1d):
     """BatchNorm1d whose batch statistics ignore padding rows.  With mask=None it is the
     stock module (same parameters and buffers, so state dicts are interchangeable); with a
@@ -110,10 +115,18 @@ class MySageConvHistory(torch.nn.Module):
         his = out
         if self.need_grad and self.training and history_size > 0:
             his.retain_grad()
-        out = self.lin_l(out)
         if self.root_weight:
             root = x[:num_node] if num_node != 0 else x
-            out = out + self.lin_r(root if root.dtype == out.dtype else root.to(out.dtype))
+            root = root if root.dtype == out.dtype else root.to(out.dtype)
+            if FUSE_ROOT_PRODUCT:
+                # lin_l(aggr) + lin_r(root) as ONE product over [aggr | root]: half the GEMM launches of
+                # the layer in forward and backward (their shapes are small and launch-bound)
+                w = torch.cat([self.lin_l.weight, self.lin_r.weight], dim=1)
+                out = F.linear(torch.cat([out, root], dim=1), w, self.lin_l.bias)
+            else:
+                out = self.lin_l(out) + self.lin_r(root)
+        else:
+            out = self.lin_l(out)
         return out, his
 
 
