@@ -16,9 +16,11 @@ ROOT = os.path.dirname(HERE)
 STEPS = 10
 
 
-def _train_worker(rank, world, port, exchange, q):
+def _train_worker(rank, world, port, exchange, deterministic, q):
     sys.path.insert(0, os.path.join(ROOT, "history-cache_b200"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    if deterministic:      # every aggregation backward takes the fixed-order gather
+        os.environ["HISCACHE_DETERMINISTIC_BWD"] = "1"
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
@@ -67,10 +69,10 @@ def _train_worker(rank, world, port, exchange, q):
     dist.destroy_process_group()
 
 
-def _run(world, exchange, port):
+def _run(world, exchange, port, deterministic=False):
     sys.path.insert(0, HERE)
     from _mp import run_ranks
-    return run_ranks(_train_worker, world, (port, exchange), timeout=300)
+    return run_ranks(_train_worker, world, (port, exchange, deterministic), timeout=300)
 
 
 def _check(runs):
@@ -105,3 +107,22 @@ def test_two_ranks_both_exchanges_agree():
         sa, sb = set(a["owned"].tolist()), set(b["owned"].tolist())
         assert len(sa & sb) / max(1, len(sa | sb)) > 0.97
         assert np.allclose(a["losses"], b["losses"], rtol=5e-3, atol=5e-3)
+
+
+def test_two_ranks_reproducible_step_makes_both_exchanges_identical():
+    """With the fixed-order backward (HISCACHE_DETERMINISTIC_BWD=1) nothing in a step depends on
+    the order of floating-point atomics any more, so the two forms of the exchange, which implement
+    one logical table, must give the SAME run: identical admitted sets on every owner, identical
+    hit counts, identical losses and parameters, bit for bit."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    base = 30300 + os.getpid() % 50
+    peer = _run(2, "peer", base, deterministic=True)
+    nccl = _run(2, "nccl", base + 60, deterministic=True)
+    _check(peer)
+    _check(nccl)
+    for a, b in zip(peer, nccl):
+        assert a["hits"] == b["hits"]
+        assert set(a["owned"].tolist()) == set(b["owned"].tolist())
+        assert a["losses"] == b["losses"]
+        assert np.array_equal(a["params"], b["params"])
