@@ -740,7 +740,7 @@ def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, see
     return out
 
 
-def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cpu_steps=2, seed=0):
+def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cpu_steps=2, seed=0, graph=True):
     """configs[4] at a stated reduced size: 2-layer RGCN (hidden 1024, 153 classes, 5 relations) on a
     heterogeneous graph with three node types in the proportions 121 M : 122 M : 26 K, Zipf 2.0
     degrees, fp16 dim-768 features in pinned host memory, batch 1 000, fan-outs 25/15.  The full
@@ -763,15 +763,33 @@ def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cp
     loader = Loader(graph, fan, 1000, "history_uvm", seed=seed, iters_per_epoch=1 << 30)
     tr = HistoryTrainer(cfg, graph=graph, uvm=uvm, loader=loader, storage_dtype=torch.float16, seed=seed)
     tr.model.train()
-    it = loader.train_loader
+    caps = ecap = None
+    if graph:       # the step replayed as one CUDA graph over fixed-shape batches, as for configs[2]
+        caps, ecap = loader.calibrate(32, slack=1.0, align=128)
+        it = loader.iterate_padded(1 << 30, caps, ecap)
+    else:
+        it = loader.train_loader
     batches = [next(it) for _ in range(warmup + steps)]
+    if graph:
+        n_eager = min(6, warmup)
+        for b in batches[:n_eager]:
+            tr.train_step(b)
+        fit = [b for b in batches if b.mask is not None][:2]
+        if len(fit) == 2:
+            tr.enable_cuda_graph(caps, ecap, fit)
+        else:
+            graph = False
     tr.table.load_stats.zero_()
     ms, issue = _time_steps(tr.train_step, batches, warmup)
     stats = tr.table.load_stats.tolist()
     host_rows = stats[0] / (steps + warmup)
     ms_e2e, h2d = _e2e_steps(tr, [b.pin() for b in batches], warmup)
     n_prof = min(steps, 10)
+    if tr.graphed is not None:
+        tr.graphed.enabled = False      # eager pass: every library call bracketed by events
     kt = _kernel_table(tr, batches[warmup:], n_prof)
+    if tr.graphed is not None:
+        tr.graphed.enabled = True
     peak, src = _peak()
     link = measure_h2d_peak(device)
     roofs = []
@@ -782,6 +800,8 @@ def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cp
         # the (relation, destination) sums are written once
         nn = [int(v) for v in batches[-1].num_node_in_layer]
         ne = [int(v) for v in batches[-1].num_edge_in_layer]
+        if batches[-1].mask is not None:      # fixed shape: the real edge count is in ptr
+            ne[1] = int(batches[-1].ptr[nn[1]])
         byts = ne[1] * feat * 2 + R * nn[1] * feat * 4 + 8 * (R * nn[1] + 1 + ne[1]) + 4 * ne[1]
         roofs.append({"bound": "hbm", "kernel": "aggr_fwd_vec_kernel<half, edge weights> over the relation-"
                                                 "segmented block of the first conv",
@@ -802,6 +822,7 @@ def bench_config5(device, steps=30, warmup=12, nodes=4_000_000, cache_gb=1.0, cp
            "warmup": warmup, "host_issue_ms_per_step": round(issue, 4),
            "e2e": {"value": round(1e3 / ms_e2e, 2), "unit": "iters/s", "h2d_bytes_per_step": int(h2d),
                    "d2h_bytes_per_step": 4},
+           "cuda_graph": {"caps": caps, "edge_cap": ecap} if graph else None,
            "nodes": nodes, "node_types": [bounds[1], bounds[2] - bounds[1], bounds[3] - bounds[2]],
            "edges": graph.num_edges, "feature_cache_gb": cache_gb, "prep_s": round(prep_s, 1),
            "full_size": "121 M / 122 M / 26 K nodes, ~1.7 B edges, 373 GB of features: cannot be held",

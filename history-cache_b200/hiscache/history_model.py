@@ -377,7 +377,8 @@ class HistoryRGCN(torch.nn.Module):
                 self.table.produced_embedding.retain_grad()
             else:
                 x, his = conv(x, batch.ptr, batch.idx, et, None, None, None, used, 0, n)
-            x = self.bns[i].act(x, None, self.dropout)
+            mask = getattr(batch, "mask", None)   # fixed-shape batches carry a row mask
+            x = self.bns[i].act(x, None if mask is None else mask[:n], self.dropout)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, etypes[:int(ne[0])], None, None, None,
                                 um[-2] if um is not None else None, 0, int(nn[0]))
         return x.log_softmax(dim=-1)
