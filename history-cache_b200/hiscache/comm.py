@@ -34,7 +34,22 @@ def _dist_all2all(send, group=None, recv=None):
     tail = tuple(send[0].shape[1:])
     if recv is None:
         recv = [torch.empty((rc[i],) + tail, dtype=send[0].dtype, device=dev) for i in range(world)]
-    dist.all_to_all(recv, [t.contiguous() for t in send], group=group)
+    for i in range(world):      # a wrong buffer would otherwise leave the ranks waiting on each other
+        if recv[i].shape[0] != rc[i]:
+            raise ValueError(f"rank {i} sends {rc[i]} rows into a buffer of {recv[i].shape[0]}")
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all(recv, [t.contiguous() for t in send], group=group)
+        return recv
+    # backends without the list form (gloo): one split-size exchange over concatenated pieces
+    width = 1
+    for d in tail:
+        width *= d
+    sc = counts.tolist()
+    flat = torch.cat([t.reshape(t.shape[0], width) for t in send]) if sum(sc) else send[0].new_empty((0, width))
+    out = flat.new_empty((sum(rc), width))
+    dist.all_to_all_single(out, flat, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    for i, piece in enumerate(out.split(rc)):
+        recv[i].copy_(piece.view(recv[i].shape))
     return recv
 
 

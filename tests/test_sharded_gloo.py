@@ -167,3 +167,45 @@ def test_every_rank_runs_the_same_number_of_iterations():
         counts = {l.iters_per_epoch for l in loaders}
         assert len(counts) == 1, f"world {world}: {counts}"
         assert sum(1 for _ in loaders[-1].train_loader) == loaders[0].iters_per_epoch
+
+
+def _ragged_worker(rank, world, port, q):
+    """all2all in the one-process-per-GPU convention with a different number of rows for every
+    (source, destination) pair, empty pieces included (hiscache/comm.py:5-44 moves whatever sizes
+    tensor_2d[src][dst] has)."""
+    for p in (os.path.join(ROOT, "history-cache_b200"), HERE):
+        sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+
+    def body():
+        from hiscache.comm import all2allnaive, all2allnaive_prealloc
+        rows = lambda s, d: (3 * s + 5 * d) % 4          # 0 for some pairs
+        send = [torch.full((rows(rank, d), 3), float(10 * rank + d)) for d in range(world)]
+        got = all2allnaive(send)
+        for s in range(world):
+            assert got[s].shape == (rows(s, rank), 3), (s, got[s].shape)
+            assert bool((got[s] == 10 * s + rank).all())
+        recv = [torch.empty((rows(s, rank), 3)) for s in range(world)]
+        out = all2allnaive_prealloc(send, recv)
+        assert all(torch.equal(a, b) for a, b in zip(out, got))
+        # a receive buffer of the wrong length is refused on every rank before anything moves
+        bad = [torch.empty((rows(s, rank) + 1, 3)) for s in range(world)]
+        try:
+            all2allnaive_prealloc(send, bad)
+        except ValueError:
+            pass
+        else:
+            raise AssertionError("a mismatched receive buffer was accepted")
+        return sum(t.shape[0] for t in got)
+
+    from _mp import report_and_exit
+    report_and_exit(q, rank, body)
+    dist.destroy_process_group()
+
+
+def test_all2all_with_mismatched_split_sizes():
+    from _mp import run_ranks
+    world = 3
+    res = run_ranks(_ragged_worker, world, (29400 + os.getpid() % 200,), timeout=240)
+    assert sum(res) == sum((3 * s + 5 * d) % 4 for s in range(world) for d in range(world))
