@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--graph", default=os.environ.get("HC_BENCH_GRAPH", "auto"), choices=["auto", "on", "off"],
                     help="replay the step from CUDA graphs over fixed-shape (padded) batches: one graph on "
                          "one GPU, two captured segments around the eager gradient all-reduce on several")
+    ap.add_argument("--look-ahead", default="on", choices=["on", "off"],
+                    help="the captured step fetches the next batch's host feature rows beside its compute")
     ap.add_argument("--graph-slack", type=float, default=1.0,
                     help="fixed shape = this factor x the largest layer sizes of --graph-calibrate probe batches")
     ap.add_argument("--graph-calibrate", type=int, default=64)
@@ -192,16 +194,20 @@ def conv0_bytes(batch, feat, elem):
     return e * feat * elem + n_d * feat * 4 + 8 * (n_d + 1 + e)
 
 
-def _region(trainer, batches, world, device, barrier, feed=None):
+def _region(trainer, batches, world, device, barrier, feed=None, after=None):
     """Times one region of len(batches) steps: barrier + synchronize on both sides, CUDA events on
-    the training stream.  Returns (device ms, host issue ms, losses or None)."""
+    the training stream.  Returns (device ms, host issue ms, losses or None).  Every step is told
+    which batch follows it (the captured step fetches that batch's host rows beside its own
+    compute); `after` is the first batch of the next region, so that a region is K steps of the
+    running pipeline: its last step fetches for the next region what the previous region's last
+    step fetched for this one."""
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
     if feed is None:
-        for b in batches:
-            trainer.train_step(b)
+        for i, b in enumerate(batches):
+            trainer.train_step(b, batches[i + 1] if i + 1 < len(batches) else after)
         losses = None
     else:
         losses = feed(batches)
@@ -335,13 +341,25 @@ def run_ours(args):
     # ---- warm-up (also brings the history table to steady state: >= 2 x staleness).  With the
     # captured step the first warm-up steps run eagerly (the capture needs an active history).
     n_eager_warm = min(args.warmup, max(2, args.staleness // 2)) if use_graph else args.warmup
+    plain_ms, look_ahead = [], False
     for b in batches[:n_eager_warm]:
         trainer.train_step(b)
     if use_graph:
         warm = [b for b in batches if b.mask is not None][:2]
         if len(warm) < 2:      # every rank must run the same number of warm-up steps (collectives)
             raise RuntimeError("no batch fits the fixed shape; raise --graph-slack")
-        trainer.enable_cuda_graph(caps, ecap, warm)
+        look_ahead = args.look_ahead == "on"
+        if look_ahead:
+            # first the captured step WITHOUT the look-ahead branch, timed on a few regions for
+            # comparison; the capture that everything below measures replaces it
+            trainer.enable_cuda_graph(caps, ecap, warm, look_ahead=False)
+            for b in batches[n_eager_warm:args.warmup]:
+                trainer.train_step(b)
+            for r in range(min(repeats, 5)):
+                ms_r, _, _ = _region(trainer, batches[args.warmup + r * K: args.warmup + (r + 1) * K], world,
+                                     device, barrier)
+                plain_ms.append(max_over_ranks(ms_r))
+        trainer.enable_cuda_graph(caps, ecap, warm, look_ahead=look_ahead)
         for b in batches[n_eager_warm:args.warmup]:
             trainer.train_step(b)
     barrier()
@@ -352,10 +370,12 @@ def run_ours(args):
     sampler = ClockSampler(physical_gpu_index(local_rank))
     sampler.start()
     trainer.table.load_stats.zero_()
+    trainer.table.stage_stats.zero_()
     l0 = hb.launch_count()
     reg_ms, reg_issue = [], []
     for r in range(repeats):
-        ms_r, issue_r, _ = _region(trainer, timed[r], world, device, barrier)
+        ms_r, issue_r, _ = _region(trainer, timed[r], world, device, barrier,
+                                   after=timed[r + 1][0] if r + 1 < repeats else None)
         reg_ms.append(max_over_ranks(ms_r))
         reg_issue.append(max_over_ranks(issue_r))
     ms = statistics.median(reg_ms)
@@ -364,6 +384,7 @@ def run_ours(args):
         launches += trainer.graphed.library_kernels_per_step * sum(
             1 for b in timed[0] if trainer.graphed.fits(b))
     stats = trainer.table.load_stats.tolist()
+    staged = trainer.table.stage_stats.tolist()
 
     # ---- timed: e2e.  Every step copies its batch structures from page-locked host memory and
     # reads its loss back to the host; both are pipelined (hiscache/pipeline.py): the copy of batch
@@ -372,14 +393,16 @@ def run_ours(args):
     pipe = HostBatchPipeline(trainer, host_batches)
     e2e_ms, losses_all = [], []
     for r in range(repeats):
-        ms_r, _, losses = _region(trainer, timed_host[r], world, device, barrier, feed=pipe.run)
+        nxt = timed_host[r + 1][0] if r + 1 < repeats else None
+        ms_r, _, losses = _region(trainer, timed_host[r], world, device, barrier,
+                                  feed=lambda hbs, nxt=nxt: pipe.run(hbs, after=nxt))
         e2e_ms.append(max_over_ranks(ms_r))
         losses_all += losses
     ms_e2e = statistics.median(e2e_ms)
     # the same with the copy and the read-back inline (blocking), for comparison
     def blocking(hbs):
         out = []
-        for hbatch in hbs:
+        for hbatch in hbs:      # no look-ahead here: the next batch is not on the device yet
             out.append(float(trainer.train_step(hbatch.to(device, non_blocking=True)).item()))
         return out
     blk_ms = []
@@ -400,7 +423,12 @@ def run_ours(args):
                      "seeds are windows of a shuffled order of the training nodes")
     elif use_graph:
         itf = loader.iterate_fixed(1 << 30, caps, ecap, reuse=4)
-        samp_feed = lambda xs: [trainer.train_step(next(itf)) for _ in xs]
+        drawn = [next(itf)]
+
+        def samp_feed(xs):
+            for _ in xs:
+                drawn.append(next(itf))
+                trainer.train_step(drawn.pop(0), drawn[0])
         samp_note = ("each step samples its batch with the device-side fixed-shape sampler (hc_sample_fixed, "
                      "no host read-back) and replays the captured segments")
     else:
@@ -443,7 +471,8 @@ def run_ours(args):
 
     # host-link bytes per step: rows read from host memory by the load kernel
     steps_value = K * repeats
-    host_rows_per_step = stats[0] / steps_value
+    # rows of the host table a step needs: read in the step, or taken from what was fetched ahead
+    host_rows_per_step = (stats[0] + stats[2]) / steps_value
     feat_bytes = args.feat * 2
 
     peaks = {}
@@ -546,6 +575,18 @@ def run_ours(args):
                 "blocking_value": round(world * K / (statistics.median(blk_ms) * 1e-3), 2)},
         "with_sampling": {"value": round(world * n_samp / (ms_samp * 1e-3), 2), "unit": "iters/s", "steps": n_samp,
                           "note": samp_note, "last_batch_counters_nodes_edges_cutnodes_cutedges": cut},
+        "look_ahead": {
+            "enabled": bool(look_ahead),
+            "rows_fetched_ahead_per_step": round(staged[0] / steps_value, 1),
+            "rows_taken_from_them_per_step": round(stats[2] / steps_value, 1),
+            "rows_read_in_the_step_per_step": round(stats[0] / steps_value, 1),
+            "fetched_in_vain_frac": round((staged[0] - stats[2]) / max(staged[0], 1), 4),
+            "host_link_bytes_per_step": int((staged[0] + stats[0]) / steps_value * feat_bytes),
+            "value_without": round(world * K / (statistics.median(plain_ms) * 1e-3), 2) if plain_ms else None,
+            "note": "the captured step fetches the NEXT batch's host feature rows on a second branch beside "
+                    "its own compute (hiscache/graphed.py); rows whose consumers turn out to be served from "
+                    "history were fetched in vain; a timed region is K steps of the running pipeline",
+        } if use_graph else None,
         "gpu_launches": int(launches),
         "gpu_launches_note": "library kernels per K-step region (PyTorch's own kernels not counted)",
         "host_issue_ms_per_step": round(statistics.median(reg_issue) / K, 4),

@@ -110,6 +110,9 @@ struct LoadArgs {
   void* x; int x_dtype; int64_t x_stride;
   uint8_t* load_mask_out; unsigned long long* stats;
   int host_mode, cache_mode, zero_mode;
+  // rows fetched ahead of the step: staged_rows[i] is host_table[sub_to_full[i]] where staged_mask[i]
+  const void* staged_rows; const uint8_t* staged_mask; int staged_mode;
+  int sparse_out;   // rows that are not loaded need not be written (the staging call)
 };
 
 template <int G>
@@ -117,33 +120,43 @@ __global__ void __launch_bounds__(256) load_rows_kernel(const LoadArgs a) {
   const int gl = threadIdx.x % G;
   const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / G;
   const bool live = i < a.n;
-  int from_host = 0, from_cache = 0;
+  int from_host = 0, from_cache = 0, from_staged = 0;
   if (live) {
     const int64_t sf = a.sub2feat ? a.sub2feat[i] : -1;
     const bool used = a.used == nullptr || a.used[i] != 0;
-    const bool load = used && sf == -1;
-    if (load) {
+    bool load = used && sf == -1;
+    if (load && a.sparse_out) {
+      const int64_t g = a.sub_to_full[i];
+      load = g >= 0 && g < a.host_rows;
+    }
+    if (load && a.staged_mask && a.staged_mask[i]) {
+      move_row(a.staged_rows, a.x_dtype, i * (int64_t)a.feat, a.x, a.x_dtype, i * a.x_stride, a.feat, gl, G,
+               a.staged_mode);
+      from_staged = gl == 0;
+    } else if (load) {
       const int64_t g = a.sub_to_full[i];
       const bool ok = g >= 0 && g < a.host_rows;
       move_row(ok ? a.host_table : nullptr, a.host_dtype, g * a.host_stride, a.x, a.x_dtype,
                i * a.x_stride, a.feat, gl, G, ok ? a.host_mode : a.zero_mode);
       from_host = gl == 0;
-    } else if (sf != -1) {
+    } else if (sf != -1 && !(a.sparse_out && a.feat_cache == nullptr)) {
       int64_t r = sf < 0 ? sf + a.cache_rows : sf;
       const bool ok = r >= 0 && r < a.cache_rows;
       move_row(ok ? a.feat_cache : nullptr, a.cache_dtype, r * a.cache_stride, a.x, a.x_dtype,
                i * a.x_stride, a.feat, gl, G, ok ? a.cache_mode : a.zero_mode);
       from_cache = gl == 0;
-    } else {
+    } else if (!a.sparse_out) {
       move_row(nullptr, a.x_dtype, 0, a.x, a.x_dtype, i * a.x_stride, a.feat, gl, G, a.zero_mode);
     }
     if (a.load_mask_out && gl == 0) a.load_mask_out[i] = load ? 1 : 0;
   }
   if (a.stats) {
     const int h = __syncthreads_count(from_host), c = __syncthreads_count(from_cache);
+    const int p = __syncthreads_count(from_staged);
     if (threadIdx.x == 0) {
       if (h) atomicAdd(a.stats, (unsigned long long)h);
       if (c) atomicAdd(a.stats + 1, (unsigned long long)c);
+      if (p) atomicAdd(a.stats + 2, (unsigned long long)p);     // only callers that stage rows get here
     }
   }
 }
@@ -159,6 +172,7 @@ __global__ void __launch_bounds__(256) load_rows_kernel(const LoadArgs a) {
 constexpr int kBulkWarps = 4;      // warps per block
 constexpr int kBulkTile = 32;      // rows per tile = one row per lane
 constexpr int kBulkSpin = 1 << 22; // bound of every wait loop
+constexpr int kStageBlocks = 32;   // grid of a staging call (hc_stage_host_rows), see stage_rows_kernel
 
 __global__ void __launch_bounds__(kBulkWarps * 32)
     load_rows_bulk_kernel(const LoadArgs a, const int row_bytes, const int64_t tiles) {
@@ -177,31 +191,39 @@ __global__ void __launch_bounds__(kBulkWarps * 32)
   const int es = a.x_dtype == HC_F16 ? 2 : 4;
   bool engine_ok = true;
   uint32_t phase = 0;
-  unsigned long long n_host = 0, n_cache = 0;
+  unsigned long long n_host = 0, n_cache = 0, n_staged = 0;
   int which = 0;
   const int64_t warps_total = (int64_t)gridDim.x * kBulkWarps;
   for (int64_t t = (int64_t)blockIdx.x * kBulkWarps + warp; t < tiles; t += warps_total) {
     const int64_t i = t * kBulkTile + lane;
     const bool live = i < a.n;
     const void* src = nullptr;
-    bool load = false, from_cache = false;
+    bool load = false, from_cache = false, from_staged = false;
     if (live) {
       const int64_t sf = a.sub2feat ? a.sub2feat[i] : -1;
       const bool used = a.used == nullptr || a.used[i] != 0;
       load = used && sf == -1;
-      if (load) {
+      if (load && a.staged_mask && a.staged_mask[i]) {
+        src = reinterpret_cast<const char*>(a.staged_rows) + i * (int64_t)row_bytes;
+        from_staged = true;
+        load = false;
+      } else if (load) {
         const int64_t g = a.sub_to_full[i];
         if (g >= 0 && g < a.host_rows)
           src = reinterpret_cast<const char*>(a.host_table) + g * a.host_stride * es;
+        else if (a.sparse_out)
+          load = false;     // an id outside the table is not staged; the step gives it a zero row
       } else if (sf != -1) {
         const int64_t r = sf < 0 ? sf + a.cache_rows : sf;
         if (r >= 0 && r < a.cache_rows) src = reinterpret_cast<const char*>(a.feat_cache) + r * a.cache_stride * es;
         from_cache = true;
       }
-      if (a.load_mask_out) a.load_mask_out[i] = load ? 1 : 0;
+      if (a.load_mask_out) a.load_mask_out[i] = (load || from_staged) ? 1 : 0;
     }
     n_host += __popc(__ballot_sync(kFull, load));
     n_cache += __popc(__ballot_sync(kFull, from_cache));
+    n_staged += __popc(__ballot_sync(kFull, from_staged));
+    if (a.sparse_out && !__any_sync(kFull, src != nullptr)) continue;   // nothing to move in this tile
     const int64_t left = a.n - t * kBulkTile;
     const int rows_here = (int)(left < kBulkTile ? left : kBulkTile);
     char* xrow = reinterpret_cast<char*>(a.x) + i * (int64_t)row_bytes;
@@ -256,6 +278,7 @@ __global__ void __launch_bounds__(kBulkWarps * 32)
   if (a.stats && lane == 0) {
     if (n_host) atomicAdd(a.stats, n_host);
     if (n_cache) atomicAdd(a.stats + 1, n_cache);
+    if (n_staged) atomicAdd(a.stats + 2, n_staged);
   }
 }
 
@@ -334,6 +357,68 @@ using namespace hc;
     default: { constexpr int kG = 32; __VA_ARGS__; } break; \
   }
 
+// ---------------------------------------------------------------------------
+// Staging of host rows beside a training step (hc_stage_host_rows).  The call shares the GPU with
+// the step's own kernels, so it is written to need almost nothing of an SM: a few small blocks, no
+// shared memory, no polling.  A batch is seen as a list of 16-byte units (unit u belongs to row
+// u / units_per_row); consecutive lanes take consecutive units, every thread issues kStageUnroll
+// independent 16-byte loads before it stores the first, and a warp that waits for the host link
+// is simply stalled on its loads.  kStageBlocks x 128 threads x kStageUnroll loads are several
+// thousand 128-byte read requests in flight, an order of magnitude more than the link takes.
+// ---------------------------------------------------------------------------
+namespace hc {
+
+constexpr int kStageThreads = 128;
+constexpr int kStageUnroll = 8;
+
+__global__ void __launch_bounds__(kStageThreads)
+    stage_rows_kernel(const LoadArgs a, const int units_per_row, const int64_t units) {
+  const int es = a.x_dtype == HC_F16 ? 2 : 4;
+  const int64_t tile = (int64_t)kStageThreads * kStageUnroll;
+  unsigned long long n_rows = 0, n_skipped = 0;
+  for (int64_t base = (int64_t)blockIdx.x * tile; base < units; base += (int64_t)gridDim.x * tile) {
+    uint4 v[kStageUnroll];
+    bool take[kStageUnroll];
+#pragma unroll
+    for (int j = 0; j < kStageUnroll; ++j) {
+      const int64_t u = base + (int64_t)j * kStageThreads + threadIdx.x;
+      take[j] = false;
+      if (u < units) {
+        const int64_t i = u / units_per_row;
+        const int off = (int)(u - i * units_per_row);
+        const bool cached = a.sub2feat != nullptr && a.sub2feat[i] != -1;
+        const bool wanted = a.used == nullptr || a.used[i] != 0;
+        const int64_t g = a.sub_to_full[i];
+        take[j] = wanted && !cached && g >= 0 && g < a.host_rows;
+        if (take[j])
+          v[j] = ldg16(reinterpret_cast<const char*>(a.host_table) + g * a.host_stride * es + 16 * off);
+        if (off == 0) {
+          a.load_mask_out[i] = take[j] ? 1 : 0;
+          n_rows += take[j];
+          n_skipped += wanted && cached;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kStageUnroll; ++j) {
+      if (take[j]) {
+        const int64_t u = base + (int64_t)j * kStageThreads + threadIdx.x;
+        reinterpret_cast<uint4*>(a.x)[u] = v[j];
+      }
+    }
+  }
+  if (a.stats) {
+    n_rows = __reduce_add_sync(kFull, (unsigned)n_rows);
+    n_skipped = __reduce_add_sync(kFull, (unsigned)n_skipped);
+    if ((threadIdx.x & 31) == 0) {
+      if (n_rows) atomicAdd(a.stats, n_rows);
+      if (n_skipped) atomicAdd(a.stats + 1, n_skipped);
+    }
+  }
+}
+
+}  // namespace hc
+
 extern "C" int hc_map_lookup(const int64_t* map, int64_t map_len, const int64_t* ids, int64_t n,
                              int64_t offset, int64_t force_miss_below, int64_t* out, void* stream) {
   HC_REQUIRE(n >= 0 && map_len >= 0, HC_ERR_SIZE);
@@ -370,13 +455,14 @@ extern "C" int hc_gather_rows(const void* table, int32_t table_dtype, int64_t ta
   return 0;
 }
 
-extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
-                            int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
-                            int64_t cache_rows, int64_t cache_stride, int32_t feat,
-                            const int64_t* sub_to_full, const int64_t* sub2feat,
-                            const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
-                            int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
-                            void* stream) {
+static int load_rows_impl(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                          int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
+                          int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                          const int64_t* sub_to_full, const int64_t* sub2feat,
+                          const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                          int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                          const void* staged_rows, const uint8_t* staged_mask, int sparse_out,
+                          void* stream) {
   HC_REQUIRE(n >= 0 && feat > 0 && host_rows >= 0 && cache_rows >= 0, HC_ERR_SIZE);
   HC_REQUIRE(dtype_size(x_dtype) != 0, HC_ERR_DTYPE);
   if (n == 0) return 0;
@@ -402,10 +488,24 @@ extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t 
   a.zero_mode = move_mode(nullptr, x_dtype, 0, x, x_dtype, x_stride, feat);
   a.host_mode = host_table ? move_mode(host_table, a.host_dtype, host_stride, x, x_dtype, x_stride, feat) : a.zero_mode;
   a.cache_mode = feat_cache ? move_mode(feat_cache, a.cache_dtype, cache_stride, x, x_dtype, x_stride, feat) : a.zero_mode;
+  a.staged_rows = staged_mask ? staged_rows : nullptr;
+  a.staged_mask = staged_mask;
+  a.sparse_out = sparse_out;
+  a.staged_mode = staged_mask ? move_mode(staged_rows, x_dtype, feat, x, x_dtype, x_stride, feat) : a.zero_mode;
   int worst = a.zero_mode < a.host_mode ? a.zero_mode : a.host_mode;
   if (a.cache_mode < worst) worst = a.cache_mode;
+  if (a.staged_mode < worst) worst = a.staged_mode;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int row_bytes = feat * dtype_size(x_dtype);
+  if (sparse_out && a.host_mode == 2 && x_stride == feat && load_mask_out != nullptr) {
+    const int upr = row_bytes / 16;
+    const int64_t units = n * upr;
+    int64_t blocks = ceil_div(units, (int64_t)kStageThreads * kStageUnroll);
+    if (blocks > kStageBlocks) blocks = kStageBlocks;
+    stage_rows_kernel<<<(unsigned)blocks, kStageThreads, 0, st>>>(a, upr, units);
+    HC_LAUNCH_OK();
+    return 0;
+  }
   if (worst == 2 && x_stride == feat && row_bytes <= 512 && n >= kBulkTile) {
     const int64_t tiles = ceil_div(n, kBulkTile);
     const size_t smem = (size_t)kBulkWarps * 2 * kBulkTile * row_bytes;
@@ -431,6 +531,43 @@ extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t 
   HC_DISPATCH_G(G, load_rows_kernel<kG><<<(unsigned)blocks, 256, 0, st>>>(a));
   HC_LAUNCH_OK();
   return 0;
+}
+
+extern "C" int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                            int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
+                            int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                            const int64_t* sub_to_full, const int64_t* sub2feat,
+                            const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                            int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                            void* stream) {
+  return load_rows_impl(host_table, host_dtype, host_rows, host_stride, feat_cache, cache_dtype, cache_rows,
+                        cache_stride, feat, sub_to_full, sub2feat, used, n, x, x_dtype, x_stride,
+                        load_mask_out, stats, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int hc_load_rows_staged(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                                   int64_t host_stride, const void* feat_cache, int32_t cache_dtype,
+                                   int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                                   const int64_t* sub_to_full, const int64_t* sub2feat,
+                                   const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                                   int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                                   const void* staged_rows, const uint8_t* staged_mask,
+                                   void* stream) {
+  HC_REQUIRE(staged_rows && staged_mask, HC_ERR_NULL);
+  return load_rows_impl(host_table, host_dtype, host_rows, host_stride, feat_cache, cache_dtype, cache_rows,
+                        cache_stride, feat, sub_to_full, sub2feat, used, n, x, x_dtype, x_stride,
+                        load_mask_out, stats, staged_rows, staged_mask, 0, stream);
+}
+
+extern "C" int hc_stage_host_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
+                                  int64_t host_stride, int32_t feat, const int64_t* ids,
+                                  const int64_t* sub2feat, const uint8_t* consider, int64_t n,
+                                  void* staged_rows, uint8_t* staged_mask, int64_t* stats,
+                                  void* stream) {
+  HC_REQUIRE(n == 0 || (staged_rows && staged_mask), HC_ERR_NULL);
+  return load_rows_impl(host_table, host_dtype, host_rows, host_stride, nullptr, host_dtype, 0, 0, feat, ids,
+                        sub2feat, consider, n, staged_rows, host_dtype, feat, staged_mask, stats, nullptr,
+                        nullptr, 1, stream);
 }
 
 extern "C" int hc_owner_lookup(const int64_t* map, int64_t map_len, const int64_t* ids, int64_t n,

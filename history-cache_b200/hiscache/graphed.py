@@ -17,14 +17,84 @@ import torch
 from .sampler import Batch
 
 
+class _LookAhead:
+    """Fetching the NEXT batch's host feature rows beside the current step.
+
+    Reading feature rows over the host link is the longest kernel of a step and depends on
+    nothing the step computes except which rows history makes unnecessary, so the captured step
+    forks a second branch right after its own input rows are assembled:
+
+        main   lookup, used masks, load (takes staged rows) | forward ... backward, optimiser, admission
+        side                                                | stage(next ids) ------------------> join
+
+    `stage` (HistoryCache.stage_host_rows) copies the host rows of the announced batch into
+    `rows` and marks them in `mask`; the next step's load reads a marked row from `rows` instead
+    of the host table.  The staging reads node ids only, so rows whose consumers later turn out to
+    be served from history are moved in vain (counted by `table.stage_stats` against
+    `table.load_stats`); a row that is not marked is fetched in the step as before.  `mask` is
+    cleared whenever the batch that arrives is not the one that was announced.
+    """
+
+    def __init__(self, table, n_rows, device):
+        buf = table.uvm.buffer
+        self.table = table
+        self.ids = torch.zeros(n_rows, dtype=torch.int64, device=device)
+        self.valid = torch.zeros(n_rows, dtype=torch.bool, device=device)
+        self.rows = torch.zeros((n_rows, buf.shape[1]), dtype=buf.dtype, device=device)
+        self.mask = torch.zeros(n_rows, dtype=torch.uint8, device=device)
+        self.side = torch.cuda.Stream(device=device)
+        self.device = device
+        self.announced = None
+
+    def __enter__(self):
+        # only a step issued by the owner of the look-ahead may consume what it staged
+        self.table.staged = (self.rows, self.mask)
+        return self
+
+    def __exit__(self, *exc):
+        self.table.staged = None
+        self.join()
+        return False
+
+    @staticmethod
+    def usable(table) -> bool:
+        return (getattr(table, "uvm", None) is not None and "history" in str(table.feat_mode)
+                and not table.uvm.buffer.is_cuda)
+
+    def fork(self, ids=None, valid=None):
+        """Called on the main stream once the current batch's rows are assembled."""
+        main = torch.cuda.current_stream(self.device)
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            self.table.stage_host_rows(self.ids if ids is None else ids,
+                                       self.valid if valid is None else valid, self.rows, self.mask)
+
+    def join(self):
+        torch.cuda.current_stream(self.device).wait_stream(self.side)
+
+    def announce(self, batch, next_batch, fits):
+        """Host side of a replay: what was staged must be for `batch`; `next_batch` is staged now."""
+        if self.announced is not batch:
+            self.mask.zero_()
+        if next_batch is not None and fits(next_batch):
+            self.ids.copy_(next_batch.sub_to_full, non_blocking=True)
+            self.valid.copy_(next_batch.mask, non_blocking=True)
+            self.announced = next_batch
+        else:
+            self.valid.zero_()
+            self.announced = None
+
+
 class GraphedStep:
     """Owns the static input batch and the captured graph of `trainer._step_body(batch)`."""
 
-    def __init__(self, trainer, caps, edge_cap, warmup_batches):
+    def __init__(self, trainer, caps, edge_cap, warmup_batches, look_ahead=True):
         self.trainer = trainer
         self.caps, self.edge_cap = list(caps), int(edge_cap)
         dev = trainer.device
         L = len(self.caps) - 1
+        self.ahead = (_LookAhead(trainer.table, self.caps[L], dev)
+                      if look_ahead and _LookAhead.usable(trainer.table) else None)
         b = Batch()
         b.ptr = torch.zeros(self.caps[L - 1] + 1, dtype=torch.int64, device=dev)
         b.idx = torch.zeros(self.edge_cap, dtype=torch.int64, device=dev)
@@ -41,7 +111,7 @@ class GraphedStep:
         with torch.cuda.stream(s):
             for wb in warmup_batches:
                 self._load(wb)
-                trainer._step_body(self.static)
+                self._body()
         torch.cuda.current_stream(dev).wait_stream(s)
         torch.cuda.synchronize(dev)
         import hiscache_backend as hb
@@ -49,8 +119,17 @@ class GraphedStep:
         self._load(warmup_batches[-1])
         before = hb.launch_count()
         with torch.cuda.graph(self.graph):
-            self.loss = trainer._step_body(self.static)
+            self.loss = self._body()
         self.library_kernels_per_step = hb.launch_count() - before
+        if self.ahead is not None:      # nothing is staged for the first replay
+            self.ahead.mask.zero_()
+            self.ahead.valid.zero_()
+
+    def _body(self):
+        if self.ahead is None:
+            return self.trainer._step_body(self.static)
+        with self.ahead:
+            return self.trainer._step_body(self.static, after_load=self.ahead.fork)
 
     enabled = True      # set False to make every batch take the eager step (e.g. for per-kernel timing)
 
@@ -67,8 +146,10 @@ class GraphedStep:
         st.mask.copy_(batch.mask, non_blocking=True)
         st.y.copy_(batch.y, non_blocking=True)
 
-    def run(self, batch):
+    def run(self, batch, next_batch=None):
         self._load(batch)
+        if self.ahead is not None:
+            self.ahead.announce(batch, next_batch, self.fits)
         self.graph.replay()
         return self.loss
 
@@ -95,35 +176,69 @@ class _SeedWindow:
 
 class GraphedSampledStep:
     """Sampling AND the training iteration as one CUDA graph (one GPU): the device-side fixed-shape
-    sampler (hc_sample_fixed) needs no host read-back, so it is captured in front of
-    `trainer._step_body`; a replay draws the next batch and trains on it with a single launch."""
+    sampler (hc_sample_fixed) needs no host read-back, so it is captured with
+    `trainer._step_body`; a replay draws a batch and trains with a single launch.
 
-    def __init__(self, trainer, loader, caps, edge_cap, warmup=2):
+    With look_ahead the graph is software-pipelined by one batch: a replay trains on the batch
+    the previous replay drew, while a second branch draws the next one and then (once the current
+    batch's rows are assembled) fetches its host feature rows:
+
+        main   cur <- next | lookup, load (staged rows) | forward ... admission
+        side               | sample(next) ..............| stage(next) ----------> join
+    """
+
+    def __init__(self, trainer, loader, caps, edge_cap, warmup=2, look_ahead=True):
         import hiscache_backend as hb
         self.trainer, self.loader = trainer, loader
         self.caps, self.edge_cap = list(caps), int(edge_cap)
         dev = trainer.device
+        L = len(self.caps) - 1
         self.seeds = _SeedWindow(loader, min(loader.batch_size, self.caps[0]))
-        sampler = loader.sampler
+        self.sampler = loader.sampler
         self.fixed = None
+        self.ahead = (_LookAhead(trainer.table, self.caps[L], dev)
+                      if look_ahead and _LookAhead.usable(trainer.table) else None)
         s = torch.cuda.Stream(device=dev)
         s.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(s):
+            if self.ahead is not None:
+                self.seeds.advance()
+                self.next = self._draw()         # the batch the first body trains on
+                self.cur = Batch()
+                for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
+                    setattr(self.cur, k, torch.empty_like(getattr(self.next, k)))
+                self.cur.num_node_in_layer = self.next.num_node_in_layer
+                self.cur.num_edge_in_layer = self.next.num_edge_in_layer
             for _ in range(max(1, warmup)):
                 self.seeds.advance()
-                b = sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
-                self.fixed = b.fixed
-                trainer._step_body(b)
+                self._body()
         torch.cuda.current_stream(dev).wait_stream(s)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
-        self.seeds.advance()
         before = hb.launch_count()
-        with torch.cuda.graph(self.graph):
-            b = sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
-            self.loss = trainer._step_body(b)
+        with torch.cuda.graph(self.graph):     # records without running: no window of seeds is used up
+            self.loss = self._body()
         self.library_kernels_per_step = hb.launch_count() - before
         self.counters = self.fixed["counters"]
+        # the capture ran nothing: `next` and the staged rows are still those of the last warm-up body
+
+    def _draw(self):
+        b = self.sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
+        self.fixed = b.fixed
+        return b
+
+    def _body(self):
+        tr, ah = self.trainer, self.ahead
+        if ah is None:
+            return tr._step_body(self._draw())
+        cur, nxt = self.cur, self.next
+        for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
+            getattr(cur, k).copy_(getattr(nxt, k), non_blocking=True)
+        ah.side.wait_stream(torch.cuda.current_stream(ah.device))
+        with torch.cuda.stream(ah.side):
+            self.next = nxt = self._draw()      # overwrites the buffers `cur` was copied from
+        with ah:
+            return tr._step_body(cur, after_load=lambda: ah.fork(nxt.sub_to_full, nxt.mask))
 
     def run(self):
         self.seeds.advance()
@@ -149,12 +264,15 @@ class GraphedDataParallelStep:
     collectives in the same order).
     """
 
-    def __init__(self, trainer, caps, edge_cap, warmup_batches):
+    def __init__(self, trainer, caps, edge_cap, warmup_batches, look_ahead=True):
         import hiscache_backend as hb
         self.trainer = tr = trainer
         self.caps, self.edge_cap = list(caps), int(edge_cap)
         dev = tr.device
         L = len(self.caps) - 1
+        # the look-ahead branch joins at the end of segment A, before the all-reduce
+        self.ahead = (_LookAhead(tr.table, self.caps[L], dev)
+                      if look_ahead and _LookAhead.usable(tr.table) else None)
         b = Batch()
         b.ptr = torch.zeros(self.caps[L - 1] + 1, dtype=torch.int64, device=dev)
         b.idx = torch.zeros(self.edge_cap, dtype=torch.int64, device=dev)
@@ -195,11 +313,23 @@ class GraphedDataParallelStep:
             self._segment_b(True)
         self.library_kernels_per_step = hb.launch_count() - before
         # the two captures recorded a step without running it: nothing was published or admitted
+        if self.ahead is not None:      # nothing is staged for the first replay
+            self.ahead.mask.zero_()
+            self.ahead.valid.zero_()
 
     def _segment_a(self):
         tr = self.trainer
         self.flat.zero_()
-        tr.table.lookup_and_load(self.static, tr.num_layer)
+        if self.ahead is None:
+            tr.table.lookup_and_load(self.static, tr.num_layer)
+            return self._compute_a()
+        with self.ahead:
+            tr.table.lookup_and_load(self.static, tr.num_layer)
+            self.ahead.fork()
+            return self._compute_a()
+
+    def _compute_a(self):
+        tr = self.trainer
         out = tr.model(self.static)
         self.loss = tr.loss_fn(out, self.static.y)
         self.loss.backward()
@@ -226,9 +356,11 @@ class GraphedDataParallelStep:
         st.mask.copy_(batch.mask, non_blocking=True)
         st.y.copy_(batch.y, non_blocking=True)
 
-    def run(self, batch):
+    def run(self, batch, next_batch=None):
         tr = self.trainer
         self._load(batch)
+        if self.ahead is not None:
+            self.ahead.announce(batch, next_batch, self.fits)
         self.graph_a.replay()
         tr._reduce_flat()
         self.graph_b.replay()

@@ -67,7 +67,11 @@ class HistoryCache:
         self._header = torch.zeros(1, dtype=torch.int64, device=self.device)
         self._n_admitted = torch.zeros(1, dtype=torch.int64, device=self.device)
         self._thres = torch.zeros(1, dtype=torch.float32, device=self.device)
-        self.load_stats = torch.zeros(2, dtype=torch.int64, device=self.device)
+        # rows taken by lookup_and_load from {host table, feature cache, rows staged ahead}
+        self.load_stats = torch.zeros(3, dtype=torch.int64, device=self.device)
+        # rows moved by stage_host_rows: {from the host table, skipped (in the feature cache), -}
+        self.stage_stats = torch.zeros(3, dtype=torch.int64, device=self.device)
+        self.staged = None      # (rows, mask) filled by stage_host_rows for the batch that comes next
         self.produced_embedding = None
         self.row_score = None          # filled by the aggregation's backward pass
         self._sink = None
@@ -200,8 +204,31 @@ class HistoryCache:
                                                        num_layer)
         self.glb_iter += 1
         batch.x = hb.load_rows(self.uvm.buffer, feat_cache, batch.sub_to_full, self.sub2feat,
-                               self.used_masks[0], out_dtype=x_dtype, stats=self.load_stats)
+                               self.used_masks[0], out_dtype=x_dtype, stats=self.load_stats,
+                               staged=self._staged_for(batch))
         return None
+
+    def _staged_for(self, batch):
+        st = self.staged
+        if st is None or st[0].shape[0] != batch.sub_to_full.shape[0]:
+            return None
+        return st
+
+    @torch.no_grad()
+    def stage_host_rows(self, ids, valid, rows_out, mask_out):
+        """Fetches, ahead of the step that will use them, the host rows of the nodes `ids` ([n]
+        global ids, `valid` [n] marking the entries that are real) into rows_out / mask_out;
+        `lookup_and_load` of a batch with these ids then reads those rows from device memory
+        (set `self.staged = (rows_out, mask_out)`).  Rows that sit in the feature cache now are
+        skipped: if one of them has been displaced by the time the step runs, the step reads it
+        from the host as before.  Rows that the step turns out not to need (their consumers are
+        served from history) were moved in vain; results never change, since host rows are
+        constant.  May run on any stream, also beside a step that is admitting rows: the map is
+        read with whole-word loads and either value of an entry is handled.
+
+        The reference loads inside the step only (hiscache/history_cache.py:327-350)."""
+        sub2feat = hb.map_lookup(self.full2embed, ids, offset=self.total_num_node)
+        hb.stage_host_rows(self.uvm.buffer, ids, sub2feat, valid, rows_out, mask_out, stats=self.stage_stats)
 
     # -- admission ----------------------------------------------------------
     def score_sink(self, n):

@@ -49,7 +49,7 @@ class HistoryTableTrainer:
         self.num_layer = len(self.model.convs)
         self.glb_iter = 0
 
-    def train_step(self, batch):
+    def train_step(self, batch, next_batch=None):
         import hiscache_backend as hb
         t = self.table
         self.optimizer.zero_grad(set_to_none=True)
@@ -104,13 +104,16 @@ class HistoryTrainer:
         self.graphed = None
 
     # one iteration of cxg_train_epoch (history_trainer.py:183-191)
-    def train_step(self, batch):
+    def train_step(self, batch, next_batch=None):
+        """`next_batch` (optional): the batch the following call will get.  The captured step then
+        fetches its host feature rows beside this step's compute (hiscache/graphed.py); results do
+        not depend on it."""
         g = self.graphed
         if g is not None and g.fits(batch):
             # the ring restart is decided on the host, so it happens outside the captured step
             if self.table.staleness_thres > 0 and (self.glb_iter % self.table.staleness_thres) == 0:
                 self.table._header.zero_()
-            loss = g.run(batch)
+            loss = g.run(batch, next_batch)
             self.table.glb_iter += 1
         else:
             loss = self._step_body(batch, reset=None)
@@ -118,11 +121,14 @@ class HistoryTrainer:
         self.glb_iter += 1
         return loss
 
-    def _step_body(self, batch, reset=False):
+    def _step_body(self, batch, reset=False, after_load=None):
         """Everything of one iteration that runs on the device; with reset=False it contains no
-        host-side decision and can be captured in a CUDA graph."""
+        host-side decision and can be captured in a CUDA graph.  `after_load` is called once the
+        batch's input rows have been assembled (the captured step forks its look-ahead there)."""
         self.optimizer.zero_grad(set_to_none=True)
         self.table.lookup_and_load(batch, len(self.model.convs))
+        if after_load is not None:
+            after_load()
         out = self.model(batch)
         loss = self.loss_fn(out, batch.y)
         loss.backward()
@@ -130,19 +136,21 @@ class HistoryTrainer:
         self.table.update_history(batch, self.glb_iter, reset=reset)
         return loss
 
-    def enable_cuda_graph(self, caps, edge_cap, warmup_batches):
-        """Captures the step for fixed-shape batches of these caps (hiscache/graphed.py)."""
+    def enable_cuda_graph(self, caps, edge_cap, warmup_batches, look_ahead=True):
+        """Captures the step for fixed-shape batches of these caps (hiscache/graphed.py).
+        look_ahead: the captured step also fetches the host rows of the batch announced as
+        `next_batch`, beside its own compute."""
         from .graphed import GraphedStep
         self.model.train()
-        self.graphed = GraphedStep(self, caps, edge_cap, warmup_batches)
+        self.graphed = GraphedStep(self, caps, edge_cap, warmup_batches, look_ahead=look_ahead)
         return self.graphed
 
-    def enable_sampled_cuda_graph(self, caps, edge_cap):
+    def enable_sampled_cuda_graph(self, caps, edge_cap, look_ahead=True):
         """Captures sampling + step as one graph (hiscache/graphed.py:GraphedSampledStep);
         `train_step_sampled()` then draws and trains on the next batch with one launch."""
         from .graphed import GraphedSampledStep
         self.model.train()
-        self.sampled = GraphedSampledStep(self, self.loader, caps, edge_cap)
+        self.sampled = GraphedSampledStep(self, self.loader, caps, edge_cap, look_ahead=look_ahead)
         return self.sampled
 
     def train_step_sampled(self):
@@ -158,8 +166,12 @@ class HistoryTrainer:
         self.model.train()
         tepoch = time.time()
         n = 0
-        for batch in self.loader.train_loader:
-            self.train_step(batch)
+        it = iter(self.loader.train_loader)
+        batch = next(it, None)
+        while batch is not None:
+            following = next(it, None)
+            self.train_step(batch, following)
+            batch = following
             n += 1
         torch.cuda.synchronize()
         log.info(f"epoch time: {time.time() - tepoch} ({n} iterations)")

@@ -75,7 +75,8 @@ class ShardedHistoryCache(HistoryCache):
         self.glb_iter += 1
         batch.x = hb.load_rows(self.uvm.buffer, self.buffer.view(-1, self.in_channels),
                                batch.sub_to_full, self.sub2feat, self.used_masks[0],
-                               out_dtype=self.uvm.buffer.dtype, stats=self.load_stats)
+                               out_dtype=self.uvm.buffer.dtype, stats=self.load_stats,
+                               staged=self._staged_for(batch))
         return None
 
     @property
@@ -218,26 +219,27 @@ class MultiGpuHistoryTrainer:
         self.optimizer.step()
         self.scheduler.step()
 
-    def enable_cuda_graph(self, caps, edge_cap, warmup_batches):
+    def enable_cuda_graph(self, caps, edge_cap, warmup_batches, look_ahead=True):
         """Replays the step for fixed-shape batches of these caps as two captured segments around
         the gradient all-reduce (hiscache/graphed.py).  Collective: every rank must call it, with
         the same number of warm-up batches."""
         from .graphed import GraphedDataParallelStep
         self.model.train()
-        self.graphed = GraphedDataParallelStep(self, caps, edge_cap, warmup_batches)
+        self.graphed = GraphedDataParallelStep(self, caps, edge_cap, warmup_batches, look_ahead=look_ahead)
         return self.graphed
 
     def update_history(self, batch):
         self.table.update_history(batch, self.glb_iter)
         self.glb_iter += 1
 
-    def train_step(self, batch):
+    def train_step(self, batch, next_batch=None):
         """The gradient all-reduce sits between the two halves of the history update: it is
         the collective that tells every owner that all ranks have published their candidates
-        and finished this step's lookups."""
+        and finished this step's lookups.  `next_batch` (optional) announces the batch of the
+        following call, whose host feature rows the captured step then fetches beside its compute."""
         g = self.graphed
         if g is not None and g.fits(batch):
-            loss = g.run(batch)
+            loss = g.run(batch, next_batch)
             self.glb_iter += 1
             return loss
         self.load(batch)
@@ -253,8 +255,12 @@ class MultiGpuHistoryTrainer:
     def cxg_train_epoch(self):
         self.model.train()
         t0 = time.time()
-        for batch in self.loader.train_loader:
-            self.train_step(batch)
+        it = iter(self.loader.train_loader)
+        batch = next(it, None)
+        while batch is not None:
+            following = next(it, None)
+            self.train_step(batch, following)
+            batch = following
         torch.cuda.synchronize()
         log.info(f"epoch time: {time.time() - t0}")
 

@@ -8,9 +8,9 @@ with several GPUs every rank then pays the slowest rank's host time as well.
 
 `HostBatchPipeline` keeps both inside the step but off its critical path:
 
-  * the structures of batch k+1 (ptr, idx, sub_to_full, y, mask) are copied on a second stream
-    into one of two preallocated device buffers while step k runs; the training stream only
-    waits on the copy's event;
+  * the structures of the following batches (ptr, idx, sub_to_full, y, mask) are copied on a
+    second stream into one of `depth` preallocated device buffers while earlier steps run; the
+    training stream only waits on the copy's event;
   * the loss of step k is copied into page-locked memory behind the step and read by the host
     one step later, after its event has completed.
 
@@ -27,7 +27,7 @@ _KEYS = ("ptr", "idx", "sub_to_full", "y", "mask")
 
 class HostBatchPipeline:
 
-    def __init__(self, trainer, host_batches, depth=2):
+    def __init__(self, trainer, host_batches, depth=3):
         self.trainer = trainer
         self.dev = trainer.device
         self.depth = int(depth)
@@ -46,6 +46,8 @@ class HostBatchPipeline:
         self.consumed = [None] * self.depth
         self.loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(self.depth)]
         self.loss_ready = [torch.cuda.Event() for _ in range(self.depth)]
+        self._done = 0          # steps run so far: batch g of the whole sequence uses slot g % depth
+        self._staged = {}       # g -> (host batch, its device copy), copied but not yet trained on
 
     def _stage(self, hbatch, slot):
         """Starts the copy of one host batch into device slot `slot`; returns the device view."""
@@ -65,32 +67,56 @@ class HostBatchPipeline:
         b.num_node_in_layer, b.num_edge_in_layer = hbatch.num_node_in_layer, hbatch.num_edge_in_layer
         return b
 
-    def run(self, host_batches):
-        """One training step per host batch; returns the list of losses (floats)."""
+    def run(self, host_batches, after=None):
+        """One training step per host batch; returns the list of losses (floats).  Batches are
+        copied `depth - 1` steps ahead, and the one that follows is announced to the step, which
+        can then fetch its feature rows beside its own compute (HistoryTrainer.train_step).
+        `after`: the batch the next call of run() will start with; it is copied and announced
+        during this call's last steps, so that consecutive calls form one running pipeline."""
         tr = self.trainer
         main = torch.cuda.current_stream(self.dev)
         losses = []
         n = len(host_batches)
         if n == 0:
             return losses
-        staged = self._stage(host_batches[0], 0)
-        pending = None              # (slot) of the loss still on its way to the host
+        seq = list(host_batches) + ([after] if after is not None else [])
+        base, depth, ahead = self._done, self.depth, self.depth - 1
+
+        def ensure(j):      # seq[j] is on its way to the device (global position base + j)
+            g = base + j
+            have = self._staged.get(g)
+            if have is None or have[0] is not seq[j]:
+                self._staged[g] = (seq[j], self._stage(seq[j], g % depth))
+
+        for g in [g for g in self._staged if g < base]:
+            del self._staged[g]
+        for j in range(min(ahead, len(seq))):
+            ensure(j)
+        pending = None              # slot of the loss still on its way to the host
         for i in range(n):
-            slot = i % self.depth
-            batch = staged
+            g = base + i
+            slot = g % depth
+            ensure(i)
+            batch = self._staged.pop(g)[1]
             main.wait_event(self.copied[slot])
-            if i + 1 < n:
-                staged = self._stage(host_batches[i + 1], (i + 1) % self.depth)
-            loss = tr.train_step(batch)
+            following = None
+            if i + 1 < len(seq):
+                ensure(i + 1)
+                following = self._staged[g + 1][1]      # its ids are read on the training stream
+                main.wait_event(self.copied[(g + 1) % depth])
+            loss = tr.train_step(batch, following)
             self.loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)
             self.loss_ready[slot].record(main)
             ev = torch.cuda.Event()
             ev.record(main)
             self.consumed[slot] = ev
+            if i + ahead < len(seq):        # reuses the slot of the step before this one
+                ensure(i + ahead)
             if pending is not None:
                 self.loss_ready[pending].synchronize()
                 losses.append(float(self.loss_host[pending][0]))
             pending = slot
         self.loss_ready[pending].synchronize()
         losses.append(float(self.loss_host[pending][0]))
+        self._done += n
         return losses

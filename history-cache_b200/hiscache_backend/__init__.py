@@ -350,6 +350,10 @@ def declare_batch(ptr_t, idx_t, n_nodes):
     that all layers aggregate over (layer k uses the rows [0, num_node_k)).  The backward passes
     of the batch can then share ONE transposition (see shared_transpose)."""
     _declared[ptr_t.device] = (_graph_key(ptr_t, idx_t), int(n_nodes))
+    # a declaration opens a new batch: the same buffers may have been refilled by a library call
+    # (which leaves no trace in the tensors' version counters), and a step that is being captured
+    # must record its own transposition instead of borrowing the one of the warm-up
+    _shared_t.pop(ptr_t.device, None)
 
 
 def shared_transpose(ptr_t, idx_t):
@@ -758,11 +762,15 @@ def gather_rows(table, rows, zero_missing=False, out_dtype=None):
 
 
 def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=None,
-              want_mask=False, stats=None):
+              want_mask=False, stats=None, out=None, mask_out=None, staged=None):
     """One-pass batch.x assembly (hiscache/history_cache.py:327-350).  host_table may be a
     pinned host tensor (rows are then read over the host link by the kernel) or a CUDA
-    tensor.  Returns x, or (x, load_mask) when want_mask."""
-    dev = require_cuda(sub_to_full, sub2feat, used, feat_cache,
+    tensor.  Returns x, or (x, load_mask) when want_mask.
+
+    out / mask_out: preallocated destinations ([n, F] rows, [n] uint8 mask).
+    staged = (rows [n, F], mask [n] uint8): host rows fetched ahead of the step by
+    `stage_host_rows`; a row whose mask is set is read from there instead of host_table.  `stats` then needs three counters (host, cache, staged)."""
+    dev = require_cuda(sub_to_full, sub2feat, used, feat_cache, out, mask_out,
                        host_table if host_table.is_cuda else None)
     if not host_table.is_cuda and not host_table.is_pinned():
         raise RuntimeError("load_rows: a host feature table must be pinned memory")
@@ -770,23 +778,77 @@ def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=Non
     sub_to_full = i64c(sub_to_full, "sub_to_full")
     sub2feat = i64c(sub2feat, "sub2feat")
     n, F = sub_to_full.shape[0], host_table.shape[1]
-    x = torch.empty((n, F), dtype=out_dtype or host_table.dtype, device=dev)
-    mask = torch.empty(n, dtype=torch.uint8, device=dev) if want_mask else None
+    dt = out_dtype or host_table.dtype
+    if out is None:
+        x = torch.empty((n, F), dtype=dt, device=dev)
+    else:
+        if tuple(out.shape) != (n, F) or out.dtype != dt or not out.is_contiguous():
+            raise ValueError(f"load_rows: out must be a contiguous [{n}, {F}] {dt} tensor")
+        x = out
+    if mask_out is not None:
+        if mask_out.dtype != torch.uint8 or mask_out.shape[0] != n or not mask_out.is_contiguous():
+            raise ValueError(f"load_rows: mask_out must be a contiguous uint8 tensor of {n} entries")
+        mask = mask_out
+    else:
+        mask = torch.empty(n, dtype=torch.uint8, device=dev) if want_mask else None
     if used is not None:
         used = used.contiguous()
+        if used.shape[0] != n or used.element_size() != 1:
+            raise ValueError(f"load_rows: used must have {n} one-byte entries")
     cd, cr, cs = HC_F32, 0, 0
     if feat_cache is not None:
         feat_cache = rows2d(feat_cache)
         cd, cr = dtype_code(feat_cache), feat_cache.shape[0]
         cs = feat_cache.stride(0) if cr > 1 else F
-    with on_device(dev), _span("hc_load_rows", dev):
-        check(lib.hc_load_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
-                               host_table.stride(0) if host_table.shape[0] > 1 else F,
-                               ptr(feat_cache), cd, cr, cs, F, ptr(sub_to_full), ptr(sub2feat),
-                               ptr(used), n, ptr(x), dtype_code(x), F, ptr(mask), ptr(stats),
-                               stream_of(dev)), "hc_load_rows")
+    common = (ptr(host_table), dtype_code(host_table), host_table.shape[0],
+              host_table.stride(0) if host_table.shape[0] > 1 else F,
+              ptr(feat_cache), cd, cr, cs, F, ptr(sub_to_full), ptr(sub2feat),
+              ptr(used), n, ptr(x), dtype_code(x), F, ptr(mask), ptr(stats))
+    if staged is None:
+        with on_device(dev), _span("hc_load_rows", dev):
+            check(lib.hc_load_rows(*common, stream_of(dev)), "hc_load_rows")
+    else:
+        s_rows, s_mask = staged
+        require_cuda(s_rows, s_mask)
+        if (tuple(s_rows.shape) != (n, F) or s_rows.dtype != x.dtype or not s_rows.is_contiguous()
+                or s_mask.dtype != torch.uint8 or s_mask.shape[0] != n or not s_mask.is_contiguous()):
+            raise ValueError(f"load_rows: staged must be ([{n}, {F}] {x.dtype} rows, [{n}] uint8 mask)")
+        if stats is not None and stats.numel() < 3:
+            raise ValueError("load_rows: stats needs three counters when rows are staged")
+        with on_device(dev), _span("hc_load_rows", dev):
+            check(lib.hc_load_rows_staged(*common, ptr(s_rows), ptr(s_mask), stream_of(dev)),
+                  "hc_load_rows_staged")
     _called()
     return (x, mask.view(torch.bool)) if want_mask else x
+
+
+def stage_host_rows(host_table, ids, sub2feat, consider, rows_out, mask_out, stats=None):
+    """Copies host_table[ids[i]] into rows_out[i] and sets mask_out[i] for every i that is to be
+    considered and is not in the feature cache (sub2feat[i] == -1); other rows of rows_out are
+    unspecified.  The result feeds `load_rows(..., staged=(rows_out, mask_out))` of a later step."""
+    dev = require_cuda(ids, sub2feat, consider, rows_out, mask_out, host_table if host_table.is_cuda else None)
+    if not host_table.is_cuda and not host_table.is_pinned():
+        raise RuntimeError("stage_host_rows: a host feature table must be pinned memory")
+    host_table = rows2d(host_table)
+    ids = i64c(ids, "ids")
+    n, F = ids.shape[0], host_table.shape[1]
+    if sub2feat is not None:
+        sub2feat = i64c(sub2feat, "sub2feat")
+        if sub2feat.shape[0] != n:
+            raise ValueError(f"stage_host_rows: sub2feat must have {n} entries")
+    if consider is not None:
+        consider = consider.contiguous()
+        if consider.shape[0] != n or consider.element_size() != 1:
+            raise ValueError(f"stage_host_rows: consider must have {n} one-byte entries")
+    if (tuple(rows_out.shape) != (n, F) or rows_out.dtype != host_table.dtype or not rows_out.is_contiguous()
+            or mask_out.dtype != torch.uint8 or mask_out.shape[0] != n or not mask_out.is_contiguous()):
+        raise ValueError(f"stage_host_rows: outputs must be [{n}, {F}] {host_table.dtype} rows and [{n}] uint8 mask")
+    with on_device(dev), _span("hc_stage_host_rows", dev):
+        check(lib.hc_stage_host_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
+                                     host_table.stride(0) if host_table.shape[0] > 1 else F, F, ptr(ids),
+                                     ptr(sub2feat), ptr(consider), n, ptr(rows_out), ptr(mask_out), ptr(stats),
+                                     stream_of(dev)), "hc_stage_host_rows")
+    _called()
 
 
 # ---------------------------------------------------------------------------

@@ -436,6 +436,44 @@ int hc_load_rows(const void* host_table, int32_t host_dtype, int64_t host_rows,
                  int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
                  void* stream);
 
+/*
+ * hc_load_rows for a batch whose host rows were (partly) fetched ahead of the
+ * step.  staged_rows is [n, feat] in device memory, dtype x_dtype, contiguous;
+ * where staged_mask[i] != 0 it holds host_table[sub_to_full[i]] and a row that
+ * hc_load_rows would read from host_table is read from there instead:
+ *   x[i] = !load_mask[i] ? (as hc_load_rows)
+ *        : staged_mask[i] ? staged_rows[i] : host_table[sub_to_full[i]]
+ * The result equals hc_load_rows' for any staged_mask (host rows never change);
+ * only the bytes that cross the host link during the step differ.  stats is
+ * int64[3] here: {rows from host_table, rows from the feature cache, rows from
+ * staged_rows}.  The reference loads in the step only (history_cache.py:
+ * 327-350) and has no counterpart.
+ */
+int hc_load_rows_staged(const void* host_table, int32_t host_dtype,
+                        int64_t host_rows, int64_t host_stride,
+                        const void* feat_cache, int32_t cache_dtype,
+                        int64_t cache_rows, int64_t cache_stride, int32_t feat,
+                        const int64_t* sub_to_full, const int64_t* sub2feat,
+                        const uint8_t* used, int64_t n, void* x, int32_t x_dtype,
+                        int64_t x_stride, uint8_t* load_mask_out, int64_t* stats,
+                        const void* staged_rows, const uint8_t* staged_mask,
+                        void* stream);
+
+/*
+ * The staging for hc_load_rows_staged; on any stream, at any time before the
+ * step that consumes it:
+ *   staged_mask[i] = (consider == NULL || consider[i]) && (sub2feat == NULL || sub2feat[i] == -1)
+ *   staged_rows[i] = host_table[ids[i]]      where staged_mask[i]
+ * Rows whose mask is 0 are left unspecified (they may or may not be written).
+ * staged_rows is [n, feat] of host_dtype, contiguous.  stats (int64[3], may be
+ * NULL): [0] += rows copied, [1] += rows skipped because sub2feat[i] != -1.
+ */
+int hc_stage_host_rows(const void* host_table, int32_t host_dtype,
+                       int64_t host_rows, int64_t host_stride, int32_t feat,
+                       const int64_t* ids, const int64_t* sub2feat,
+                       const uint8_t* consider, int64_t n, void* staged_rows,
+                       uint8_t* staged_mask, int64_t* stats, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Multi-GPU table exchange helpers                                         */
 /* ------------------------------------------------------------------------ */

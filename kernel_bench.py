@@ -102,7 +102,7 @@ def bench_bwd_gather(n_dst, deg, n_src, feat, reps, dev="cuda:0"):
     return ms, byts, ms_t
 
 
-def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0", sort_ids=False):
+def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0", sort_ids=False, stage=False):
     """batch.x assembly.  bytes = rows read (F*s each) + rows written (F*s) + 8*n ids (+ 8*n map)."""
     es = 2 if dtype == torch.float16 else 4
     if host and thp:
@@ -130,7 +130,12 @@ def bench_load(n, n_table, feat, dtype, reps, host, thp=False, dev="cuda:0", sor
     if sort_ids:     # requests issued in address order
         pool = [torch.sort(p)[0] for p in pool]
     it = iter(pool * 2)
-    ms = time_launches(lambda: hb.load_rows(table, None, next(it), None, None), reps)
+    if stage:   # the small-grid call that fetches a later batch's rows beside a training step
+        rows = torch.empty((n, feat), dtype=dtype, device=dev)
+        mask = torch.empty(n, dtype=torch.uint8, device=dev)
+        ms = time_launches(lambda: hb.stage_host_rows(table, next(it), None, None, rows, mask), reps)
+    else:
+        ms = time_launches(lambda: hb.load_rows(table, None, next(it), None, None), reps)
     return ms, n * feat * es * 2 + 8 * n
 
 
@@ -162,6 +167,7 @@ def main():
     ap.add_argument("--thp", action="store_true", help="load --host: back the table with 2 MB huge pages")
     ap.add_argument("--reps", type=int, default=10)
     ap.add_argument("--sorted", action="store_true", help="load: row ids in ascending order")
+    ap.add_argument("--stage", action="store_true", help="load: time hc_stage_host_rows (small grid) instead")
     ap.add_argument("--skew", action="store_true",
                     help="neighbours drawn as floor(n_src * u^3) (hub sources) instead of uniformly")
     args = ap.parse_args()
@@ -197,8 +203,8 @@ def main():
                  "fwd_plus_scatter_GBps": round((b_f + b_s) / (ms_f + ms_s) / 1e6, 1)}
     else:
         ms, byts = bench_load(args.dst, args.src, args.feat, dt, args.reps, args.host, args.thp,
-                              sort_ids=args.sorted)
-        extra = {"sorted": args.sorted, "thp": args.thp}
+                              sort_ids=args.sorted, stage=args.stage)
+        extra = {"sorted": args.sorted, "thp": args.thp, "stage": args.stage}
     print(json.dumps({"op": args.op, "dst": args.dst, "deg": args.deg, "src": args.src, "feat": args.feat,
                       "dtype": args.dtype, "host": args.host, "hit_rate": args.hit_rate, "skew": args.skew,
                       "ms": round(ms, 4), "bytes": byts, "GBps": round(byts / ms / 1e6, 1), **extra}))

@@ -278,3 +278,30 @@ def test_autograd_switches_to_gather_for_large_blocks(backend, oracle, monkeypat
     gb, _, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, np.abs(g), hmap=hmap, want_grad_history=False)
     close(xs.grad, want, 1e-5, bound=gb, terms=int(np.bincount(idx, minlength=n_src).max()), label="bwd_gather")
     assert score.cpu().numpy().tobytes() == oracle.score_rows(g).tobytes()
+
+
+def test_shared_transposition_is_rebuilt_for_buffers_refilled_behind_torch(backend, oracle, monkeypatch):
+    """Two batches in the SAME (ptr, idx) tensors, the second written without touching the
+    tensors' version counters (as a library call that fills preallocated outputs does): each
+    declaration gets its own transposition, so the second backward follows the second batch."""
+    monkeypatch.setattr(backend, "DETERMINISTIC_BWD", True)
+    rng = np.random.default_rng(21)
+    num_dst, n_src, feat = 300, 700, 64
+    ptr_a, idx_a = csr_block(rng, num_dst, n_src, 5)
+    ptr_b, idx_b = csr_block(rng, num_dst, n_src, 5)
+    assert idx_a.shape == idx_b.shape and not np.array_equal(idx_a, idx_b)
+    ptr_t, idx_t = cu(ptr_a), cu(idx_a)
+    x = rng.standard_normal((n_src, feat), dtype=np.float32)
+    g = rng.standard_normal((num_dst, feat), dtype=np.float32)
+    for ptr, idx in ((ptr_a, idx_a), (ptr_b, idx_b)):
+        before = (ptr_t._version, idx_t._version)
+        ptr_t.data.copy_(cu(ptr))
+        idx_t.data.copy_(cu(idx))
+        assert (ptr_t._version, idx_t._version) == before
+        backend.declare_batch(ptr_t, idx_t, n_src)
+        xs = cu(x).requires_grad_(True)
+        backend.aggr_forward(xs, ptr_t, idx_t, num_dst).backward(cu(g))
+        want, _, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, g, want_grad_history=False)
+        gb, _, _ = oracle.aggr_bwd(ptr, idx, x, num_dst, np.abs(g), want_grad_history=False)
+        close(xs.grad, want, 1e-5, bound=gb, terms=int(np.bincount(idx, minlength=n_src).max()),
+              label="bwd_gather_shared")

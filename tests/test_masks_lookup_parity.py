@@ -202,3 +202,45 @@ def test_edge_types_follow_node_type_ranges(backend, oracle):
     E = int(b["ptr"][rows])
     assert np.array_equal(got.cpu().numpy()[:E], want)
     assert set(np.unique(want).tolist()) <= {0, 1, 2, 3, 4}
+
+
+@pytest.mark.parametrize("feat,host_dt", [(128, np.float16), (100, np.float32), (64, np.float32), (33, np.float32)])
+@pytest.mark.parametrize("pinned", [False, True])
+def test_load_rows_with_rows_staged_ahead(backend, oracle, feat, host_dt, pinned):
+    """Staging (hc_load_rows without a cache) followed by hc_load_rows_staged gives the oracle's x
+    whatever happened in between: the feature cache may have lost rows since the staging, the used
+    mask may exclude staged rows, and rows that were not staged still come from the host table."""
+    rng = np.random.default_rng(feat + 7 * pinned)
+    N, n = 5000, 2100
+    host = rng.standard_normal((N, feat)).astype(host_dt)
+    cache = rng.standard_normal((300, feat)).astype(host_dt)
+    sub_to_full = rng.choice(N, size=n, replace=False).astype(np.int64)
+    in_cache_then = np.where(rng.random(n) < 0.4, rng.integers(0, 300, size=n), -1).astype(np.int64)
+    valid = rng.random(n) < 0.9
+    ht = torch.from_numpy(host)
+    ht = ht.pin_memory() if pinned else ht.cuda()
+    rows = torch.full((n, feat), 7, dtype=ht.dtype, device="cuda")
+    smask = torch.zeros(n, dtype=torch.uint8, device="cuda")
+    st = torch.zeros(3, dtype=torch.int64, device="cuda")
+    backend.stage_host_rows(ht, cu(sub_to_full), cu(in_cache_then), cu(valid), rows, smask, stats=st)
+    want_staged = valid & (in_cache_then == -1)
+    assert np.array_equal(smask.cpu().numpy().astype(bool), want_staged)
+    assert np.array_equal(rows.cpu().numpy()[want_staged], host[sub_to_full[want_staged]])
+    assert st.tolist()[0] == int(want_staged.sum())
+    # by the time of the step a third of the cached rows are gone and the used mask is known
+    in_cache_now = np.where(rng.random(n) < 0.33, -1, in_cache_then).astype(np.int64)
+    used = rng.random(n) < 0.7
+    stats = torch.zeros(3, dtype=torch.int64, device="cuda")
+    x, mask = backend.load_rows(ht, cu(cache), cu(sub_to_full), cu(in_cache_now), cu(used), want_mask=True,
+                                stats=stats, staged=(rows, smask))
+    want_x, want_mask = oracle.load_rows(host, cache, sub_to_full, in_cache_now, used)
+    assert np.array_equal(mask.cpu().numpy(), want_mask)
+    assert np.array_equal(x.float().cpu().numpy(), want_x.astype(np.float32))
+    from_staged = int((want_mask & want_staged).sum())
+    assert stats.tolist() == [int(want_mask.sum()) - from_staged, int((in_cache_now != -1).sum()), from_staged]
+    # nothing staged at all is the plain call
+    smask.zero_()
+    x0 = backend.load_rows(ht, cu(cache), cu(sub_to_full), cu(in_cache_now), cu(used), staged=(rows, smask))
+    assert torch.equal(x0, x)
+    with pytest.raises(ValueError):
+        backend.load_rows(ht, cu(cache), cu(sub_to_full), cu(in_cache_now), cu(used), staged=(rows[:-1], smask))
