@@ -65,7 +65,7 @@ def parse():
                          "one GPU, two captured segments around the eager gradient all-reduce on several")
     ap.add_argument("--look-ahead", default="on", choices=["on", "off"],
                     help="the captured step fetches the next batch's host feature rows beside its compute")
-    ap.add_argument("--graph-slack", type=float, default=1.0,
+    ap.add_argument("--graph-slack", type=float, default=1.03,
                     help="fixed shape = this factor x the largest layer sizes of --graph-calibrate probe batches")
     ap.add_argument("--graph-calibrate", type=int, default=64)
     ap.add_argument("--min-timed-s", type=float, default=2.0,
@@ -318,6 +318,8 @@ def run_ours(args):
     # `value` is the median region.
     K = args.steps
     use_graph = args.graph == "on" or (args.graph == "auto" and GRAPH_BY_DEFAULT)
+    if use_graph and world > 1 and trainer.table.exchange != "peer":
+        use_graph = False       # the all-to-all exchange issues collectives inside the step: never captured
     caps = ecap = None
     if use_graph:
         caps, ecap = loader.calibrate(args.graph_calibrate, slack=args.graph_slack, align=128)
@@ -410,6 +412,24 @@ def run_ours(args):
         ms_r, _, _ = _region(trainer, timed_host[r], world, device, barrier, feed=blocking)
         blk_ms.append(max_over_ranks(ms_r))
     clocks = sampler.stop()
+
+    # the look-ahead's staging call on its own (it normally runs beside a step)
+    stage_ms = None
+    ah = getattr(trainer.graphed, "ahead", None) if use_graph else None
+    if ah is not None:
+        t_st = []
+        for b in timed[0][:10]:
+            if b.mask is None:
+                continue
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            trainer.table.stage_host_rows(b.sub_to_full, b.mask, ah.rows, ah.mask)
+            e1.record()
+            t_st.append((e0, e1))
+        torch.cuda.synchronize()
+        if t_st:
+            stage_ms = statistics.median(a.elapsed_time(b) for a, b in t_st)
+        ah.announced = None     # what is staged now belongs to no announced batch
 
     # ---- the same step with the batch sampled inside it (hc_sample_* / hc_relabel kernels)
     n_samp = min(max(K, 30), 200)
@@ -582,6 +602,8 @@ def run_ours(args):
             "rows_read_in_the_step_per_step": round(stats[0] / steps_value, 1),
             "fetched_in_vain_frac": round((staged[0] - stats[2]) / max(staged[0], 1), 4),
             "host_link_bytes_per_step": int((staged[0] + stats[0]) / steps_value * feat_bytes),
+            "staging_call_alone_ms": round(stage_ms, 4) if stage_ms else None,
+            "staging_blocks": hb.STAGE_BLOCKS or 16,
             "value_without": round(world * K / (statistics.median(plain_ms) * 1e-3), 2) if plain_ms else None,
             "note": "the captured step fetches the NEXT batch's host feature rows on a second branch beside "
                     "its own compute (hiscache/graphed.py); rows whose consumers turn out to be served from "

@@ -35,11 +35,13 @@ class _LookAhead:
     cleared whenever the batch that arrives is not the one that was announced.
     """
 
-    def __init__(self, table, n_rows, device):
+    def __init__(self, table, caps, edge_cap, device):
         buf = table.uvm.buffer
         self.table = table
-        self.ids = torch.zeros(n_rows, dtype=torch.int64, device=device)
-        self.valid = torch.zeros(n_rows, dtype=torch.bool, device=device)
+        n_rows = int(caps[-1])
+        # static copy of the announced batch (only its ids and its row mask are read)
+        self.next = Batch.fixed_shape(caps, edge_cap, device=device)
+        self.ids, self.valid = self.next.sub_to_full, self.next.mask
         self.rows = torch.zeros((n_rows, buf.shape[1]), dtype=buf.dtype, device=device)
         self.mask = torch.zeros(n_rows, dtype=torch.uint8, device=device)
         self.side = torch.cuda.Stream(device=device)
@@ -77,8 +79,11 @@ class _LookAhead:
         if self.announced is not batch:
             self.mask.zero_()
         if next_batch is not None and fits(next_batch):
-            self.ids.copy_(next_batch.sub_to_full, non_blocking=True)
-            self.valid.copy_(next_batch.mask, non_blocking=True)
+            if next_batch.packed is not None and next_batch.packed.numel() == self.next.packed.numel():
+                self.next.packed.copy_(next_batch.packed, non_blocking=True)
+            else:
+                self.ids.copy_(next_batch.sub_to_full, non_blocking=True)
+                self.valid.copy_(next_batch.mask, non_blocking=True)
             self.announced = next_batch
         else:
             self.valid.zero_()
@@ -93,16 +98,11 @@ class GraphedStep:
         self.caps, self.edge_cap = list(caps), int(edge_cap)
         dev = trainer.device
         L = len(self.caps) - 1
-        self.ahead = (_LookAhead(trainer.table, self.caps[L], dev)
+        self.ahead = (_LookAhead(trainer.table, self.caps, self.edge_cap, dev)
                       if look_ahead and _LookAhead.usable(trainer.table) else None)
-        b = Batch()
-        b.ptr = torch.zeros(self.caps[L - 1] + 1, dtype=torch.int64, device=dev)
-        b.idx = torch.zeros(self.edge_cap, dtype=torch.int64, device=dev)
-        b.sub_to_full = torch.zeros(self.caps[L], dtype=torch.int64, device=dev)
-        b.mask = torch.zeros(self.caps[L], dtype=torch.bool, device=dev)
-        b.y = torch.full((self.caps[0],), -100, dtype=torch.int64, device=dev)
-        b.num_node_in_layer = torch.tensor(self.caps, dtype=torch.int64)
-        b.num_edge_in_layer = torch.tensor([self.edge_cap] * L, dtype=torch.int64)
+        self.opt_stream = torch.cuda.Stream(device=dev)      # optimiser step beside the history update
+        b = Batch.fixed_shape(self.caps, self.edge_cap, device=dev)
+        b.y.fill_(-100)
         self.static = b
         self.loss = None
         # warm-up on a side stream (allocator, lazily created state, scratch buffers)
@@ -127,9 +127,9 @@ class GraphedStep:
 
     def _body(self):
         if self.ahead is None:
-            return self.trainer._step_body(self.static)
+            return self.trainer._step_body(self.static, opt_stream=self.opt_stream)
         with self.ahead:
-            return self.trainer._step_body(self.static, after_load=self.ahead.fork)
+            return self.trainer._step_body(self.static, after_load=self.ahead.fork, opt_stream=self.opt_stream)
 
     enabled = True      # set False to make every batch take the eager step (e.g. for per-kernel timing)
 
@@ -139,12 +139,7 @@ class GraphedStep:
                 and batch.idx.shape[0] == self.edge_cap)
 
     def _load(self, batch):
-        st = self.static
-        st.ptr.copy_(batch.ptr, non_blocking=True)
-        st.idx.copy_(batch.idx, non_blocking=True)
-        st.sub_to_full.copy_(batch.sub_to_full, non_blocking=True)
-        st.mask.copy_(batch.mask, non_blocking=True)
-        st.y.copy_(batch.y, non_blocking=True)
+        self.static.copy_from(batch)        # one copy when the batch is packed (Batch.fixed_shape)
 
     def run(self, batch, next_batch=None):
         self._load(batch)
@@ -179,13 +174,16 @@ class GraphedSampledStep:
     sampler (hc_sample_fixed) needs no host read-back, so it is captured with
     `trainer._step_body`; a replay draws a batch and trains with a single launch.
 
-    With look_ahead the graph is software-pipelined by one batch: a replay trains on the batch
-    the previous replay drew, while a second branch draws the next one and then (once the current
-    batch's rows are assembled) fetches its host feature rows:
+    With look_ahead the graph is software-pipelined by two batches, on three branches: a replay
+    trains on batch k, fetches the host feature rows of batch k+1 (drawn by the previous replay)
+    once its own rows are assembled, and draws batch k+2:
 
-        main   cur <- next | lookup, load (staged rows) | forward ... admission
-        side               | sample(next) ..............| stage(next) ----------> join
+        main    cur <- near <- far | lookup, load (staged rows) | forward ... admission
+        side 1                     | draw(far) ---------------------------------------> join
+        side 2                                                  | stage(near) --------> join
     """
+
+    _KEYS = ("ptr", "idx", "sub_to_full", "mask", "y")
 
     def __init__(self, trainer, loader, caps, edge_cap, warmup=2, look_ahead=True):
         import hiscache_backend as hb
@@ -196,19 +194,21 @@ class GraphedSampledStep:
         self.seeds = _SeedWindow(loader, min(loader.batch_size, self.caps[0]))
         self.sampler = loader.sampler
         self.fixed = None
-        self.ahead = (_LookAhead(trainer.table, self.caps[L], dev)
+        self.ahead = (_LookAhead(trainer.table, self.caps, self.edge_cap, dev)
                       if look_ahead and _LookAhead.usable(trainer.table) else None)
+        self.draw_stream = torch.cuda.Stream(device=dev) if self.ahead is not None else None
+        self.opt_stream = torch.cuda.Stream(device=dev)
         s = torch.cuda.Stream(device=dev)
         s.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(s):
             if self.ahead is not None:
+                # the two batches in front of the first body: `near` (trained first) and `far`
                 self.seeds.advance()
-                self.next = self._draw()         # the batch the first body trains on
-                self.cur = Batch()
-                for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
-                    setattr(self.cur, k, torch.empty_like(getattr(self.next, k)))
-                self.cur.num_node_in_layer = self.next.num_node_in_layer
-                self.cur.num_edge_in_layer = self.next.num_edge_in_layer
+                self.far = self._draw()
+                self.near, self.cur = self._like(self.far), self._like(self.far)
+                self._copy(self.near, self.far)
+                self.seeds.advance()
+                self.far = self._draw()
             for _ in range(max(1, warmup)):
                 self.seeds.advance()
                 self._body()
@@ -220,25 +220,40 @@ class GraphedSampledStep:
             self.loss = self._body()
         self.library_kernels_per_step = hb.launch_count() - before
         self.counters = self.fixed["counters"]
-        # the capture ran nothing: `next` and the staged rows are still those of the last warm-up body
+        # the capture ran nothing: near / far and the staged rows are those the last warm-up body left
 
     def _draw(self):
         b = self.sampler.sample_fixed(self.seeds.static, self.caps, self.edge_cap, out=self.fixed)
         self.fixed = b.fixed
         return b
 
+    def _like(self, b):
+        c = Batch()
+        for k in self._KEYS:
+            setattr(c, k, torch.empty_like(getattr(b, k)))
+        c.num_node_in_layer, c.num_edge_in_layer = b.num_node_in_layer, b.num_edge_in_layer
+        return c
+
+    def _copy(self, dst, src):
+        for k in self._KEYS:
+            getattr(dst, k).copy_(getattr(src, k), non_blocking=True)
+
     def _body(self):
         tr, ah = self.trainer, self.ahead
         if ah is None:
-            return tr._step_body(self._draw())
-        cur, nxt = self.cur, self.next
-        for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
-            getattr(cur, k).copy_(getattr(nxt, k), non_blocking=True)
-        ah.side.wait_stream(torch.cuda.current_stream(ah.device))
-        with torch.cuda.stream(ah.side):
-            self.next = nxt = self._draw()      # overwrites the buffers `cur` was copied from
+            return tr._step_body(self._draw(), opt_stream=self.opt_stream)
+        cur, near = self.cur, self.near
+        self._copy(cur, near)
+        self._copy(near, self.far)
+        main = torch.cuda.current_stream(ah.device)
+        self.draw_stream.wait_stream(main)
+        with torch.cuda.stream(self.draw_stream):
+            self.far = self._draw()             # overwrites the buffers `near` was copied from
         with ah:
-            return tr._step_body(cur, after_load=lambda: ah.fork(nxt.sub_to_full, nxt.mask))
+            loss = tr._step_body(cur, after_load=lambda: ah.fork(near.sub_to_full, near.mask),
+                                 opt_stream=self.opt_stream)
+        main.wait_stream(self.draw_stream)
+        return loss
 
     def run(self):
         self.seeds.advance()
@@ -267,20 +282,19 @@ class GraphedDataParallelStep:
     def __init__(self, trainer, caps, edge_cap, warmup_batches, look_ahead=True):
         import hiscache_backend as hb
         self.trainer = tr = trainer
+        if tr.world > 1 and tr.table.exchange != "peer":
+            # the all-to-all form of the exchange issues collectives inside lookup and admission,
+            # and a collective must never be part of a capture
+            raise RuntimeError("the captured data-parallel step needs the peer-memory history exchange")
         self.caps, self.edge_cap = list(caps), int(edge_cap)
         dev = tr.device
         L = len(self.caps) - 1
+        self.opt_stream = torch.cuda.Stream(device=dev)
         # the look-ahead branch joins at the end of segment A, before the all-reduce
-        self.ahead = (_LookAhead(tr.table, self.caps[L], dev)
+        self.ahead = (_LookAhead(tr.table, self.caps, self.edge_cap, dev)
                       if look_ahead and _LookAhead.usable(tr.table) else None)
-        b = Batch()
-        b.ptr = torch.zeros(self.caps[L - 1] + 1, dtype=torch.int64, device=dev)
-        b.idx = torch.zeros(self.edge_cap, dtype=torch.int64, device=dev)
-        b.sub_to_full = torch.zeros(self.caps[L], dtype=torch.int64, device=dev)
-        b.mask = torch.zeros(self.caps[L], dtype=torch.bool, device=dev)
-        b.y = torch.full((self.caps[0],), -100, dtype=torch.int64, device=dev)
-        b.num_node_in_layer = torch.tensor(self.caps, dtype=torch.int64)
-        b.num_edge_in_layer = torch.tensor([self.edge_cap] * L, dtype=torch.int64)
+        b = Batch.fixed_shape(self.caps, self.edge_cap, device=dev)
+        b.y.fill_(-100)
         self.static = b
         # one flat gradient whose slices are the parameters' .grad for good
         self.flat = torch.zeros(sum(tr._numels), dtype=torch.float32, device=dev)
@@ -336,10 +350,16 @@ class GraphedDataParallelStep:
         return tr.table.prepare_update(self.static, tr.glb_iter)
 
     def _segment_b(self, pending):
+        """Optimiser step and owner-side admission side by side: the first reads the reduced
+        gradient and writes parameters, the second reads the published areas and writes the shard."""
         tr = self.trainer
-        tr.optimizer.step()
+        main = torch.cuda.current_stream(tr.device)
+        self.opt_stream.wait_stream(main)
+        with torch.cuda.stream(self.opt_stream):
+            tr.optimizer.step()
         if pending:
             tr.table.finish_update(fence=False)
+        main.wait_stream(self.opt_stream)
 
     enabled = True      # set False to make every batch take the eager step (e.g. for per-kernel timing)
 
@@ -349,12 +369,7 @@ class GraphedDataParallelStep:
                 and batch.idx.shape[0] == self.edge_cap)
 
     def _load(self, batch):
-        st = self.static
-        st.ptr.copy_(batch.ptr, non_blocking=True)
-        st.idx.copy_(batch.idx, non_blocking=True)
-        st.sub_to_full.copy_(batch.sub_to_full, non_blocking=True)
-        st.mask.copy_(batch.mask, non_blocking=True)
-        st.y.copy_(batch.y, non_blocking=True)
+        self.static.copy_from(batch)        # one copy when the batch is packed (Batch.fixed_shape)
 
     def run(self, batch, next_batch=None):
         tr = self.trainer

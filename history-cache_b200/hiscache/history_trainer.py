@@ -121,10 +121,13 @@ class HistoryTrainer:
         self.glb_iter += 1
         return loss
 
-    def _step_body(self, batch, reset=False, after_load=None):
+    def _step_body(self, batch, reset=False, after_load=None, opt_stream=None):
         """Everything of one iteration that runs on the device; with reset=False it contains no
         host-side decision and can be captured in a CUDA graph.  `after_load` is called once the
-        batch's input rows have been assembled (the captured step forks its look-ahead there)."""
+        batch's input rows have been assembled (the captured step forks its look-ahead there).
+        `opt_stream`: the optimiser step runs there, beside the history update (they share no
+        data: one reads gradients and writes parameters, the other reads the produced embeddings
+        and their scores and writes the table); both are joined before the body returns."""
         self.optimizer.zero_grad(set_to_none=True)
         self.table.lookup_and_load(batch, len(self.model.convs))
         if after_load is not None:
@@ -132,8 +135,17 @@ class HistoryTrainer:
         out = self.model(batch)
         loss = self.loss_fn(out, batch.y)
         loss.backward()
-        self.optimizer.step()
+        if opt_stream is None:
+            self.optimizer.step()
+            self.table.update_history(batch, self.glb_iter, reset=reset)
+            return loss
+        main = torch.cuda.current_stream(self.device)
+        opt_stream.wait_stream(main)
+        with torch.cuda.stream(opt_stream):
+            # touches parameters, optimiser state and the gradients, which all outlive the join
+            self.optimizer.step()
         self.table.update_history(batch, self.glb_iter, reset=reset)
+        main.wait_stream(opt_stream)
         return loss
 
     def enable_cuda_graph(self, caps, edge_cap, warmup_batches, look_ahead=True):

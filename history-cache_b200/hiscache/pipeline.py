@@ -42,6 +42,13 @@ class HostBatchPipeline:
               "mask": torch.bool}
         self.slots = [{k: torch.empty(max(cap[k], 1), dtype=dt[k], device=self.dev) for k in _KEYS}
                       for _ in range(self.depth)]
+        # fixed-shape batches travel as one buffer (sampler.Batch.fixed_shape): one copy per batch
+        ref = next((b for b in host_batches if getattr(b, "packed", None) is not None), None)
+        self.packed_slots, self._shape = None, None
+        if ref is not None:
+            self._shape = ([int(v) for v in ref.num_node_in_layer], int(ref.idx.shape[0]))
+            self.packed_slots = [torch.empty(ref.packed.numel(), dtype=torch.uint8, device=self.dev)
+                                 for _ in range(self.depth)]
         self.copied = [torch.cuda.Event() for _ in range(self.depth)]
         self.consumed = [None] * self.depth
         self.loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(self.depth)]
@@ -54,6 +61,12 @@ class HostBatchPipeline:
         cs = self.copy_stream
         if self.consumed[slot] is not None:
             cs.wait_event(self.consumed[slot])      # the step that used this slot has finished
+        pk = getattr(hbatch, "packed", None)
+        if pk is not None and self.packed_slots is not None and pk.numel() == self.packed_slots[slot].numel():
+            with torch.cuda.stream(cs):
+                self.packed_slots[slot].copy_(pk, non_blocking=True)
+                self.copied[slot].record(cs)
+            return Batch.fixed_shape(self._shape[0], self._shape[1], packed=self.packed_slots[slot])
         b = Batch()
         with torch.cuda.stream(cs):
             for k in _KEYS:

@@ -20,9 +20,24 @@ import math
 import torch
 
 
+def fixed_layout(caps, edge_cap):
+    """Byte offsets of a fixed-shape batch's five arrays inside ONE buffer, so that such a batch
+    moves (host -> device, or into a captured step's static input) with a single copy:
+    {name: (offset, numel, dtype)}, total bytes.  Every array starts on a 16-byte boundary."""
+    L = len(caps) - 1
+    spec = (("ptr", int(caps[L - 1]) + 1, torch.int64), ("idx", int(edge_cap), torch.int64),
+            ("sub_to_full", int(caps[L]), torch.int64), ("y", int(caps[0]), torch.int64),
+            ("mask", int(caps[L]), torch.bool))
+    lay, off = {}, 0
+    for name, numel, dt in spec:
+        lay[name] = (off, numel, dt)
+        off += -(-numel * torch.empty(0, dtype=dt).element_size() // 16) * 16
+    return lay, off
+
+
 class Batch:
     __slots__ = ("ptr", "idx", "sub_to_full", "y", "num_node_in_layer", "num_edge_in_layer", "x",
-                 "edge_type", "typed_num_node_in_layer", "mask", "counters", "fixed")
+                 "edge_type", "typed_num_node_in_layer", "mask", "counters", "fixed", "packed")
 
     def __init__(self):
         self.x = None
@@ -31,24 +46,52 @@ class Batch:
         self.mask = None
         self.counters = None
         self.fixed = None
+        self.packed = None      # fixed-shape batches: the one buffer the five arrays are views of
+
+    @staticmethod
+    def fixed_shape(caps, edge_cap, device=None, packed=None):
+        """A fixed-shape batch whose arrays are views of one byte buffer (`packed`, allocated
+        zero-filled on `device` unless given)."""
+        lay, total = fixed_layout(caps, edge_cap)
+        if packed is None:
+            packed = torch.zeros(total, dtype=torch.uint8, device=device)
+        assert packed.numel() == total and packed.dtype == torch.uint8
+        b = Batch()
+        b.packed = packed
+        for name, (off, numel, dt) in lay.items():
+            nbytes = numel * torch.empty(0, dtype=dt).element_size()
+            setattr(b, name, packed[off:off + nbytes].view(dt))
+        L = len(caps) - 1
+        b.num_node_in_layer = torch.tensor([int(c) for c in caps], dtype=torch.int64)
+        b.num_edge_in_layer = torch.tensor([int(edge_cap)] * L, dtype=torch.int64)
+        return b
+
+    def _moved(self, move):
+        if self.packed is not None:
+            b = Batch.fixed_shape([int(v) for v in self.num_node_in_layer], self.idx.shape[0],
+                                  packed=move(self.packed))
+            return b
+        b = Batch()
+        for k in ("ptr", "idx", "sub_to_full", "y"):
+            setattr(b, k, move(getattr(self, k)))
+        if self.mask is not None:
+            b.mask = move(self.mask)
+        b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
+        return b
 
     def to(self, device, non_blocking=True):
-        b = Batch()
-        for k in ("ptr", "idx", "sub_to_full", "y"):
-            setattr(b, k, getattr(self, k).to(device, non_blocking=non_blocking))
-        if self.mask is not None:
-            b.mask = self.mask.to(device, non_blocking=non_blocking)
-        b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
-        return b
+        return self._moved(lambda t: t.to(device, non_blocking=non_blocking))
 
     def pin(self):
-        b = Batch()
-        for k in ("ptr", "idx", "sub_to_full", "y"):
-            setattr(b, k, getattr(self, k).cpu().pin_memory())
-        if self.mask is not None:
-            b.mask = self.mask.cpu().pin_memory()
-        b.num_node_in_layer, b.num_edge_in_layer = self.num_node_in_layer, self.num_edge_in_layer
-        return b
+        return self._moved(lambda t: t.cpu().pin_memory())
+
+    def copy_from(self, src, non_blocking=True):
+        """Overwrites this batch's arrays with src's (same shapes): one copy when both are packed."""
+        if self.packed is not None and src.packed is not None and self.packed.numel() == src.packed.numel():
+            self.packed.copy_(src.packed, non_blocking=non_blocking)
+            return
+        for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
+            getattr(self, k).copy_(getattr(src, k), non_blocking=non_blocking)
 
     def nbytes(self):
         keys = ("ptr", "idx", "sub_to_full", "y") + (("mask",) if self.mask is not None else ())
@@ -153,8 +196,8 @@ class NeighborSampler:
         batch_seed = hb.mix64(self.seed * 1_000_003 + self.batch_no)
         self.batch_no += 1
         hb.relabel_seed(seeds, self.local)
-        sub = torch.zeros(caps[L], dtype=torch.int64, device=dev)
-        mask = torch.zeros(caps[L], dtype=torch.bool, device=dev)
+        b = Batch.fixed_shape(caps, edge_cap, device=dev)       # one zero-filled buffer, five views
+        sub, mask = b.sub_to_full, b.mask
         counts = torch.zeros(caps[L - 1], dtype=torch.int64, device=dev)
         sub[:seeds.shape[0]] = seeds
         mask[:seeds.shape[0]] = True
@@ -179,16 +222,10 @@ class NeighborSampler:
         hb.relabel_reset(torch.cat(real), self.local)
         if not fits:
             return None
-        b = Batch()
-        b.sub_to_full, b.mask = sub, mask
-        b.ptr = torch.zeros(caps[L - 1] + 1, dtype=torch.int64, device=dev)
         torch.cumsum(counts, 0, out=b.ptr[1:])
-        b.idx = torch.zeros(edge_cap, dtype=torch.int64, device=dev)
         b.idx[:n_edges] = torch.cat(idxs)
-        b.y = torch.full((caps[0],), -100, dtype=torch.int64, device=dev)
+        b.y.fill_(-100)
         b.y[:seeds.shape[0]] = g.labels[seeds]
-        b.num_node_in_layer = torch.tensor(list(caps), dtype=torch.int64)
-        b.num_edge_in_layer = torch.tensor([edge_cap] * L, dtype=torch.int64)
         return b
 
     @torch.no_grad()

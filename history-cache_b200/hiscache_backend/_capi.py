@@ -104,7 +104,7 @@ _SIGS = {
     "hc_gather_rows": (C.c_int, [vp, i32, i64, i64, i32, vp, i64, i32, vp, i32, i64, vp]),
     "hc_load_rows": (C.c_int, [vp, i32, i64, i64, vp, i32, i64, i64, i32, vp, vp, vp, i64, vp,
                                i32, i64, vp, vp, vp]),
-    "hc_stage_host_rows": (C.c_int, [vp, i32, i64, i64, i32, vp, vp, vp, i64, vp, vp, vp, vp]),
+    "hc_stage_host_rows": (C.c_int, [vp, i32, i64, i64, i32, vp, vp, vp, i64, vp, vp, vp, i32, vp]),
     "hc_load_rows_staged": (C.c_int, [vp, i32, i64, i64, vp, i32, i64, i64, i32, vp, vp, vp, i64, vp,
                                       i32, i64, vp, vp, vp, vp, vp]),
     "hc_norm_scratch_bytes": (i64, [i32]),

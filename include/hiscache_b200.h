@@ -467,12 +467,17 @@ int hc_load_rows_staged(const void* host_table, int32_t host_dtype,
  * Rows whose mask is 0 are left unspecified (they may or may not be written).
  * staged_rows is [n, feat] of host_dtype, contiguous.  stats (int64[3], may be
  * NULL): [0] += rows copied, [1] += rows skipped because sub2feat[i] != -1.
+ * The call is meant to run beside a training step and therefore uses a small
+ * grid (the more host reads are outstanding, the more the step's own kernels
+ * are slowed down); max_blocks > 0 overrides the default number of thread
+ * blocks (16).
  */
 int hc_stage_host_rows(const void* host_table, int32_t host_dtype,
                        int64_t host_rows, int64_t host_stride, int32_t feat,
                        const int64_t* ids, const int64_t* sub2feat,
                        const uint8_t* consider, int64_t n, void* staged_rows,
-                       uint8_t* staged_mask, int64_t* stats, void* stream);
+                       uint8_t* staged_mask, int64_t* stats, int32_t max_blocks,
+                       void* stream);
 
 /* ------------------------------------------------------------------------ */
 /* Multi-GPU table exchange helpers                                         */

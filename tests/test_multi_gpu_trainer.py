@@ -16,7 +16,7 @@ ROOT = os.path.dirname(HERE)
 STEPS = 10
 
 
-def _train_worker(rank, world, port, exchange, deterministic, q):
+def _train_worker(rank, world, port, exchange, deterministic, q, graph_mode=None):
     sys.path.insert(0, os.path.join(ROOT, "history-cache_b200"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     if deterministic:      # every aggregation backward takes the fixed-order gather
@@ -47,10 +47,33 @@ def _train_worker(rank, world, port, exchange, deterministic, q):
                 yield from tr.loader.train_loader
         it = epochs()
         losses, hits = [], []
-        for _ in range(STEPS):
-            b = next(it)
-            losses.append(float(tr.train_step(b).detach()))
-            hits.append(int((tr.table.sub2embed != -1).sum()))
+        staged_rows = None
+        if graph_mode is None:
+            for _ in range(STEPS):
+                b = next(it)
+                losses.append(float(tr.train_step(b).detach()))
+                hits.append(int((tr.table.sub2embed != -1).sum()))
+        else:
+            # the step replayed from two captured segments around the eager all-reduce, with
+            # ("ahead") or without ("plain") the branch that fetches the next batch's host rows
+            caps, ecap = tr.loader.calibrate(10, slack=1.3, align=64)
+            caps = [int(v) for v in caps]
+            both_caps = torch.tensor(caps + [int(ecap)], device=dev)
+            dist.all_reduce(both_caps, op=dist.ReduceOp.MAX)     # one shape for all ranks
+            caps, ecap = both_caps[:-1].tolist(), int(both_caps[-1])
+            itp = tr.loader.iterate_padded(1 << 30, caps, ecap)
+            pool = [next(itp) for _ in range(STEPS + 5)]
+            for b in pool[:3]:
+                tr.train_step(b)
+            tr.enable_cuda_graph(caps, ecap, pool[3:5], look_ahead=graph_mode == "ahead")
+            assert (tr.graphed.ahead is not None) == (graph_mode == "ahead")
+            tr.table.load_stats.zero_()
+            steps = pool[5:]
+            for i, b in enumerate(steps):
+                nxt = steps[i + 1] if i + 1 < len(steps) else None
+                losses.append(float(tr.train_step(b, nxt).detach()))
+                hits.append(int((tr.table.sub2embed != -1).sum()))
+            staged_rows = tr.table.load_stats.tolist()[2]
         torch.cuda.synchronize()
         flat = torch.cat([p.detach().flatten() for p in tr.model.parameters()])
         # replicas identical: every rank holds the same parameters
@@ -59,7 +82,7 @@ def _train_worker(rank, world, port, exchange, deterministic, q):
         same = all(torch.equal(both[0], x) for x in both)
         owned = torch.nonzero(tr.table.table.full_to_slot != -1).flatten().cpu().numpy()
         res = dict(losses=losses, hits=hits, same=same, owned=owned, params=flat.cpu().numpy(),
-                   overflow=tr.table.table.overflow_count, header=tr.table.header)
+                   overflow=tr.table.table.overflow_count, header=tr.table.header, staged_rows=staged_rows)
         tr.table.table.close()
         return res
 
@@ -69,9 +92,15 @@ def _train_worker(rank, world, port, exchange, deterministic, q):
     dist.destroy_process_group()
 
 
-def _run(world, exchange, port, deterministic=False):
+def _graph_worker(rank, world, port, exchange, graph_mode, q):
+    _train_worker(rank, world, port, exchange, True, q, graph_mode=graph_mode)
+
+
+def _run(world, exchange, port, deterministic=False, graph_mode=None):
     sys.path.insert(0, HERE)
     from _mp import run_ranks
+    if graph_mode is not None:
+        return run_ranks(_graph_worker, world, (port, exchange, graph_mode), timeout=300)
     return run_ranks(_train_worker, world, (port, exchange, deterministic), timeout=300)
 
 
@@ -125,4 +154,24 @@ def test_two_ranks_reproducible_step_makes_both_exchanges_identical():
         assert a["hits"] == b["hits"]
         assert set(a["owned"].tolist()) == set(b["owned"].tolist())
         assert a["losses"] == b["losses"]
+        assert np.array_equal(a["params"], b["params"])
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_captured_step_with_look_ahead_equals_the_one_without(world):
+    """The data-parallel step replayed from its two captured segments, with and without the
+    branch that fetches the next batch's host feature rows beside segment A: the rows a step
+    trains on are the same, so (fixed-order backward) the runs are identical bit for bit."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    base = 30500 + os.getpid() % 50 + 120 * world
+    plain = _run(world, "peer", base, graph_mode="plain")
+    ahead = _run(world, "peer", base + 60, graph_mode="ahead")
+    _check(plain)
+    _check(ahead)
+    for a, b in zip(plain, ahead):
+        assert a["staged_rows"] == 0 and b["staged_rows"] > 0
+        assert a["hits"] == b["hits"]
+        assert a["losses"] == b["losses"]
+        assert set(a["owned"].tolist()) == set(b["owned"].tolist())
         assert np.array_equal(a["params"], b["params"])
