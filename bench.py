@@ -442,15 +442,15 @@ def run_ours(args):
         samp_note = ("sampling (hc_sample_fixed, no host read-back) and the step replayed as ONE CUDA graph; "
                      "seeds are windows of a shuffled order of the training nodes")
     elif use_graph:
-        itf = loader.iterate_fixed(1 << 30, caps, ecap, reuse=4)
+        itf = loader.iterate_fixed(1 << 30, caps, ecap, reuse=4, stream=torch.cuda.Stream(device=device))
         drawn = [next(itf)]
 
         def samp_feed(xs):
             for _ in xs:
                 drawn.append(next(itf))
                 trainer.train_step(drawn.pop(0), drawn[0])
-        samp_note = ("each step samples its batch with the device-side fixed-shape sampler (hc_sample_fixed, "
-                     "no host read-back) and replays the captured segments")
+        samp_note = ("each step's batch is drawn by the device-side fixed-shape sampler (hc_sample_fixed, no host "
+                     "read-back) on the loader's own stream, two batches ahead, beside the captured segments")
     else:
         samp_feed = lambda xs: [trainer.train_step(next(it)) for _ in xs]
     samp_feed([None] * 3)

@@ -271,8 +271,15 @@ class GraphedDataParallelStep:
                     publish of the admission candidates
         eager       all-reduce (average) of the flat gradient: the collective that also tells every
                     owner that all ranks have published and finished their lookups
-        segment B   optimiser step, owner-side eviction + admission, iteration counter
+        segment B   optimiser step beside owner-side eviction + admission, iteration counter
         eager       the table's fence (orders the admission before the next step's lookups)
+
+    The look-ahead (host feature rows of the announced next batch) does not live inside a segment
+    here: segment A alone is shorter than the fetch.  It is issued eagerly on a stream of its own
+    before segment A is launched, and runs beside segment A, the all-reduce and segment B.  It
+    writes the staging buffer of the other parity, so segment A exists in two captured variants
+    (one per staging buffer) that share their memory pool; the next step waits for the fetch
+    before it launches its segment A.
 
     Every rank replays the same two graphs around the same two collectives, whether its batch fits
     the fixed shape or not (a batch that does not fit takes the eager step, which issues the same
@@ -290,9 +297,12 @@ class GraphedDataParallelStep:
         dev = tr.device
         L = len(self.caps) - 1
         self.opt_stream = torch.cuda.Stream(device=dev)
-        # the look-ahead branch joins at the end of segment A, before the all-reduce
         self.ahead = (_LookAhead(tr.table, self.caps, self.edge_cap, dev)
                       if look_ahead and _LookAhead.usable(tr.table) else None)
+        self.parity = 0
+        if self.ahead is not None:      # staging buffers by step parity
+            self.rows = [self.ahead.rows, torch.zeros_like(self.ahead.rows)]
+            self.masks = [self.ahead.mask, torch.zeros_like(self.ahead.mask)]
         b = Batch.fixed_shape(self.caps, self.edge_cap, device=dev)
         b.y.fill_(-100)
         self.static = b
@@ -321,29 +331,46 @@ class GraphedDataParallelStep:
         before = hb.launch_count()
         self.graph_a = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_a):
-            self._segment_a()
+            self._segment_a(0)
         self.graph_b = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph_b, pool=self.graph_a.pool()):
             self._segment_b(True)
         self.library_kernels_per_step = hb.launch_count() - before
-        # the two captures recorded a step without running it: nothing was published or admitted
-        if self.ahead is not None:      # nothing is staged for the first replay
-            self.ahead.mask.zero_()
-            self.ahead.valid.zero_()
+        self.graphs_a = [self.graph_a]
+        # what a replay of a variant leaves behind for the host (the loss, the lookup results the
+        # table exposes) are tensors of that variant's capture: they are kept per variant, which
+        # also keeps their memory out of the other variant's capture
+        self._outputs = [self._snapshot()]
+        if self.ahead is not None:
+            g1 = torch.cuda.CUDAGraph()     # the same segment reading the other staging buffer
+            with torch.cuda.graph(g1, pool=self.graph_a.pool()):
+                self._segment_a(1)
+            self.graphs_a.append(g1)
+            self._outputs.append(self._snapshot())
+            for m in self.masks:            # nothing is staged for the first replay
+                m.zero_()
+        # the captures recorded a step without running it: nothing was published or admitted
 
-    def _segment_a(self):
+    _TABLE_OUTPUTS = ("sub2embed", "_rows", "_cached_embedding", "sub2feat", "used_masks")
+
+    def _snapshot(self):
+        t = self.trainer.table
+        return self.loss, {k: getattr(t, k, None) for k in self._TABLE_OUTPUTS}
+
+    def _expose(self, parity):
+        self.loss, attrs = self._outputs[parity]
+        for k, v in attrs.items():
+            setattr(self.trainer.table, k, v)
+
+    def _segment_a(self, parity=0):
         tr = self.trainer
         self.flat.zero_()
-        if self.ahead is None:
+        if self.ahead is not None:
+            tr.table.staged = (self.rows[parity], self.masks[parity])
+        try:
             tr.table.lookup_and_load(self.static, tr.num_layer)
-            return self._compute_a()
-        with self.ahead:
-            tr.table.lookup_and_load(self.static, tr.num_layer)
-            self.ahead.fork()
-            return self._compute_a()
-
-    def _compute_a(self):
-        tr = self.trainer
+        finally:
+            tr.table.staged = None
         out = tr.model(self.static)
         self.loss = tr.loss_fn(out, self.static.y)
         self.loss.backward()
@@ -371,12 +398,31 @@ class GraphedDataParallelStep:
     def _load(self, batch):
         self.static.copy_from(batch)        # one copy when the batch is packed (Batch.fixed_shape)
 
+    def _announce(self, batch, next_batch):
+        """What is staged in this step's buffer must be for `batch`; the fetch for `next_batch`
+        starts now, into the other buffer, on the look-ahead's own stream."""
+        ah, p = self.ahead, self.parity
+        main = torch.cuda.current_stream(ah.device)
+        main.wait_stream(ah.side)               # the fetch for this step has finished
+        if ah.announced is not batch:
+            self.masks[p].zero_()
+        ah.announced = None
+        if next_batch is not None and self.fits(next_batch):
+            ah.next.copy_from(next_batch)
+            ah.side.wait_stream(main)           # ... and the other buffer's last reader too
+            with torch.cuda.stream(ah.side):
+                ah.table.stage_host_rows(ah.ids, ah.valid, self.rows[1 - p], self.masks[1 - p])
+            ah.announced = next_batch
+
     def run(self, batch, next_batch=None):
         tr = self.trainer
         self._load(batch)
         if self.ahead is not None:
-            self.ahead.announce(batch, next_batch, self.fits)
-        self.graph_a.replay()
+            self._announce(batch, next_batch)
+        self.graphs_a[self.parity].replay()
+        self._expose(self.parity)
+        if self.ahead is not None:
+            self.parity ^= 1
         tr._reduce_flat()
         self.graph_b.replay()
         tr.table.table.fence()

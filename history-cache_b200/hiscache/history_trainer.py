@@ -17,7 +17,7 @@ import torch.nn.functional as F
 from .feature_store import HostFeatureStore
 from .history_cache import HistoryCache
 from .history_model import get_model
-from .sampler import get_loader
+from .sampler import get_loader, wait_ready
 from .util import cfg_get, log
 
 
@@ -108,6 +108,7 @@ class HistoryTrainer:
         """`next_batch` (optional): the batch the following call will get.  The captured step then
         fetches its host feature rows beside this step's compute (hiscache/graphed.py); results do
         not depend on it."""
+        wait_ready(self.device, batch, next_batch)
         g = self.graphed
         if g is not None and g.fits(batch):
             # the ring restart is decided on the host, so it happens outside the captured step

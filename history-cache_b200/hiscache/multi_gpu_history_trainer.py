@@ -18,7 +18,7 @@ import hiscache_backend as hb
 from .feature_store import HostFeatureStore
 from .history_cache import HistoryCache
 from .history_model import get_model
-from .sampler import get_loader
+from .sampler import get_loader, wait_ready
 from .sharded import PeerHistoryTable, ShardedHistoryTable
 from .util import cfg_get, log
 
@@ -237,6 +237,7 @@ class MultiGpuHistoryTrainer:
         the collective that tells every owner that all ranks have published their candidates
         and finished this step's lookups.  `next_batch` (optional) announces the batch of the
         following call, whose host feature rows the captured step then fetches beside its compute."""
+        wait_ready(self.device, batch, next_batch)
         g = self.graphed
         if g is not None and g.fits(batch):
             loss = g.run(batch, next_batch)

@@ -20,6 +20,15 @@ import math
 import torch
 
 
+def wait_ready(device, *batches):
+    """Makes the current stream of `device` wait for batches that were produced on another stream
+    (Loader.iterate_fixed with a stream); a no-op for all others."""
+    for b in batches:
+        ev = getattr(b, "ready", None) if b is not None else None
+        if ev is not None:
+            torch.cuda.current_stream(device).wait_event(ev)
+
+
 def fixed_layout(caps, edge_cap):
     """Byte offsets of a fixed-shape batch's five arrays inside ONE buffer, so that such a batch
     moves (host -> device, or into a captured step's static input) with a single copy:
@@ -37,7 +46,7 @@ def fixed_layout(caps, edge_cap):
 
 class Batch:
     __slots__ = ("ptr", "idx", "sub_to_full", "y", "num_node_in_layer", "num_edge_in_layer", "x",
-                 "edge_type", "typed_num_node_in_layer", "mask", "counters", "fixed", "packed")
+                 "edge_type", "typed_num_node_in_layer", "mask", "counters", "fixed", "packed", "ready")
 
     def __init__(self):
         self.x = None
@@ -47,6 +56,7 @@ class Batch:
         self.counters = None
         self.fixed = None
         self.packed = None      # fixed-shape batches: the one buffer the five arrays are views of
+        self.ready = None       # event after which the arrays are valid (batches drawn on another stream)
 
     @staticmethod
     def fixed_shape(caps, edge_cap, device=None, packed=None):
@@ -385,25 +395,50 @@ class Loader:
                 b = self.sampler.sample(seeds)
             yield b
 
-    def iterate_fixed(self, n_iters, caps, edge_cap, reuse=2):
+    def iterate_fixed(self, n_iters, caps, edge_cap, reuse=2, stream=None, ahead=2):
         """Fixed-shape batches built without any device->host read (NeighborSampler.sample_fixed).
         Seeds are a window of a shuffled order of the training nodes, so they are distinct without
         a de-duplication (whose size would have to reach the host).  `reuse` output buffers are
-        cycled: a yielded batch stays valid until `reuse` more batches have been drawn."""
+        cycled: a yielded batch stays valid until `reuse` more batches have been drawn.
+
+        stream: the batches are drawn there, `ahead` batches in front of the one that is yielded,
+        so that sampling runs beside the consumer's training steps; a yielded batch carries the
+        event `ready` that its consumer's stream has to wait for (sampler.wait_ready; the trainers'
+        train_step does)."""
         n = self.train_ids.shape[0]
+        dev = self.graph.device
         bs = min(self.batch_size, n, int(caps[0]))
         if getattr(self, "_order", None) is None:
-            self._order = self.train_ids[torch.randperm(n, generator=self._gen, device=self.graph.device)]
+            self._order = self.train_ids[torch.randperm(n, generator=self._gen, device=dev)]
             self._cursor = 0
-        outs = [None] * max(1, int(reuse))
-        for k in range(n_iters):
+        ahead = int(ahead) if stream is not None else 0
+        outs = [None] * max(1, int(reuse), ahead + 2 if stream is not None else 1)
+
+        def draw(k):
             if self._cursor + bs > n:
                 self._cursor = 0
             seeds = self._order[self._cursor:self._cursor + bs]
             self._cursor += bs
             b = self.sampler.sample_fixed(seeds, caps, edge_cap, out=outs[k % len(outs)])
             outs[k % len(outs)] = b.fixed
-            yield b
+            return b
+
+        if stream is None:
+            for k in range(n_iters):
+                yield draw(k)
+            return
+        queue = []
+        for k in range(n_iters + ahead):
+            if k < n_iters:
+                # the step that used the buffer refilled now was issued at least two steps ago
+                stream.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(stream):
+                    b = draw(k)
+                    b.ready = torch.cuda.Event()
+                    b.ready.record(stream)
+                queue.append(b)
+            if k >= ahead:
+                yield queue.pop(0)
 
     @property
     def train_loader(self):

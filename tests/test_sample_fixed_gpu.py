@@ -76,3 +76,19 @@ def test_iterate_fixed_feeds_a_training_run(backend):
     it = loader.iterate_fixed(12, caps, ecap)
     losses = [float(tr.train_step(b)) for b in it]
     assert all(np.isfinite(losses)) and tr.table.header > 0
+
+
+def test_iterate_fixed_on_its_own_stream_yields_the_same_batches(backend):
+    """Drawing ahead on a second stream changes when a batch is sampled, not what it holds."""
+    from hiscache.sampler import Loader, wait_ready
+    g = _graph()
+    dev = torch.device("cuda:0")
+    a = Loader(g, [15, 10, 5], 256, "history_uvm", seed=1, iters_per_epoch=1 << 30)
+    b = Loader(g, [15, 10, 5], 256, "history_uvm", seed=1, iters_per_epoch=1 << 30)
+    caps, ecap = a.calibrate(8, slack=1.2, align=64)
+    side = torch.cuda.Stream(device=dev)
+    for x, y in zip(a.iterate_fixed(9, caps, ecap), b.iterate_fixed(9, caps, ecap, stream=side, ahead=2)):
+        assert x.ready is None and y.ready is not None
+        wait_ready(dev, y)
+        for k in ("ptr", "idx", "sub_to_full", "mask", "y"):
+            assert torch.equal(getattr(x, k), getattr(y, k)), k
