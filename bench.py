@@ -516,7 +516,8 @@ def run_ours(args):
         ms_load, _ = per_launch("hc_load_rows")
         if ms_load:
             byts = host_rows_per_step * feat_bytes
-            top.append({"kernel": "load_rows_bulk_kernel (batch.x assembly; host rows over the host link)",
+            top.append({"kernel": "load_rows_bulk_kernel (batch.x assembly with ALL host rows read in the step, as the "
+                                  "eager step and a step without look-ahead do)",
                         "bound": "host-link", "ms_per_launch": round(ms_load, 4),
                         "bytes_per_launch": int(byts), "achieved": round(byts / ms_load / 1e6, 2),
                         "peak": host_link_peak, "unit": "GB/s",
@@ -524,6 +525,17 @@ def run_ours(args):
                         "peak_source": "pinned cudaMemcpy H2D of 256 MB on this box, best of 5",
                         "note": "algorithmic bytes = host rows x row bytes; the same launch also copies the "
                                 "feature-cache rows inside HBM"})
+        if stage_ms:
+            byts = staged[0] / steps_value * feat_bytes
+            top.append({"kernel": "stage_rows_kernel (look-ahead: the next batch's host rows, beside the step)",
+                        "bound": "host-link", "ms_per_launch": round(stage_ms, 4),
+                        "bytes_per_launch": int(byts), "achieved": round(byts / stage_ms / 1e6, 2),
+                        "peak": host_link_peak, "unit": "GB/s",
+                        "frac": round(byts / stage_ms / 1e6 / host_link_peak, 4) if host_link_peak else None,
+                        "peak_source": "pinned cudaMemcpy H2D of 256 MB on this box, best of 5",
+                        "note": "timed alone; deliberately a small grid (16 blocks): with more host reads "
+                                "outstanding the step's own kernels slow down by more than the call gains, and "
+                                "all it has to do is finish within the step it runs beside"})
         dom = f"hc_aggr_fwd[f16,F={args.feat}]"
         ms_f, _ = per_launch(dom)
         if ms_f:
@@ -688,14 +700,16 @@ MAG_REL_TABLE = [0, 1, 1,      # into a paper  from paper / author / institution
 
 
 def _time_steps(step, batches, warmup):
-    for b in batches[:warmup]:
-        step(b)
+    """Every step is told which batch follows (a captured step fetches its host rows ahead)."""
+    nxt = lambda i: batches[i + 1] if i + 1 < len(batches) else None
+    for i in range(warmup):
+        step(batches[i], nxt(i))
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
-    for b in batches[warmup:]:
-        step(b)
+    for i in range(warmup, len(batches)):
+        step(batches[i], nxt(i))
     e1.record()
     issue = (time.perf_counter() - t0) * 1e3
     torch.cuda.synchronize()
