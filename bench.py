@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--graph", default=os.environ.get("HC_BENCH_GRAPH", "auto"), choices=["auto", "on", "off"],
                     help="replay the step from CUDA graphs over fixed-shape (padded) batches: one graph on "
                          "one GPU, two captured segments around the eager gradient all-reduce on several")
+    ap.add_argument("--huge-pages", action="store_true",
+                    help="one GPU: back the host feature table with 2 MB transparent huge pages")
     ap.add_argument("--look-ahead", default="on", choices=["on", "off"],
                     help="the captured step fetches the next batch's host feature rows beside its compute")
     ap.add_argument("--graph-slack", type=float, default=1.03,
@@ -166,7 +168,8 @@ def setup_workload(args, rank, world, device, need_features=True):
             if rank == 0:
                 os.unlink(os.path.join("/dev/shm", name))  # pages stay while mapped
         else:
-            uvm = HostFeatureStore.synthetic(args.nodes, args.feat, torch.float16, args.seed, device)
+            uvm = HostFeatureStore.synthetic(args.nodes, args.feat, torch.float16, args.seed, device,
+                                             huge_pages=args.huge_pages)
     t_feat = time.time() - t0
     fanouts = [int(f) for f in args.fanouts.split(",")]
     loader = Loader(graph, fanouts, args.batch, "history_uvm", seed=args.seed, rank=rank, world=world,

@@ -44,11 +44,28 @@ class HostFeatureStore:
     # -- construction -------------------------------------------------------
     @staticmethod
     def synthetic(num_nodes, feat, dtype=torch.float16, seed=0, device="cuda:0", shared_name=None,
-                  rank=0, world=1, chunk_rows=1 << 22):
+                  rank=0, world=1, chunk_rows=1 << 22, huge_pages=False):
         """N(0,1) rows generated on the GPU in chunks and copied to page-locked host memory.
         With `shared_name`, rank 0 of a box fills /dev/shm/<shared_name> and every rank maps
-        and registers the same pages (the caller must barrier between fill and use)."""
+        and registers the same pages (the caller must barrier between fill and use).
+        huge_pages (private table only): an anonymous mapping advised to use 2 MB transparent
+        huge pages, registered with CUDA after it has been filled."""
         device = torch.device(device)
+        if shared_name is None and huge_pages:
+            nbytes = num_nodes * feat * torch.empty(0, dtype=dtype).element_size()
+            two_mb = 2 << 20
+            mm = mmap.mmap(-1, nbytes + two_mb, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS)
+            mm.madvise(mmap.MADV_HUGEPAGE)
+            raw = np.frombuffer(mm, dtype=np.uint8)
+            off = (-raw.ctypes.data) % two_mb
+            arr = raw[off:off + nbytes].view(_NP[dtype]).reshape(num_nodes, feat)
+            buf = torch.from_numpy(arr)
+            HostFeatureStore._fill(buf, seed, device, chunk_rows)       # touches every page
+            with torch.cuda.device(device):
+                rc = torch.cuda.cudart().cudaHostRegister(buf.data_ptr(), nbytes, 0)
+            if int(rc) != 0:
+                raise RuntimeError(f"cudaHostRegister failed with {rc}")
+            return HostFeatureStore(buf, device, _keepalive=mm)
         if shared_name is None:
             buf = torch.empty((num_nodes, feat), dtype=dtype, pin_memory=True)
             HostFeatureStore._fill(buf, seed, device, chunk_rows)
