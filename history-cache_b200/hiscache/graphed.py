@@ -8,6 +8,11 @@ replayed with a single launch.  Padding rows have no neighbours, are masked out 
 norm statistics, the loss, the admission quantile and the admission itself, so a replayed step
 computes what the eager step computes on the unpadded batch.
 
+Once the step is replayed it is bound by the GPU, and its longest kernel is the read of host
+feature rows; the captured step therefore has branches beside its main chain: the host rows of
+the NEXT batch (_LookAhead), the optimiser step beside the history update, and, where the
+sampler is captured too, the drawing of the batch after next.
+
 The reference has no counterpart (it runs eagerly: hiscache/history_trainer.py:176-193).
 """
 from __future__ import annotations

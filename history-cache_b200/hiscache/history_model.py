@@ -69,68 +69,6 @@ def tall_linear(x, w, b):
     return _TallLinear.apply(x, w, b) if SPLIT_WGRAD > 1 else F.linear(x, w, b)
 
 
-FUSE_BIAS = os.environ.get("HISCACHE_FUSE_BIAS", "1") not in ("", "0")
-_PAD = 4            # columns appended for the bias (fp32: keeps rows 16-byte multiples)
-_ones_pad = {}      # (rows, device) -> [rows, _PAD] holding 1, 0, 0, 0
-_zero_pad = {}      # (rows, device) -> [rows, _PAD - 1] zeros
-
-
-def _pad_blocks(n, h, dev):
-    key = (n, dev)
-    if key not in _ones_pad:
-        t = torch.zeros((n, _PAD), dtype=torch.float32, device=dev)
-        t[:, 0] = 1.0
-        _ones_pad[key] = t
-    key2 = (h, dev)
-    if key2 not in _zero_pad:
-        _zero_pad[key2] = torch.zeros((h, _PAD - 1), dtype=torch.float32, device=dev)
-    return _ones_pad[key], _zero_pad[key2]
-
-
-class _SageProduct(torch.autograd.Function):
-    """lin_l(aggr) + lin_r(root) with the bias as ONE product
-
-        [aggr | root | 1 0 0 0] @ [Wl | Wr | b 0 0 0].T
-
-    so that one slab-batched product in backward yields the gradients of both weights AND of the
-    bias (no ones-row product, no column sum of its own), and each of the three is reduced over
-    the slabs straight into its own contiguous tensor (no split copies of a fused gradient).
-    Per layer and step this replaces seven small launches by four.  The parameters stay
-    lin_l.weight, lin_l.bias and lin_r.weight."""
-
-    @staticmethod
-    def forward(ctx, aggr, root, wl, wr, b):
-        n, f = aggr.shape
-        ones, zeros = _pad_blocks(n, wl.shape[0], aggr.device)
-        xc = torch.cat([aggr, root, ones], dim=1)
-        wc = torch.cat([wl, wr, b.unsqueeze(1), zeros], dim=1)
-        ctx.save_for_backward(xc, wc)
-        ctx.f = f
-        return xc @ wc.t()
-
-    @staticmethod
-    def backward(ctx, g):
-        xc, wc = ctx.saved_tensors
-        f = ctx.f
-        g = g.contiguous()
-        n = xc.shape[0]
-        ga = gr = None
-        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
-            gx = g @ wc[:, :2 * f]
-            ga, gr = gx[:, :f], gx[:, f:]
-        s = SPLIT_WGRAD
-        while s > 1 and (n % s or n // s < 256):
-            s //= 2
-        if s > 1:
-            parts = torch.bmm(g.view(s, n // s, -1).transpose(1, 2), xc.view(s, n // s, -1))
-        else:
-            parts = (g.t() @ xc).unsqueeze(0)
-        gwl = parts[:, :, :f].sum(0)
-        gwr = parts[:, :, f:2 * f].sum(0)
-        gb = parts[:, :, 2 * f].sum(0)
-        return ga, gr, gwl, gwr, gb
-
-
 class MaskedBatchNorm1d(torch.nn.BatchNorm1d):
     """BatchNorm1d whose batch statistics ignore padding rows.  With mask=None it is the
     stock module (same parameters and buffers, so state dicts are interchangeable); with a
@@ -229,10 +167,7 @@ class MySageConvHistory(torch.nn.Module):
         if self.root_weight:
             root = x[:num_node] if num_node != 0 else x
             root = root if root.dtype == out.dtype else root.to(out.dtype)
-            if (FUSE_ROOT_PRODUCT and FUSE_BIAS and self.lin_l.bias is not None and out.is_cuda
-                    and out.dtype == torch.float32 and torch.is_grad_enabled()):
-                out = _SageProduct.apply(out, root, self.lin_l.weight, self.lin_r.weight, self.lin_l.bias)
-            elif FUSE_ROOT_PRODUCT:
+            if FUSE_ROOT_PRODUCT:
                 # lin_l(aggr) + lin_r(root) as ONE product over [aggr | root]: half the GEMM launches of
                 # the layer in forward and backward (their shapes are small and launch-bound)
                 w = torch.cat([self.lin_l.weight, self.lin_r.weight], dim=1)
