@@ -426,7 +426,8 @@ def run_ours(args):
                 continue
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            trainer.table.stage_host_rows(b.sub_to_full, b.mask, ah.rows, ah.mask)
+            trainer.table.stage_host_rows(b.sub_to_full, b.mask, ah.rows, ah.mask,
+                                          max_blocks=getattr(trainer.graphed, "stage_blocks", None))
             e1.record()
             t_st.append((e0, e1))
         torch.cuda.synchronize()
@@ -618,7 +619,7 @@ def run_ours(args):
             "fetched_in_vain_frac": round((staged[0] - stats[2]) / max(staged[0], 1), 4),
             "host_link_bytes_per_step": int((staged[0] + stats[0]) / steps_value * feat_bytes),
             "staging_call_alone_ms": round(stage_ms, 4) if stage_ms else None,
-            "staging_blocks": hb.STAGE_BLOCKS or 16,
+            "staging_blocks": hb.STAGE_BLOCKS or getattr(trainer.graphed, "stage_blocks", 16),
             "value_without": round(world * K / (statistics.median(plain_ms) * 1e-3), 2) if plain_ms else None,
             "note": "the captured step fetches the NEXT batch's host feature rows on a second branch beside "
                     "its own compute (hiscache/graphed.py); rows whose consumers turn out to be served from "

@@ -403,6 +403,11 @@ class GraphedDataParallelStep:
     def _load(self, batch):
         self.static.copy_from(batch)        # one copy when the batch is packed (Batch.fixed_shape)
 
+    # The fetch has the whole step to hide behind here (not only the part after the load, as in the
+    # one-graph form), so it takes a smaller grid than the library's default of 16: measured on two
+    # GPUs 2 113 iterations/s with 12 blocks (0.76 ms alone) against 2 041 with 16 (0.60 ms alone).
+    stage_blocks = 12
+
     def _announce(self, batch, next_batch):
         """What is staged in this step's buffer must be for `batch`; the fetch for `next_batch`
         starts now, into the other buffer, on the look-ahead's own stream."""
@@ -416,7 +421,8 @@ class GraphedDataParallelStep:
             ah.next.copy_from(next_batch)
             ah.side.wait_stream(main)           # ... and the other buffer's last reader too
             with torch.cuda.stream(ah.side):
-                ah.table.stage_host_rows(ah.ids, ah.valid, self.rows[1 - p], self.masks[1 - p])
+                ah.table.stage_host_rows(ah.ids, ah.valid, self.rows[1 - p], self.masks[1 - p],
+                                         max_blocks=self.stage_blocks)
             ah.announced = next_batch
 
     def run(self, batch, next_batch=None):

@@ -215,7 +215,7 @@ class HistoryCache:
         return st
 
     @torch.no_grad()
-    def stage_host_rows(self, ids, valid, rows_out, mask_out):
+    def stage_host_rows(self, ids, valid, rows_out, mask_out, max_blocks=None):
         """Fetches, ahead of the step that will use them, the host rows of the nodes `ids` ([n]
         global ids, `valid` [n] marking the entries that are real) into rows_out / mask_out;
         `lookup_and_load` of a batch with these ids then reads those rows from device memory
@@ -224,11 +224,14 @@ class HistoryCache:
         from the host as before.  Rows that the step turns out not to need (their consumers are
         served from history) were moved in vain; results never change, since host rows are
         constant.  May run on any stream, also beside a step that is admitting rows: the map is
-        read with whole-word loads and either value of an entry is handled.
+        read with whole-word loads and either value of an entry is handled.  `max_blocks`: grid
+        of the staging kernel (None: the library's default; fewer blocks disturb the step less
+        and take longer).
 
         The reference loads inside the step only (hiscache/history_cache.py:327-350)."""
         sub2feat = hb.map_lookup(self.full2embed, ids, offset=self.total_num_node)
-        hb.stage_host_rows(self.uvm.buffer, ids, sub2feat, valid, rows_out, mask_out, stats=self.stage_stats)
+        hb.stage_host_rows(self.uvm.buffer, ids, sub2feat, valid, rows_out, mask_out, stats=self.stage_stats,
+                           max_blocks=max_blocks)
 
     # -- admission ----------------------------------------------------------
     def score_sink(self, n):

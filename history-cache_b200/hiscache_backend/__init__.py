@@ -822,7 +822,7 @@ def load_rows(host_table, feat_cache, sub_to_full, sub2feat, used, out_dtype=Non
     return (x, mask.view(torch.bool)) if want_mask else x
 
 
-# thread blocks of a staging call (0 = the library's default); a tuning knob for measurements
+# thread blocks of a staging call; non-zero overrides every caller's choice (a knob for measurements)
 STAGE_BLOCKS = int(os.environ.get("HISCACHE_STAGE_BLOCKS", "0"))
 
 
@@ -851,7 +851,7 @@ def stage_host_rows(host_table, ids, sub2feat, consider, rows_out, mask_out, sta
         check(lib.hc_stage_host_rows(ptr(host_table), dtype_code(host_table), host_table.shape[0],
                                      host_table.stride(0) if host_table.shape[0] > 1 else F, F, ptr(ids),
                                      ptr(sub2feat), ptr(consider), n, ptr(rows_out), ptr(mask_out), ptr(stats),
-                                     int(STAGE_BLOCKS if max_blocks is None else max_blocks),
+                                     int(STAGE_BLOCKS or (max_blocks or 0)),
                                      stream_of(dev)), "hc_stage_host_rows")
     _called()
 
