@@ -754,7 +754,7 @@ def _peak():
     return float(peaks.get("hbm_gbs", 6650.0)), ("measured" if peaks else "fallback")
 
 
-def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, seed=0):
+def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, seed=0, graph=True):
     """configs[1]: 3-layer SAGE (hidden 256, 47 classes) on a 2.4 M-node power-law graph (Zipf 2.0,
     mean out-degree 26), fp32 dim-100 features in HBM, batch 1 000, fan-outs 15/10/5, per-layer
     history tables with a staleness limit of 10 iterations (HistoryTableTrainer)."""
@@ -772,11 +772,32 @@ def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, see
     loader = Loader(graph, fan, 1000, "memory", seed=seed, iters_per_epoch=1 << 30)
     tr = HistoryTableTrainer(cfg, graph=graph, uvm=uvm, loader=loader, seed=seed)
     tr.model.train()
-    it = loader.train_loader
-    batches = [next(it) for _ in range(warmup + steps)]
+    captured = False
+    if graph:
+        # the step replayed from one CUDA graph over fixed-shape batches; the first steps run eagerly
+        # (they also fill the tables), then the capture
+        caps, ecap = loader.calibrate(48, slack=1.03, align=128)
+        it = loader.iterate_padded(1 << 30, caps, ecap)
+        batches = [next(it) for _ in range(warmup + steps)]
+        fit = [b for b in batches if b.mask is not None]
+        n_eager = min(warmup, 12)
+        for b in batches[:n_eager]:
+            tr.train_step(b)
+        if len(fit) >= 2:
+            tr.enable_cuda_graph(caps, ecap, fit[:2])
+            captured = True
+    else:
+        it = loader.train_loader
+        batches = [next(it) for _ in range(warmup + steps)]
     ms, issue = _time_steps(tr.train_step, batches, warmup)
     hits = sum(int((m != -1).sum()) for m in tr.table.sub_to_history)
+    ms_eager = None
+    if captured:
+        tr.graphed.enabled = False
+        ms_eager, _ = _time_steps(tr.train_step, batches[warmup:warmup + 30], 5)
     kt = _kernel_table(tr, batches[warmup:], min(steps, 20))
+    if captured:
+        tr.graphed.enabled = True
     n_prof = min(steps, 20)
     peak, src = _peak()
     dom = f"hc_aggr_fwd[f32,F={feat}]"
@@ -790,10 +811,14 @@ def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, see
                 "us_per_launch": round(ms_l * 1e3, 2), "traffic": None,
                 "note": "block far smaller than L2: latency bound; history hits counted as gathered"}
     out = {"workload": "configs[1]: 3-layer SAGE, 2.4M-node power-law graph, fp32 dim-100 features in HBM, "
-                       "per-layer history tables, staleness limit 10",
+                       "per-layer history tables, staleness limit 10"
+                       + ("; step replayed from one CUDA graph over fixed-shape batches" if captured else ""),
            "value": round(1e3 / ms, 2), "unit": "iters/s", "ms_per_step": round(ms, 4), "steps": steps,
            "warmup": warmup, "host_issue_ms_per_step": round(issue, 4), "nodes": nodes, "edges": graph.num_edges,
            "history_hits_last_step": hits, "roofline": roof,
+           "cuda_graph": ({"caps": caps, "edge_cap": ecap,
+                           "fixed_shape_batches": f"{sum(1 for b in batches if b.mask is not None)}/{len(batches)}",
+                           "eager_value": round(1e3 / ms_eager, 2) if ms_eager else None} if captured else None),
            "kernel_ms_per_step": {k: round(v["ms_total"] / n_prof, 4) for k, v in sorted(kt.items())}}
     if cpu_steps > 0:
         sys.path.insert(0, os.path.join(ROOT, "oracle"))
@@ -805,15 +830,16 @@ def bench_config2(device, steps=60, warmup=25, nodes=2_400_000, cpu_steps=3, see
         host = feats.cpu().numpy()
         ctr = CpuTrainer(host, nodes, feat, hidden, classes, 3, buffer_elems=600_000 * 256,
                          sorted_indices=graph.sorted_indices.cpu().numpy()[:0], rate=0.5, staleness=10, seed=seed)
+        nat_it = loader.train_loader        # the same workload in its natural (unpadded) shape
         cb = [(b.ptr.cpu().numpy(), b.idx.cpu().numpy(), b.sub_to_full.cpu().numpy(), b.y.cpu().numpy(),
-               [int(v) for v in b.num_node_in_layer]) for b in batches[:cpu_steps + 1]]
+               [int(v) for v in b.num_node_in_layer]) for b in [next(nat_it) for _ in range(cpu_steps + 1)]]
         ctr.step(*cb[0])
         t0 = time.time()
         for c in cb[1:]:
             ctr.step(*c)
         dt = time.time() - t0
         out["cpu_baseline"] = {"value": round(cpu_steps / dt, 4), "unit": "iters/s", "cores": cores, "kind": "port",
-                               "sample": f"{cpu_steps} iterations of the same batches after 1 warm-up, CPU restatement "
+                               "sample": f"{cpu_steps} iterations of the same workload after 1 warm-up, CPU restatement "
                                          "with ONE unified history buffer of the same number of rows (the per-layer "
                                          "table trainer has no CPU restatement); history starts empty"}
     del tr, feats, uvm, graph
@@ -1053,7 +1079,8 @@ def run_other(args):
         return
     cs = 0 if args.no_cpu_baseline else args.cpu_steps
     if args.config == 2:
-        r = bench_config2(device, steps=args.steps, warmup=args.warmup, cpu_steps=cs, seed=args.seed)
+        r = bench_config2(device, steps=args.steps, warmup=args.warmup, cpu_steps=cs, seed=args.seed,
+                          graph=args.graph != "off")
     else:
         r = bench_config5(device, steps=args.steps, warmup=args.warmup, cpu_steps=cs, seed=args.seed,
                           nodes=min(args.nodes, 16_000_000), cache_gb=args.cache_gb)

@@ -224,7 +224,8 @@ class HistorySAGE(torch.nn.Module):
                 t.history_out.append(his)
             else:
                 x, his = conv(x, batch.ptr, batch.idx, None, None, 0, n)
-            x = self.bns[i].act(x, None, self.dropout)
+            mask = getattr(batch, "mask", None)   # fixed-shape batches carry a row mask
+            x = self.bns[i].act(x, None if mask is None else mask[:n], self.dropout)
         x, his = self.convs[-1](x, batch.ptr, batch.idx, None, None, 0, int(nn[0]))
         return x.log_softmax(dim=-1)
 

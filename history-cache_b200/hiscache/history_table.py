@@ -64,6 +64,19 @@ class HistoryTable:
         self.graph_struct_norm = int(cfg_get(config, "history.graph_struct_norm", 0))
         self.sub_to_history = []
         self._compact = None
+        # With `iter_dev` (a device int64[1], see use_device_iteration) check-in stamps and the
+        # staleness test take the iteration number from the device, so that a step replayed from
+        # a CUDA graph stamps and evicts with the right value.
+        self.iter_dev = None
+
+    def use_device_iteration(self, glb_iter=0):
+        """Keeps the iteration counter on the device from now on (`tick()` advances it)."""
+        self.iter_dev = torch.full((1,), int(glb_iter), dtype=torch.int64, device=self.device)
+        return self.iter_dev
+
+    def tick(self):
+        if self.iter_dev is not None:
+            self.iter_dev.add_(1)
 
     def show(self):
         print("used_table", [int((h != -1).sum()) for h in self.history_to_full_layered])
@@ -77,18 +90,22 @@ class HistoryTable:
         return [self.hidden_channels] * (self.num_layers - 1) + [self.out_channels]
 
     # -- lookup (history_table.py:94-125) ------------------------------------
-    def lookup(self, sub_to_full, num_node_in_layer):
+    def lookup(self, sub_to_full, num_node_in_layer, valid=None):
         """sub_to_history[layer][r] = table slot of node r or -1 (seeds always -1).  The
         compacted forms the reference also builds (`tmp_history_buffer_layered`,
         `sub_to_history_layered`) are made on first read: the aggregation kernel can index the
-        table with `sub_to_history` directly."""
+        table with `sub_to_history` directly.  `valid`: row mask of a fixed-shape batch; padding
+        rows never hit."""
         self.sub_to_history = []
         self._compact = None
         num_seed = int(num_node_in_layer[0])
         for layer_id in range(self.num_layers):
             n = int(num_node_in_layer[self.num_layers_all - 1 - layer_id])
-            self.sub_to_history.append(hb.map_lookup(self.full_to_history_layered[layer_id],
-                                                     sub_to_full[:n], force_miss_below=num_seed))
+            s2h = hb.map_lookup(self.full_to_history_layered[layer_id], sub_to_full[:n],
+                                force_miss_below=num_seed)
+            if valid is not None:
+                s2h = torch.where(valid[:n], s2h, torch.full_like(s2h, -1))
+            self.sub_to_history.append(s2h)
 
     def _build_compact(self):
         bufs, maps = [], []
@@ -138,21 +155,43 @@ class HistoryTable:
             num_node = int(batch.num_node_in_layer[self.num_layers_all - 1 - layer_id])
             his = self.history_out[layer_id][:num_node]
             score = self._score(layer_id, batch, num_node)
-            thres = hb.select_threshold(score, self.rate)
+            used, thres = used_masks[layer_id + 1], self._threshold(score, self.rate, batch, num_node)
+            valid = getattr(batch, "mask", None)
+            if valid is not None:       # padding rows of a fixed-shape batch are never admitted
+                used = used[:num_node] & valid[:num_node]
+            stamp = glb_iter if self.iter_dev is None else hb.CHECKIN_MARKER
             hb.record_history(his.detach(), self.history_buffer_layered[layer_id],
-                              used_masks[layer_id + 1], sub_to_full, self.sub_to_history[layer_id],
+                              used, sub_to_full, self.sub_to_history[layer_id],
                               self.history_to_full_layered[layer_id],
                               self.full_to_history_layered[layer_id],
                               self.cuda_header_layered[layer_id], score, thres,
-                              self.checkin_iter[layer_id], glb_iter)
+                              self.checkin_iter[layer_id], stamp)
+            if self.iter_dev is not None:
+                hb.stamp_checkin(self.checkin_iter[layer_id], self.iter_dev)
+
+    def _threshold(self, score, q, batch, num_node):
+        """torch.quantile(score, q) over the real rows of the batch (history_table.py:173,230)."""
+        valid = getattr(batch, "mask", None)
+        if valid is None:
+            return hb.select_threshold(score, q)
+        v = valid[:num_node]
+        padded = torch.where(v, score, torch.full_like(score, float("inf")))
+        return hb.select_threshold(padded, q, n_valid=v.sum(dtype=torch.int64).reshape(1))
+
+    def _evict_stale(self, layer_id, glb_iter, limit):
+        if self.iter_dev is None:
+            hb.evict_stale(self.checkin_iter[layer_id], self.history_to_full_layered[layer_id],
+                           self.full_to_history_layered[layer_id], glb_iter, limit)
+        else:
+            hb.evict_stale_dev(self.checkin_iter[layer_id], self.history_to_full_layered[layer_id],
+                               self.full_to_history_layered[layer_id], self.iter_dev, limit)
 
     # -- eviction (history_table.py:189-254) ---------------------------------
     def evict_by_staleness(self, glb_iter, staleness_thres):
         if isinstance(staleness_thres, int):
             staleness_thres = [staleness_thres] * self.num_layers
         for layer_id in range(self.num_layers):
-            hb.evict_stale(self.checkin_iter[layer_id], self.history_to_full_layered[layer_id],
-                           self.full_to_history_layered[layer_id], glb_iter, staleness_thres[layer_id])
+            self._evict_stale(layer_id, glb_iter, staleness_thres[layer_id])
 
     def evict_by_both(self, batch, glb_iter, staleness_thres):
         if self.method == "staleness":
@@ -165,12 +204,11 @@ class HistoryTable:
                 continue
             num_node = int(batch.num_node_in_layer[self.num_layers_all - 1 - layer_id])
             score = self._score(layer_id, batch, num_node)
-            thres = hb.select_threshold(score, 1 - self.rate)
+            thres = self._threshold(score, 1 - self.rate, batch, num_node)
             hb.evict_by_score(self.sub_to_history[layer_id], score, thres, self.checkin_iter[layer_id],
                               self.history_to_full_layered[layer_id],
                               self.full_to_history_layered[layer_id])
-            hb.evict_stale(self.checkin_iter[layer_id], self.history_to_full_layered[layer_id],
-                           self.full_to_history_layered[layer_id], glb_iter, staleness_thres[layer_id])
+            self._evict_stale(layer_id, glb_iter, staleness_thres[layer_id])
 
     def evict_history(self, batch, glb_iter):
         self.evict_by_both(batch, glb_iter, self.staleness_thres)

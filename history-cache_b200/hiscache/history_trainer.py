@@ -44,31 +44,65 @@ class HistoryTableTrainer:
         self.table = HistoryTable(config, total_num_node=g.num_nodes, storage_dtype=storage_dtype)
         self.model = get_model(config, self.table).to(self.device)
         self.optimizer = torch.optim.Adam(self.model.parameters(), lr=cfg_get(config, "train.optimizer.lr", 1e-3),
-                                          fused=True)
+                                          fused=True, capturable=True)
         self.loss_fn = F.nll_loss
         self.num_layer = len(self.model.convs)
         self.glb_iter = 0
+        self.graphed = None
 
     def train_step(self, batch, next_batch=None):
+        wait_ready(self.device, batch, next_batch)
+        g = self.graphed
+        if g is not None and g.fits(batch):
+            loss = g.run(batch, next_batch)
+        else:
+            loss = self._step_body(batch)
+        self.glb_iter += 1
+        return loss
+
+    def _step_body(self, batch, reset=False, after_load=None, opt_stream=None):
+        """One iteration on the device.  Once the table keeps its iteration counter on the device
+        (enable_cuda_graph) the body contains no host-side value that changes from step to step
+        and can be captured in a CUDA graph."""
         import hiscache_backend as hb
         t = self.table
         self.optimizer.zero_grad(set_to_none=True)
         nn = [int(v) for v in batch.num_node_in_layer]
-        t.lookup(batch.sub_to_full, nn)
+        t.lookup(batch.sub_to_full, nn, valid=getattr(batch, "mask", None))
         # history exists one hop from the seeds as far as the pruning kernel is concerned
         # (grad_check.cu:122-124): that is table layer num_layers_all - 2
         hop1 = t.sub_to_history[t.num_layers_all - 2] if t.num_layers_all >= 2 else None
         used = hb.count_history_reconstruct(batch.ptr, batch.idx, hop1, batch.sub_to_full.shape[0],
                                             batch.y.shape[0], self.num_layer)
         batch.x = hb.load_rows(self.uvm.buffer, None, batch.sub_to_full, None, used[0])
+        if after_load is not None:
+            after_load()
         out = self.model(batch)
         loss = self.loss_fn(out, batch.y)
         loss.backward()
-        self.optimizer.step()
+        if opt_stream is None:
+            self.optimizer.step()
+        else:           # beside the table update: they share no data
+            main = torch.cuda.current_stream(self.device)
+            opt_stream.wait_stream(main)
+            with torch.cuda.stream(opt_stream):
+                self.optimizer.step()
         t.record_history(batch.sub_to_full, batch, self.glb_iter, used)
         t.evict_history(batch, self.glb_iter)
-        self.glb_iter += 1
+        t.tick()
+        if opt_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(opt_stream)
         return loss
+
+    def enable_cuda_graph(self, caps, edge_cap, warmup_batches, look_ahead=False):
+        """Replays the step for fixed-shape batches of these caps from one CUDA graph
+        (hiscache/graphed.py).  The table's iteration counter moves to the device."""
+        from .graphed import GraphedStep
+        self.model.train()
+        if self.table.iter_dev is None:
+            self.table.use_device_iteration(self.glb_iter)
+        self.graphed = GraphedStep(self, caps, edge_cap, warmup_batches, look_ahead=look_ahead)
+        return self.graphed
 
 
 class HistoryTrainer:
