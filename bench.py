@@ -441,7 +441,7 @@ def run_ours(args):
     cut = None
     if use_graph and world == 1:
         # the device-side fixed-shape sampler is captured in front of the step: one launch per step
-        trainer.enable_sampled_cuda_graph(caps, ecap)
+        trainer.enable_sampled_cuda_graph(caps, ecap, look_ahead=look_ahead)
         samp_feed = lambda xs: [trainer.train_step_sampled() for _ in xs]
         samp_note = ("sampling (hc_sample_fixed, no host read-back) and the step replayed as ONE CUDA graph; "
                      "seeds are windows of a shuffled order of the training nodes")
