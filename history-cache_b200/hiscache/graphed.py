@@ -233,15 +233,10 @@ class GraphedSampledStep:
         return b
 
     def _like(self, b):
-        c = Batch()
-        for k in self._KEYS:
-            setattr(c, k, torch.empty_like(getattr(b, k)))
-        c.num_node_in_layer, c.num_edge_in_layer = b.num_node_in_layer, b.num_edge_in_layer
-        return c
+        return Batch.fixed_shape(self.caps, self.edge_cap, device=b.ptr.device)
 
     def _copy(self, dst, src):
-        for k in self._KEYS:
-            getattr(dst, k).copy_(getattr(src, k), non_blocking=True)
+        dst.copy_from(src)      # one copy: the sampler's output is one buffer too
 
     def _body(self):
         tr, ah = self.trainer, self.ahead

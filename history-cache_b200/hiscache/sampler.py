@@ -177,17 +177,22 @@ class NeighborSampler:
         if int(self.batch_no) != getattr(self, "_batch_no_seen", -1):
             self._batch_no_dev.fill_(int(self.batch_no))     # follow the host-side counter
         L = len(self.fanouts)
+        if out is None:     # the five arrays are views of one buffer, so the batch moves with one copy
+            pk = Batch.fixed_shape(list(caps), int(edge_cap), device=dev)
+            out = {"ptr": pk.ptr, "idx": pk.idx, "sub_to_full": pk.sub_to_full, "mask": pk.mask, "y": pk.y,
+                   "counters": torch.zeros(4, dtype=torch.int64, device=dev), "packed": pk.packed}
         o = hb.sample_fixed(g.ptr, g.idx, seeds, self.local, self.seed, self._batch_no_dev, self.fanouts,
                             list(caps), int(edge_cap), out=out)
         self.batch_no += 1
         self._batch_no_seen = int(self.batch_no)
         b = Batch()
         b.ptr, b.idx, b.sub_to_full, b.mask = o["ptr"], o["idx"][:int(edge_cap)], o["sub_to_full"], o["mask"]
-        if out is None or "y" not in o:
+        if "y" not in o:
             o["y"] = torch.full((caps[0],), -100, dtype=torch.int64, device=dev)
         o["y"].fill_(-100)
         o["y"][:seeds.shape[0]] = g.labels[seeds]
         b.y = o["y"]
+        b.packed = o.get("packed")
         b.num_node_in_layer = torch.tensor(list(caps), dtype=torch.int64)
         b.num_edge_in_layer = torch.tensor([int(edge_cap)] * L, dtype=torch.int64)
         b.counters, b.fixed = o["counters"], o
